@@ -1,0 +1,114 @@
+/* natsl_b200.h — C ABI of the B200 (sm_100a) NAtSL hybrid-attention kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*),
+ * launches asynchronously on that stream and returns an int status: 0 on success, a
+ * negative NATSL_ERR_* code otherwise, with a message available from natsl_last_error()
+ * (per calling thread).  Nothing here allocates device memory: the caller owns every
+ * buffer.  Tensors are contiguous, token-major:  q,k [B,T,H,K], v,o [B,T,H,V], g,beta
+ * [B,T,H].  Activations are bf16; decays, scales and states are fp32.
+ *
+ * Reference = automl/NeuralAttentionSearchLinear; paths below are relative to its root.
+ * The reference has no native FFI: its hot path is Triton launched from Python, so each
+ * entry cites the Python/Triton function it replaces.
+ */
+#ifndef NATSL_B200_H
+#define NATSL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NATSL_B200_ABI_VERSION 1
+
+/* element types of loosely-typed inputs */
+#define NATSL_DT_BF16 0
+#define NATSL_DT_F32 1
+#define NATSL_DT_F16 2
+#define NATSL_DT_I32 3
+
+/* linear-branch update rule */
+#define NATSL_RULE_GDN 0   /* gated delta rule */
+#define NATSL_RULE_MAMBA 1 /* Mamba2 / SSD    */
+
+/* flags */
+#define NATSL_FLAG_DECAY_SKIPPED 1      /* decay_for_non_gdn_blocks / decay_for_non_mamba_blocks      */
+#define NATSL_FLAG_ATTN_OWN_CHUNK 2     /* softmax branch also covers the query's own block ('all', 'attn') */
+#define NATSL_FLAG_NO_TRAILING_QUIRK 4  /* carry the decay also over skipped blocks after the last selected one */
+
+#define NATSL_ATTN_BT 128 /* query rows per attention tile; the attn_n_iters table is built for it */
+
+/* status codes */
+#define NATSL_OK 0
+#define NATSL_ERR_BAD_SHAPE (-1)
+#define NATSL_ERR_UNSUPPORTED (-2)
+#define NATSL_ERR_NULL (-3)
+#define NATSL_ERR_CUDA (-4)
+#define NATSL_ERR_TOO_LARGE (-5)
+
+const char* natsl_last_error(void);
+int natsl_abi_version(void);
+
+/* Selection tables from the op types [B,TN,HN,2] (column 0 softmax, column 1 linear).
+ * Replaces: round / index sort / block counts, src/nats/ops/mixed_ops/mixed_attn_gdn.py:88-100;
+ * prepare_nats_block_indices src/nats/ops/nats_util.py:6-32; prepare_nats_chunk_offsets :35-64;
+ * compute_attn_n_iters_per_block :67-121; compute_starting_idx_for_chunks :124-162.
+ * Outputs (int32): types_i, indices [B,TN,HN,2]; n_blocks [B,HN,2]; n_chunks_lin [B*HN];
+ * offsets [B*HN+1]; chunk_indices [B*HN*cdiv(T,64), 2] (first offsets[B*HN] rows valid, may be
+ * NULL); starting_h_idx [B,cdiv(T,64),HN]; attn_n_iters [B,cdiv(T,attn_bt),HN]. */
+int natsl_build_tables(const void* types, int types_dtype, int B, int TN, int HN, int T, int nbs, int attn_bt,
+                       int32_t* types_i, int32_t* indices, int32_t* n_blocks, int32_t* n_chunks_lin, int32_t* offsets,
+                       int32_t* chunk_indices, int32_t* starting_h_idx, int32_t* attn_n_iters, void* stream);
+
+/* Chunk-masked softmax attention forward.  q [B,T,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16;
+ * o [B,T,HQ,DV] bf16; lse [B,T,HQ] fp32 (base 2).  attn_n_iters must come from
+ * natsl_build_tables with attn_bt = NATSL_ATTN_BT.
+ * Replaces: parallel_attn_nats_fwd src/nats/ops/attns/attns.py:1421-1531 (kernel :62-353). */
+int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i, const int32_t* indices,
+                   const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int DK,
+                   int DV, int nbs, float scale, int flags, void* stream);
+
+/* Debug/parity: dense 0/1 mask [B,HQ,T,T] (uint8) from the same tile walk as natsl_attn_fwd.
+ * Counterpart: store_msk=True of the reference kernel, src/nats/ops/attns/attns.py:214-217,
+ * 321-323, 1495-1498. */
+int natsl_attn_dense_mask(const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters, uint8_t* mask,
+                          int B, int T, int HQ, int HN, int nbs, int flags, void* stream);
+
+/* Chunk-local cumsum of the log decay, g and gcs [B,T,H] fp32.
+ * Replaces: chunk_local_cumsum calls at src/nats/ops/mamba/chunk.py:49-51,
+ * src/nats/ops/gated_delta_rule/chunk.py:52-54. */
+int natsl_chunk_local_cumsum(const float* g, float* gcs, int B, int T, int H, void* stream);
+
+/* Gated-delta-rule chunk preparation: k_rstd, gcs [B,T,H] fp32; w [B,T,H,K], u [B,T,H,V] bf16.
+ * Replaces: l2norm_fwd(k) src/nats/ops/mixed_ops/mixed_attn_gdn.py:119-121; chunk_local_cumsum;
+ * chunk_scaled_dot_kkt_nats_fwd src/nats/ops/common/chunk_scaled_dot_kkt.py:272-374;
+ * solve_tril_nats src/nats/ops/utils/solve_tril.py:484-569;
+ * recompute_w_u_nats_fwd src/nats/ops/gated_delta_rule/wy_fast.py:386-457. */
+int natsl_gdn_chunk_prep(const void* k, const void* v, const float* g, const void* beta, int beta_dtype, void* w,
+                         void* u, float* gcs, float* k_rstd, int B, int T, int H, int K, int V, int use_l2norm,
+                         void* stream);
+
+/* State recurrence.  h [B,cdiv(T,64),H,K,V] bf16 = the state each chunk reads; carry
+ * [B,cdiv(T,64),H] fp32 = decay of skipped blocks before each chunk; ht [B,H,K,V] fp32 or NULL;
+ * h0 [B,H,K,V] fp32 or NULL.  For NATSL_RULE_MAMBA pass w = NULL, u = v, k_rstd = NULL.
+ * Replaces: chunk_gated_delta_rule_nats_fwd_h src/nats/ops/common/chunk_delta_h.py:638-732
+ * (kernel :40-324), chunk_mamaba_nats_fwd_h src/nats/ops/mamba/chunk_h.py:220-290 (kernel :35-218)
+ * and chunk_cumsum_non_gated_chunks src/nats/ops/utils/cumsum.py:136-180. */
+int natsl_linear_fwd_h(int rule, const void* k, const void* w, const void* u, const float* gcs, const float* k_rstd,
+                       const int32_t* types_i, const int32_t* indices, const int32_t* n_blocks, const float* h0,
+                       void* h, float* carry, float* ht, int B, int T, int H, int HN, int K, int V, int nbs, int flags,
+                       void* stream);
+
+/* Output of every chunk, o [B,T,H,V] bf16.
+ * Replaces: l2norm_fwd(q) src/nats/ops/mixed_ops/mixed_attn_gdn.py:119-120; chunk_fwd_nats_o
+ * src/nats/ops/common/chunk_o.py:1176-1259 (kernel :35-215); chunk_mamba_fwd_nats_o
+ * src/nats/ops/mamba/chunk_o.py:200-277 (kernel :34-198). */
+int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, const void* u, const float* gcs,
+                       const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
+                       int V, float scale, int use_l2norm, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NATSL_B200_H */

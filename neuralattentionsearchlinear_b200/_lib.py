@@ -1,0 +1,67 @@
+"""ctypes binding of ``lib/libnatsl_b200.so`` (the C ABI declared in ``include/natsl_b200.h``).
+
+There is no fallback: if the library has not been built, importing the ops raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "lib", "libnatsl_b200.so")
+
+DT_BF16, DT_F32, DT_F16, DT_I32 = 0, 1, 2, 3
+RULE_GDN, RULE_MAMBA = 0, 1
+FLAG_DECAY_SKIPPED, FLAG_ATTN_OWN_CHUNK, FLAG_NO_TRAILING_QUIRK = 1, 2, 4
+ATTN_BT = 128
+
+_p, _i, _f = C.c_void_p, C.c_int, C.c_float
+
+# name -> argtypes; every function returns int except natsl_last_error
+PROTOTYPES = {
+    "natsl_abi_version": [],
+    "natsl_build_tables": [_p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
+    "natsl_attn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_attn_dense_mask": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_chunk_local_cumsum": [_p, _p, _i, _i, _i, _p],
+    "natsl_gdn_chunk_prep": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_linear_fwd_h": [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_linear_fwd_o": [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+}
+
+_lib = None
+
+
+class NatslError(RuntimeError):
+    pass
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NatslError(
+            f"{LIB_PATH} is missing: build it with `python -m neuralattentionsearchlinear_b200.build` "
+            "(needs nvcc). There is no CPU or PyTorch fallback for these ops.")
+    lib = C.CDLL(LIB_PATH)
+    lib.natsl_last_error.restype = C.c_char_p
+    lib.natsl_last_error.argtypes = []
+    for name, args in PROTOTYPES.items():
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def call(name: str, *args) -> None:
+    lib = load()
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise NatslError(f"{name} failed with status {status}: {lib.natsl_last_error().decode()}")
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a torch tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()

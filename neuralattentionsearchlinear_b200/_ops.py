@@ -1,0 +1,87 @@
+"""Thin launch wrappers: allocate outputs with torch, pass raw pointers to the C ABI."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .nats_util import SelectionTables, cdiv, current_stream_ptr
+
+BF16 = torch.bfloat16
+
+
+def _need(cond: bool, msg: str, exc=ValueError):
+    if not cond:
+        raise exc(msg)
+
+
+def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
+    """q [B,T,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16 -> (o [B,T,HQ,DV] bf16, lse [B,T,HQ] fp32 base-2)."""
+    _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "softmax branch needs bf16 q/k/v", TypeError)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, T, HQ, DK = q.shape
+    HKV, DV = k.shape[2], v.shape[3]
+    HN = tables.types_i.shape[2]
+    o = torch.empty(B, T, HQ, DV, dtype=BF16, device=q.device)
+    lse = torch.empty(B, T, HQ, dtype=torch.float32, device=q.device)
+    flags = _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0
+    _lib.call("natsl_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
+              tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(),
+              B, T, HQ, HKV, HN, DK, DV, tables.nats_block_size, float(scale), flags, current_stream_ptr(q.device))
+    return o, lse
+
+
+def attn_dense_mask(tables: SelectionTables, HQ: int, own_chunk: bool) -> torch.Tensor:
+    """Debug: the dense boolean mask [B,HQ,T,T] the attention kernel realises."""
+    B, TN, HN, _ = tables.types_i.shape
+    T = tables.T
+    mask = torch.empty(B, HQ, T, T, dtype=torch.uint8, device=tables.types_i.device)
+    flags = _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0
+    _lib.call("natsl_attn_dense_mask", tables.types_i.data_ptr(), tables.indices.data_ptr(),
+              tables.attn_n_iters.data_ptr(), mask.data_ptr(), B, T, HQ, HN, tables.nats_block_size, flags,
+              current_stream_ptr(mask.device))
+    return mask.bool()
+
+
+def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool,
+               use_l2norm: bool, output_final_state: bool, trailing_quirk: bool = True,
+               return_intermediates: bool = False):
+    """Linear branch forward (prep -> state recurrence -> output).  Returns (o, ht, inter)."""
+    _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "linear branch needs bf16 q/k/v", TypeError)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, T, H, K = q.shape
+    V = v.shape[3]
+    dev = q.device
+    HN = tables.types_i.shape[2]
+    NT = cdiv(T, 64)
+    nbs = tables.nats_block_size
+    st = current_stream_ptr(dev)
+    g = g.float().contiguous()
+    gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    if rule == _lib.RULE_GDN:
+        beta = beta.contiguous()
+        _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
+        w = torch.empty(B, T, H, K, dtype=BF16, device=dev)
+        u = torch.empty(B, T, H, V, dtype=BF16, device=dev)
+        krstd = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        _lib.call("natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                  _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
+                  krstd.data_ptr(), B, T, H, K, V, int(use_l2norm), st)
+    else:
+        w, u, krstd = None, v, None
+        _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
+    h = torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
+    carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)
+    ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    if h0 is not None:
+        h0 = h0.float().contiguous()
+        _need(tuple(h0.shape) == (B, H, K, V), f"initial state must be [B,H,K,V], got {tuple(h0.shape)}")
+    flags = (_lib.FLAG_DECAY_SKIPPED if decay else 0) | (0 if trailing_quirk else _lib.FLAG_NO_TRAILING_QUIRK)
+    _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krstd),
+              tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
+              h.data_ptr(), carry.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, flags, st)
+    o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
+    _lib.call("natsl_linear_fwd_o", rule, q.data_ptr(), k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(),
+              _lib.ptr(krstd), h.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V, float(scale),
+              int(use_l2norm and rule == _lib.RULE_GDN), st)
+    inter = dict(w=w, u=u, gcs=gcs, k_rstd=krstd, h=h, carry=carry) if return_intermediates else None
+    return o, ht, inter

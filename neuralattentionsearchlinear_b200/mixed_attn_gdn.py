@@ -1,0 +1,174 @@
+"""``nats_mixed_attn_gdn``: softmax branch + gated-delta-rule branch of the NAtSL-GDN layer.
+
+Same function names, argument order, defaults and return values as the reference's
+``src/nats/ops/mixed_ops/mixed_attn_gdn.py:286-325`` (training / prefill op) and ``:328-440``
+(chunk-inference op); the work is done by the C-ABI CUDA kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, _ops
+from .nats_util import CHUNK_SIZE, OFFSET_ATTN, OFFSET_LINEAR, build_selection_tables  # noqa: F401
+
+# which branches also compute the query's own (possibly incomplete) block — mixed_attn_gdn.py:29-42
+all_incomplete_ops = {
+    'all': dict(attn=True, gated_delta_net=True),
+    'attn': dict(attn=True, gated_delta_net=False),
+    'gated_delta_net': dict(attn=False, gated_delta_net=True),
+}
+
+
+def _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn, table):
+    if ops_for_incomplete_chunks not in table:
+        raise KeyError(ops_for_incomplete_chunks)
+    assert nats_block_size >= CHUNK_SIZE                                  # mixed_attn_gdn.py:90
+    if nats_block_size % CHUNK_SIZE:
+        raise NotImplementedError("nats_block_size must be a multiple of 64")
+    if attn_sw_size is not None:
+        raise NotImplementedError("sliding-window softmax (attn_sw_size) is not built")
+    if cu_seqlens is not None:
+        raise NotImplementedError("variable-length batches (cu_seqlens) are not built")
+    if use_g_for_attn:
+        raise NotImplementedError("use_g_for_attn is not built (the layers always pass False)")
+
+
+class NAtSMixedAttentionGDN(torch.autograd.Function):
+    """Forward of mixed_attn_gdn.py:47-191.  Backward (mixed_attn_gdn.py:196-283) is not built yet
+    and raises."""
+
+    @staticmethod
+    def forward(ctx, q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_gated_delta, g, beta,
+                nats_block_types, n_nats_blocks, scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats,
+                nats_block_size, attn_sw_size=None, ops_for_incomplete_chunks='gated_delta_net',
+                output_final_state_gated_delta=False, compute_dnats_for_invalid_blocks_attn=False,
+                compute_dnats_for_invalid_blocks_linear_att=True, decay_for_non_gdn_blocks=False,
+                incomplete_block_start_with_ht=True, use_g_for_attn=True, lattn_use_qk_l2norm_in_kernel=True):
+        _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
+                      all_incomplete_ops)
+        strategy = all_incomplete_ops[ops_for_incomplete_chunks]
+        if not strategy['gated_delta_net']:
+            raise NotImplementedError("ops_for_incomplete_chunks='attn' (no own-block linear term) is not built")
+        if not incomplete_block_start_with_ht:
+            raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
+        T = q_lattn.shape[1]
+        tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        o_gdn, ht, _ = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
+                                       initial_state_gated_delta, decay_for_non_gdn_blocks,
+                                       lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta)
+        ctx.mark_non_differentiable(o_gdn, o_attn)
+        return o_gdn, o_attn, ht
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("backward of nats_mixed_attn_gdn is not built yet")
+
+
+def nats_mixed_attn_gdn(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        initial_state_gated_delta: torch.Tensor,
+        g: torch.Tensor,
+        beta: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        n_nats_blocks: torch.Tensor,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        attn_sw_size: int | None = None,
+        ops_for_incomplete_chunks: str = 'gated_delta_net',
+        output_final_state_gated_delta: bool = False,
+        compute_dnats_for_invalid_blocks_attn: bool = False,
+        compute_dnats_for_invalid_blocks_linear_att: bool = True,
+        decay_for_non_gdn_blocks: bool = False,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+        lattn_use_qk_l2norm_in_kernel: bool = True,
+):
+    """-> (o_gated_delta [B,T,H,V], o_attn [B,T,HQ,V_attn], final_state [B,H,K,V] fp32 or None).
+
+    ``n_nats_blocks`` is accepted for signature parity; the counts are recomputed on the device
+    from ``nats_block_types``."""
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = k_lattn.shape[-1] ** -0.5
+    with torch.no_grad():
+        return NAtSMixedAttentionGDN.apply(
+            q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_gated_delta, g, beta,
+            nats_block_types, n_nats_blocks, scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats,
+            nats_block_size, attn_sw_size, ops_for_incomplete_chunks, output_final_state_gated_delta,
+            compute_dnats_for_invalid_blocks_attn, compute_dnats_for_invalid_blocks_linear_att,
+            decay_for_non_gdn_blocks, incomplete_block_start_with_ht, use_g_for_attn,
+            lattn_use_qk_l2norm_in_kernel)
+
+
+def _chunk_start_state(inter, ht, gcs, tables, op_type_last_chunk, T, nbs, decay):
+    """State at the start of the block that follows / contains the last token, as the reference
+    extracts it for decoding (src/nats/ops/gated_delta_rule/chunk_fwd.py:178-206)."""
+    cpb = nbs // CHUNK_SIZE
+    TN = tables.types_i.shape[1]
+    c0 = (TN - 1) * cpb                                   # first compute chunk of the last block
+    h_last = inter['h'][:, c0].float()                    # [B,H,K,V]
+    carry_last = inter['carry'][:, c0]                    # [B,H]
+    start = h_last * carry_last.exp()[..., None, None]
+    if T % nbs == 0:
+        assert op_type_last_chunk is not None
+        H = h_last.shape[1]
+        HN = op_type_last_chunk.shape[1]
+        was_linear = (op_type_last_chunk[..., OFFSET_LINEAR] > 0).repeat_interleave(H // HN, dim=1)
+        if decay:
+            blk_g = gcs[:, c0 * CHUNK_SIZE:].view(gcs.shape[0], cpb, CHUNK_SIZE, H)[:, :, -1].sum(1)
+            start = start * blk_g.exp()[..., None, None]
+        start = torch.where(was_linear[..., None, None], ht, start)
+    return start
+
+
+def nats_mixed_attn_gdn_chunk_inference(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        initial_state_gated_delta_chunk_start: torch.Tensor,
+        g: torch.Tensor,
+        beta: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        op_type_last_chunk: torch.Tensor | None,
+        n_nats_blocks: torch.Tensor,
+        n_tokens_in_current_block: int = 0,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        attn_sw_size: int | None = None,
+        ops_for_incomplete_chunks: str = 'all',
+        output_final_state_gated_delta: bool = True,
+        decay_for_non_gdn_blocks: bool = True,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+        lattn_use_qk_l2norm_in_kernel: bool = True,
+):
+    """Prefill under eval (mixed_attn_gdn.py:328-440): same kernels as ``nats_mixed_attn_gdn`` plus
+    the block-start state for the decoder.
+    -> (o_gated_delta, o_attn, final_state, chunk_start_state)."""
+    _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
+                  all_incomplete_ops)
+    if n_tokens_in_current_block:
+        raise NotImplementedError("continued prefill into a partially filled block is not built")
+    strategy = all_incomplete_ops[ops_for_incomplete_chunks]
+    if not strategy['gated_delta_net'] or not incomplete_block_start_with_ht:
+        raise NotImplementedError("only own-block linear attention starting from the carried state is built")
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = k_lattn.shape[-1] ** -0.5
+    T = q_lattn.shape[1]
+    with torch.no_grad():
+        tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        o_gdn, ht, inter = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
+                                           initial_state_gated_delta_chunk_start, decay_for_non_gdn_blocks,
+                                           lattn_use_qk_l2norm_in_kernel, True, return_intermediates=True)
+        if not output_final_state_gated_delta:
+            return o_gdn, o_attn, None, None
+        start = _chunk_start_state(inter, ht, inter['gcs'], tables, op_type_last_chunk, T, nats_block_size,
+                                   decay_for_non_gdn_blocks)
+    return o_gdn, o_attn, ht, start

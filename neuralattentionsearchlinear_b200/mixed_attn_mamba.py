@@ -1,0 +1,101 @@
+"""``nats_mixed_attn_mamba``: softmax branch + Mamba2/SSD branch of the NAtSL-Mamba2 layer.
+
+Mirrors ``src/nats/ops/mixed_ops/mixed_attn_mamba.py:295-332`` (op) and ``:363-457``
+(chunk inference).  q = C, k = B (already L2-normalised by the layer), v = x * dt, g = A * dt.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, _ops
+from .mixed_attn_gdn import _check_common, _chunk_start_state
+from .nats_util import build_selection_tables
+
+# mixed_attn_mamba.py:33-46
+all_incomplete_ops = {
+    'all': dict(attn=True, mamba=True),
+    'attn': dict(attn=True, mamba=False),
+    'mamba': dict(attn=False, mamba=True),
+}
+
+
+def nats_mixed_attn_mamba(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        initial_state_mamba: torch.Tensor,
+        g: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        n_nats_blocks: torch.Tensor,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        attn_sw_size: int | None = None,
+        ops_for_incomplete_chunks: str = 'all',
+        output_final_state_mamba: bool = False,
+        compute_dnats_for_invalid_blocks_attn: bool = False,
+        compute_dnats_for_invalid_blocks_linear_att: bool = True,
+        decay_for_non_mamba_blocks: bool = False,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+):
+    """-> (o_mamba [B,T,H,V], o_attn [B,T,HQ,V_attn], final_state [B,H,K,V] fp32 or None).  Forward only."""
+    _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
+                  all_incomplete_ops)
+    strategy = all_incomplete_ops[ops_for_incomplete_chunks]
+    if not strategy['mamba'] or not incomplete_block_start_with_ht:
+        raise NotImplementedError("only own-block linear attention starting from the carried state is built")
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = 1                                                     # mixed_attn_mamba.py:318-319
+    T = q_lattn.shape[1]
+    with torch.no_grad():
+        tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
+                                     initial_state_mamba, decay_for_non_mamba_blocks, False,
+                                     output_final_state_mamba)
+    return o_m, o_attn, ht
+
+
+def nats_mixed_attn_mamba_chunk_inference(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        initial_state_mamba_start: torch.Tensor,
+        g: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        op_type_last_chunk: torch.Tensor | None,
+        n_nats_blocks: torch.Tensor,
+        n_tokens_in_current_block: int = 0,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        ops_for_incomplete_chunks: str = 'all',
+        output_final_state_mamba: bool = True,
+        decay_for_non_mamba_blocks: bool = True,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+):
+    """-> (o_mamba, o_attn, final_state, chunk_start_state)  (mixed_attn_mamba.py:363-457)."""
+    _check_common(ops_for_incomplete_chunks, nats_block_size, None, cu_seqlens, use_g_for_attn, all_incomplete_ops)
+    if n_tokens_in_current_block:
+        raise NotImplementedError("continued prefill into a partially filled block is not built")
+    strategy = all_incomplete_ops[ops_for_incomplete_chunks]
+    if not strategy['mamba'] or not incomplete_block_start_with_ht:
+        raise NotImplementedError("only own-block linear attention starting from the carried state is built")
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = k_lattn.shape[-1] ** -0.5                             # mixed_attn_mamba.py:389-390
+    T = q_lattn.shape[1]
+    with torch.no_grad():
+        tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        o_m, ht, inter = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
+                                         initial_state_mamba_start, decay_for_non_mamba_blocks, False, True,
+                                         return_intermediates=True)
+        if not output_final_state_mamba:
+            return o_m, o_attn, None, None
+        start = _chunk_start_state(inter, ht, inter['gcs'], tables, op_type_last_chunk, T, nats_block_size,
+                                   decay_for_non_mamba_blocks)
+    return o_m, o_attn, ht, start

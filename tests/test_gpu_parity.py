@@ -1,0 +1,174 @@
+"""GPU parity tests (-m gpu): the CUDA path, called through the C ABI, against the CPU oracle on
+the same seeded inputs.  Integer tables and masks bit-exact; bf16 outputs within
+rtol = atol = 1e-2 of the oracle evaluated in fp32 on the same bf16-rounded inputs."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attn as oattn
+from oracle import gdn as ogdn
+from oracle import tables as otab
+from tests.helpers import assert_close, synth_gdn_inputs, synth_mamba_inputs
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def nat():
+    import neuralattentionsearchlinear_b200 as n
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return n
+
+
+def _tables_equal(tb, ref, B, HN):
+    assert torch.equal(tb.types_i.cpu().long(), ref["types_i"])
+    assert torch.equal(tb.indices.cpu().long(), ref["indices"])
+    assert torch.equal(tb.n_blocks.cpu().long(), ref["n_blocks"])
+    assert torch.equal(tb.offsets.cpu().long(), ref["offsets"])
+    assert torch.equal(tb.starting_h_idx.cpu().long(), ref["starting_h_idx"])
+    assert torch.equal(tb.attn_n_iters.cpu().long(), ref["attn_n_iters"])
+    assert torch.equal(tb.compact_chunk_indices().cpu().long(), ref["chunk_indices"])
+
+
+@pytest.mark.parametrize("B,T,HN,nbs,p,dtype", [
+    (1, 512, 2, 64, 0.4, torch.float32), (2, 512, 4, 64, 0.5, torch.bfloat16), (3, 1000, 3, 64, 0.25, torch.float32),
+    (2, 1024, 2, 128, 0.3, torch.float16), (8, 4096, 16, 64, 0.25, torch.bfloat16), (1, 65536, 32, 256, 0.1, torch.float32),
+    (2, 130, 2, 64, 0.5, torch.float32), (1, 64, 1, 64, 0.5, torch.float32), (1, 40000, 1, 64, 0.9, torch.float32)])
+def test_tables_bit_exact(nat, B, T, HN, nbs, p, dtype):
+    TN = -(-T // nbs)
+    types = otab.synth_types(B, TN, HN, p, seed=B + T + HN, dtype=dtype)
+    ref = otab.build_tables(types, T, nbs)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs, with_chunk_indices=True)
+    _tables_equal(tb, ref, B, HN)
+
+
+def test_tables_against_reference_generated_golden(nat, golden_dir):
+    z = np.load(os.path.join(golden_dir, "tables_ref.npz"))
+    for n in sorted({k.split("_")[0] for k in z.files}):
+        B, T, HN, nbs = z[f"{n}_meta"].tolist()
+        tb = nat.build_selection_tables(torch.from_numpy(z[f"{n}_types"]).cuda(), T, nbs, with_chunk_indices=True)
+        for key, got in [("indices", tb.indices), ("n_blocks", tb.n_blocks), ("offsets", tb.offsets),
+                         ("starting_h_idx", tb.starting_h_idx), ("attn_n_iters", tb.attn_n_iters),
+                         ("chunk_indices", tb.compact_chunk_indices())]:
+            assert np.array_equal(got.cpu().numpy().astype(np.int64), z[f"{n}_{key}"]), (n, key)
+
+
+def test_tables_all_or_nothing(nat):
+    for fill in (0.0, 1.0):
+        types = torch.full((2, 8, 2, 2), fill)
+        ref = otab.build_tables(types, 512, 64)
+        tb = nat.build_selection_tables(types.cuda(), 512, 64, with_chunk_indices=True)
+        _tables_equal(tb, ref, 2, 2)
+
+
+@pytest.mark.parametrize("B,T,HQ,HN,nbs,own", [(2, 512, 4, 4, 64, True), (1, 700, 4, 2, 64, True), (2, 1024, 2, 2, 128, True),
+                                                (1, 1500, 2, 1, 256, True), (2, 512, 4, 4, 64, False), (1, 1024, 2, 2, 128, False),
+                                                (1, 100, 2, 2, 64, True)])
+def test_dense_mask_bit_exact(nat, B, T, HQ, HN, nbs, own):
+    from neuralattentionsearchlinear_b200 import _ops
+    TN = -(-T // nbs)
+    types = otab.synth_types(B, TN, HN, 0.4, seed=T + nbs)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    got = _ops.attn_dense_mask(tb, HQ, own).cpu()
+    ref = oattn.attn_mask(types[..., 0], T, nbs, HQ, own_chunk=own)
+    assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("B,T,HQ,HKV,HN,DK,DV,nbs,own", [
+    (2, 512, 4, 4, 4, 64, 64, 64, True), (1, 700, 4, 2, 2, 128, 128, 64, True), (2, 1024, 2, 2, 2, 64, 128, 128, True),
+    (1, 1100, 2, 2, 1, 128, 64, 256, True), (2, 512, 4, 4, 4, 64, 64, 64, False), (1, 2048, 2, 2, 2, 128, 128, 64, True)])
+def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own):
+    from neuralattentionsearchlinear_b200 import _ops
+    gen = torch.Generator().manual_seed(T + DK)
+    q = torch.randn(B, T, HQ, DK, generator=gen).bfloat16()
+    k = torch.randn(B, T, HKV, DK, generator=gen).bfloat16()
+    v = torch.randn(B, T, HKV, DV, generator=gen).bfloat16()
+    types = otab.synth_types(B, -(-T // nbs), HN, 0.3, seed=T)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    o, lse = _ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), tb, DK ** -0.5, own)
+    mask = oattn.attn_mask(types[..., 0], T, nbs, HQ, own_chunk=own)
+    o_ref, lse_ref = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask, DK ** -0.5)
+    assert_close(o, o_ref, TOL, "o_attn")
+    assert_close(lse, lse_ref, TOL, "lse")
+
+
+GDN_CASES = [  # B, T, H, HN, K, V, nbs, decay, use_h0
+    (2, 512, 4, 4, 64, 64, 64, True, False),
+    (1, 700, 4, 2, 128, 128, 64, True, True),
+    (2, 384, 2, 2, 64, 128, 64, False, True),
+    (1, 1024, 2, 2, 128, 64, 128, True, True),
+    (1, 1100, 2, 1, 128, 256, 256, True, False),
+    (1, 64, 2, 2, 128, 128, 64, True, True),
+    (1, 50, 2, 2, 64, 64, 64, True, False),
+]
+
+
+@pytest.mark.parametrize("B,T,H,HN,K,V,nbs,decay,use_h0", GDN_CASES)
+def test_gdn_linear_branch(nat, B, T, H, HN, K, V, nbs, decay, use_h0):
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    q, k, v, g, beta, h0 = synth_gdn_inputs(B, T, H, K, V, seed=T + K, normalize_qk=False)
+    if not use_h0:
+        h0 = None
+    types = otab.synth_types(B, -(-T // nbs), HN, 0.35, seed=T + 1)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    o, ht, inter = _ops.linear_fwd(_lib.RULE_GDN, q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), tb, K ** -0.5,
+                                   None if h0 is None else h0.cuda(), decay, True, True, return_intermediates=True)
+    o_ref, s_ref, ir = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, beta.float(), types[..., 1], nbs=nbs,
+                                         h0=h0, decay=decay, return_intermediates=True)
+    assert_close(inter["gcs"], ir["gcs"], 1e-4, "gcs")
+    assert_close(inter["k_rstd"], ir["k_rstd"], 1e-3, "k_rstd")
+    assert_close(inter["carry"], ir["carry"], 1e-4, "carry")
+    assert_close(inter["u"], ir["u"], TOL, "u")
+    assert_close(inter["w"], ir["w"], TOL, "w")
+    assert_close(inter["h"], ir["h"], 2 * TOL, "h")
+    assert_close(o, o_ref, TOL, "o_gdn")
+    assert_close(ht, s_ref, 2 * TOL, "final_state")
+
+
+@pytest.mark.parametrize("B,T,H,HN,K,V,nbs,decay", [(1, 1024, 4, 4, 128, 64, 256, True), (2, 512, 2, 2, 64, 64, 64, True),
+                                                     (1, 900, 2, 1, 128, 128, 128, False)])
+def test_mamba_linear_branch(nat, B, T, H, HN, K, V, nbs, decay):
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    q, k, v, g, h0 = synth_mamba_inputs(B, T, H, K, V, seed=T)
+    types = otab.synth_types(B, -(-T // nbs), HN, 0.2, seed=T + 1)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    o, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q.cuda(), k.cuda(), v.cuda(), g.cuda(), None, tb, 1.0, h0.cuda(),
+                               decay, False, True)
+    o_ref, s_ref = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, None, types[..., 1], nbs=nbs, scale=1.0,
+                                     h0=h0, decay=decay, use_l2norm=False, rule="mamba")
+    assert_close(o, o_ref, TOL, "o_mamba")
+    assert_close(ht, s_ref, 2 * TOL, "final_state")
+
+
+def test_op_level_gdn_matches_recurrent_oracle(nat):
+    """The public op (both branches) on the CPU-sized configuration against the token recurrence."""
+    B, T, H, K, V = 2, 512, 4, 64, 64
+    q, k, v, g, beta, _ = synth_gdn_inputs(B, T, H, K, V, seed=0)
+    types = otab.synth_types(B, 8, H, 0.5, seed=0)
+    cu = lambda x: x.cuda()
+    o_l, o_a, ht = nat.nats_mixed_attn_gdn(cu(q), cu(k), cu(v), cu(q), cu(k), cu(v), None, cu(g), cu(beta), cu(types),
+                                           None, nats_block_size=64, ops_for_incomplete_chunks='all',
+                                           output_final_state_gated_delta=True, decay_for_non_gdn_blocks=True)
+    o_ref, s_ref = ogdn.linear_recurrent(q.float(), k.float(), v.float(), g, beta.float(), types[..., 1], nbs=64)
+    mask = oattn.attn_mask(types[..., 0], T, 64, H)
+    oa_ref, _ = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask)
+    assert_close(o_l, o_ref, TOL, "o_gdn")
+    assert_close(o_a, oa_ref, TOL, "o_attn")
+    assert_close(ht, s_ref, 2 * TOL, "final_state")
+
+
+def test_error_paths(nat):
+    from neuralattentionsearchlinear_b200 import _lib
+    types = otab.synth_types(1, 4, 2, 0.5, seed=0).cuda()
+    with pytest.raises(_lib.NatslError):
+        _lib.call("natsl_build_tables", types.data_ptr(), 1, 1, 4, 2, 256, 96, 128, None, None, None, None, None, None,
+                  None, None, None)
+    q = torch.zeros(1, 256, 2, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.NatslError):
+        nat.nats_mixed_attn_gdn(q, q, q, q, q, q, None, torch.zeros(1, 256, 2, device="cuda"),
+                                torch.zeros(1, 256, 2, device="cuda"), types, None)
+    with pytest.raises(NotImplementedError):
+        nat.nats_mixed_attn_gdn(q, q, q, q, q, q, None, None, None, types, None, attn_sw_size=16)
