@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the NAtSL-GDN hybrid attention layer forward (prefill) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one call of ``nats_mixed_attn_gdn`` (selection tables, chunk-masked softmax branch,
+gated-delta-rule branch) on one batch of seeded synthetic tensors of the single-GPU layer
+configuration: B=8, T=4096, H=HQ=16, d_k=d_v=128, block 64, bf16 in / fp32 accumulate, about
+25 % of (block, head) pairs softmax-selected, last block forced, decay over skipped blocks on.
+With N GPUs every rank runs its own batch (independent (batch, head) units, no collective in the
+data path: weak scaling); the timed region is bracketed by a barrier and a device synchronise and
+the time is the maximum over ranks.  Prints ONE JSON line on rank 0.
+
+``--impl reference`` times the reference algorithm's CPU form (the PyTorch restatement under
+``oracle/``; the reference's own code is Triton-only and cannot run on host cores) on a bounded
+sample of the same workload, on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=8, T=4096, H=16, K=128, V=128, nbs=64, p_attn=0.25)
+WORKLOAD = "natsl_gdn_layer_fwd B=8 T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25"
+
+
+# ------------------------------------------------------------------------------- inputs
+def make_inputs(seed: int, B: int, H: int):
+    """Host tensors (fp32 generation on CPU, cast to bf16).  q, k L2-normalised per head."""
+    T, K, V, nbs = CFG["T"], CFG["K"], CFG["V"], CFG["nbs"]
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, H, K, generator=gen)
+    k = torch.randn(B, T, H, K, generator=gen)
+    v = torch.randn(B, T, H, V, generator=gen)
+    q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6)
+    k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    beta = torch.randn(B, T, H, generator=gen).sigmoid()
+    g = -torch.nn.functional.softplus(torch.randn(B, T, H, generator=gen))
+    # selection: logits ~ N(0,1), attention logit shifted so that P(softmax) = p_attn; hard argmax; last block forced
+    TN = T // nbs
+    logits = torch.randn(B, TN, H, 2, generator=gen)
+    shift = (2.0 ** 0.5) * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(CFG["p_attn"])).item()
+    logits[..., 0] += shift
+    types = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
+    types[:, -1] = 1
+    return dict(q=q.bfloat16(), k=k.bfloat16(), v=v.bfloat16(), g=g, beta=beta.bfloat16(), types=types.bfloat16())
+
+
+def attention_tile_flops(types: torch.Tensor, H: int, DK: int, DV: int, C: int = 64) -> float:
+    """Algorithmic FLOPs of the softmax branch: 2*(DK+DV)*C^2 per visible (query chunk, key chunk)
+    pair = own chunk + every softmax-selected earlier chunk."""
+    sel = types[..., 0].float()                                   # [B,TN,HN]
+    B, TN, HN = sel.shape
+    later = torch.arange(TN - 1, -1, -1, dtype=torch.float32).view(1, TN, 1)   # chunks after c
+    pairs = (sel * later).sum() * (H // HN) + B * H * TN
+    return float(pairs) * 2.0 * (DK + DV) * C * C
+
+
+# ------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val == "Active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------- CPU arms
+def cpu_oracle_step(inp, b_slice: int, h_slice: int):
+    """Reference algorithm (chunk form + masked SDPA) on CPU for a [b_slice, :, h_slice] sample."""
+    from oracle import attn as oattn
+    from oracle import gdn as ogdn
+    sl = lambda x: x[:b_slice, :, :h_slice].float().contiguous()
+    q, k, v, g, beta = (sl(inp[n]) for n in ("q", "k", "v", "g", "beta"))
+    types = inp["types"][:b_slice, :, :h_slice].float()
+    T, nbs = CFG["T"], CFG["nbs"]
+    o_l, _ = ogdn.linear_chunk(q, k, v, g, beta, types[..., 1], nbs=nbs, decay=True)
+    mask = oattn.attn_mask(types[..., 0], T, nbs, h_slice)
+    o_a, _ = oattn.attn_sdpa(q, k, v, mask)
+    return o_l, o_a
+
+
+def time_cpu_baseline(inp, budget_s: float, reps: int = 1):
+    """Times the oracle on a bounded sample sized to roughly `budget_s` seconds per repetition."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    cpu_oracle_step(inp, 1, 1)
+    unit = time.perf_counter() - t0                       # one (batch, head) unit
+    H = CFG["H"]
+    hs = max(1, min(H, int(budget_s / max(unit, 1e-3))))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_oracle_step(inp, 1, hs)
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    tokens = CFG["T"] * hs / H                            # token-equivalents of the full-head layer
+    return tokens / dt, f"1 of 8 sequences x {hs} of {H} heads, T=4096 (linear in heads and batch)", dt
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    inp = make_inputs(0, 1, CFG["H"])
+    total = max(1, args.steps + args.warmup)
+    per_step = min(20.0, 150.0 / total)
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    cpu_oracle_step(inp, 1, 1)
+    unit = time.perf_counter() - t0
+    hs = max(1, min(CFG["H"], int(per_step / max(unit, 1e-3))))
+    for _ in range(args.warmup):
+        cpu_oracle_step(inp, 1, hs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_step(inp, 1, hs)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = CFG["T"] * hs / CFG["H"] / dt
+    sample = f"per step: 1 of 8 sequences x {hs} of {CFG['H']} heads, T=4096"
+    cores = torch.get_num_threads()
+    print(json.dumps({
+        "impl": "reference", "metric": "prefill_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+        "config": {"workload": WORKLOAD, "note": "reference algorithm restated in PyTorch on host cores "
+                   "(the reference's own implementation is Triton-only)"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------- GPU arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import neuralattentionsearchlinear_b200 as nat
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    _lib.load()                                           # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU fallback for the hot path")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    B, T, H, K, V, nbs = (CFG[n] for n in ("B", "T", "H", "K", "V", "nbs"))
+    host = make_inputs(1000 * rank, B, H)
+    pinned = {n: t.pin_memory() for n, t in host.items()}
+    d = {n: t.to(dev) for n, t in host.items()}
+    stream = torch.cuda.current_stream(dev)
+
+    def step(x):
+        return nat.nats_mixed_attn_gdn(x["q"], x["k"], x["v"], x["q"], x["k"], x["v"], None, x["g"], x["beta"],
+                                       x["types"], None, nats_block_size=nbs, ops_for_incomplete_chunks="all",
+                                       output_final_state_gated_delta=True, decay_for_non_gdn_blocks=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up: at least W steps and at least ~1.5 s of load, so that clocks settle and the clock
+    # sampler (started first) has samples under the same load as the timed region that follows directly
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    clocks = ClockSampler(vis.split(",")[local_rank].strip() if vis else local_rank)
+    if rank == 0:
+        clocks.start()
+    n_warm = max(3, args.warmup)
+    for _ in range(n_warm):
+        out = step(d)
+    torch.cuda.synchronize(dev)
+    t_w = time.perf_counter()
+    while time.perf_counter() - t_w < 1.5:
+        for _ in range(20):
+            out = step(d)
+        torch.cuda.synchronize(dev)
+    if rank == 0:
+        clocks.rows.clear()          # keep only samples taken under load
+    # ---- device-resident throughput
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        out = step(d)
+    e1.record(stream)
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    if rank == 0 and len(clocks.rows) < 3:
+        # the timed region was shorter than the sampling period: keep the same load up until a few samples exist
+        t_w = time.perf_counter()
+        while len(clocks.rows) < 3 and time.perf_counter() - t_w < 3.0:
+            for _ in range(20):
+                out = step(d)
+            torch.cuda.synchronize(dev)
+    clk = clocks.stop() if rank == 0 else None
+    barrier()
+    ms_step = ms_total / args.steps
+    value = world * B * T / (ms_step * 1e-3)
+
+    # ---- per-kernel durations (CUDA events between the stages of the same step, same stream)
+    names = ["tables", "attn_fwd", "gdn_prep", "scan_fwd_h", "out_fwd_o"]
+    acc = {n: 0.0 for n in names}
+    barrier()
+    for _ in range(args.steps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record(stream)
+        tb = nat.build_selection_tables(d["types"], T, nbs)
+        ev[1].record(stream)
+        _ops.attn_fwd(d["q"], d["k"], d["v"], tb, K ** -0.5, True)
+        ev[2].record(stream)
+        # the linear branch, stage by stage
+        gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        krs = torch.empty_like(gcs)
+        w = torch.empty(B, T, H, K, dtype=torch.bfloat16, device=dev)
+        u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
+        hbuf = torch.empty(B, T // 64, H, K, V, dtype=torch.bfloat16, device=dev)
+        carry = torch.empty(B, T // 64, H, dtype=torch.float32, device=dev)
+        ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
+        o = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
+        sp = stream.cuda_stream
+        _lib.call("natsl_gdn_chunk_prep", d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(), d["beta"].data_ptr(),
+                  _lib.DT_BF16, w.data_ptr(), u.data_ptr(), gcs.data_ptr(), krs.data_ptr(), B, T, H, K, V, 1, sp)
+        ev[3].record(stream)
+        _lib.call("natsl_linear_fwd_h", _lib.RULE_GDN, d["k"].data_ptr(), w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
+                  krs.data_ptr(), tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
+                  hbuf.data_ptr(), carry.data_ptr(), ht.data_ptr(), B, T, H, H, K, V, nbs, _lib.FLAG_DECAY_SKIPPED, sp)
+        ev[4].record(stream)
+        _lib.call("natsl_linear_fwd_o", _lib.RULE_GDN, d["q"].data_ptr(), d["k"].data_ptr(), w.data_ptr(), u.data_ptr(),
+                  gcs.data_ptr(), krs.data_ptr(), hbuf.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V,
+                  K ** -0.5, 1, sp)
+        ev[5].record(stream)
+        torch.cuda.synchronize(dev)
+        for i, n in enumerate(names):
+            acc[n] += ev[i].elapsed_time(ev[i + 1])
+    kernel_ms = {n: acc[n] / args.steps for n in names}
+
+    # ---- end to end: host (pinned) inputs -> device -> op -> host outputs, every step
+    h2d = sum(t.numel() * t.element_size() for t in pinned.values())
+    o_host = [torch.empty(B, T, H, V, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    ht_host = torch.empty(B, H, K, V, dtype=torch.float32).pin_memory()
+    d2h = sum(t.numel() * t.element_size() for t in o_host) + ht_host.numel() * 4
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        x = {n: t.to(dev, non_blocking=True) for n, t in pinned.items()}
+        og, oa, hts = step(x)
+        o_host[0].copy_(og, non_blocking=True)
+        o_host[1].copy_(oa, non_blocking=True)
+        ht_host.copy_(hts, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    e2e_value = world * B * T / (e2e_ms * 1e-3)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    # ---- roofline of the dominant kernel (softmax branch; tensor-bound)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peaks = json.load(open(peaks_path))
+        peak_tf, peak_src = float(peaks["bf16_tflops_sustained"]), "measured (sustained, kernel timed inside a step)"
+    else:
+        peak_tf, peak_src = 1400.0, "fallback (sustained)"
+    flops = attention_tile_flops(host["types"], H, K, V)
+    dom = max(kernel_ms, key=kernel_ms.get)
+    achieved = flops / (kernel_ms["attn_fwd"] * 1e-3) / 1e12
+    traffic = None
+    tr_path = os.path.join(ROOT, "profiles", "attn_fwd_traffic.json")
+    if os.path.exists(tr_path):
+        traffic = json.load(open(tr_path)).get("dram_bytes_per_launch_full_workload")
+    roofline = {"kernel": "attn_fwd_kernel<128,128>", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
+                "unit": "TFLOP/s", "frac": achieved / peak_tf, "traffic": traffic, "peak_source": peak_src,
+                "algorithmic_flops_per_launch": flops, "ms_per_launch": kernel_ms["attn_fwd"],
+                "slowest_stage": dom}
+    # ---- CPU baseline (oracle port) on a bounded sample
+    cpu_val, cpu_sample, _ = time_cpu_baseline({n: t for n, t in host.items()}, budget_s=15.0)
+    line = {
+        "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, generated on the host)",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)",
+                   "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"},
+        "clocks": clk, "gpu_launches": 6 * args.steps,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "kernel_ms": kernel_ms, "roofline": roofline,
+        "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": cpu_sample},
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

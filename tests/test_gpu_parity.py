@@ -172,3 +172,32 @@ def test_error_paths(nat):
                                 torch.zeros(1, 256, 2, device="cuda"), types, None)
     with pytest.raises(NotImplementedError):
         nat.nats_mixed_attn_gdn(q, q, q, q, q, q, None, None, None, types, None, attn_sw_size=16)
+
+
+def test_full_size_layer_config(nat):
+    """The benchmark configuration (B=8, T=4096, H=16, d=128, block 64, ~25 % softmax blocks) at full
+    size: two batch elements against the oracle, and batch-independence (a size-independent property:
+    (batch, head) units never interact)."""
+    import bench
+    B, T, H, K, V, nbs = (bench.CFG[n] for n in ("B", "T", "H", "K", "V", "nbs"))
+    host = bench.make_inputs(0, B, H)
+    d = {n: t.cuda() for n, t in host.items()}
+    run = lambda x: nat.nats_mixed_attn_gdn(x["q"], x["k"], x["v"], x["q"], x["k"], x["v"], None, x["g"], x["beta"],
+                                            x["types"], None, nats_block_size=nbs, ops_for_incomplete_chunks="all",
+                                            output_final_state_gated_delta=True, decay_for_non_gdn_blocks=True)
+    o_l, o_a, ht = run(d)
+    frac = host["types"][:, :-1, :, 0].float().mean().item()
+    assert 0.2 < frac < 0.3
+    for b in (0, B - 1):
+        s = {n: t[b:b + 1] for n, t in host.items()}
+        ty = s["types"].float()
+        o_ref, s_ref = ogdn.linear_chunk(s["q"].float(), s["k"].float(), s["v"].float(), s["g"], s["beta"].float(),
+                                         ty[..., 1], nbs=nbs)
+        assert_close(o_l[b:b + 1], o_ref, TOL, f"o_gdn[b={b}]")
+        assert_close(ht[b:b + 1], s_ref, 2 * TOL, f"final_state[b={b}]")
+        mask = oattn.attn_mask(ty[..., 0], T, nbs, H)
+        oa_ref, _ = oattn.attn_sdpa(s["q"].float(), s["k"].float(), s["v"].float(), mask)
+        assert_close(o_a[b:b + 1], oa_ref, TOL, f"o_attn[b={b}]")
+    sub = {n: t[3:5].contiguous() for n, t in d.items()}
+    o_l2, o_a2, ht2 = run(sub)
+    assert torch.equal(o_l2, o_l[3:5]) and torch.equal(o_a2, o_a[3:5]) and torch.equal(ht2, ht[3:5])
