@@ -32,7 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CFG = dict(B=8, T=4096, H=16, K=128, V=128, nbs=64, p_attn=0.25)
-WORKLOAD = "natsl_gdn_layer_fwd B=8 T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25"
+WORKLOAD = "natsl_gdn_layer_fwd B={B} T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25"
 
 
 # ------------------------------------------------------------------------------- inputs
@@ -164,7 +164,7 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": "prefill_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-        "config": {"workload": WORKLOAD, "note": "reference algorithm restated in PyTorch on host cores "
+        "config": {"workload": WORKLOAD.format(B=8), "note": "reference algorithm restated in PyTorch on host cores "
                    "(the reference's own implementation is Triton-only)"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -218,7 +218,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         out = step(d)
     torch.cuda.synchronize(dev)
     t_w = time.perf_counter()
-    while time.perf_counter() - t_w < 1.5:
+    while time.perf_counter() - t_w < args.min_warm_seconds:
         for _ in range(20):
             out = step(d)
         torch.cuda.synchronize(dev)
@@ -233,7 +233,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e1.record(stream)
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    if rank == 0 and len(clocks.rows) < 3:
+    if rank == 0 and len(clocks.rows) < 3 and args.min_warm_seconds > 0:
         # the timed region was shorter than the sampling period: keep the same load up until a few samples exist
         t_w = time.perf_counter()
         while len(clocks.rows) < 3 and time.perf_counter() - t_w < 3.0:
@@ -334,7 +334,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, generated on the host)",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)",
+        "config": {"workload": WORKLOAD.format(B=B), "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)",
                    "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"},
         "clocks": clk, "gpu_launches": 6 * args.steps,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -354,7 +354,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (default: the benchmark's 8; "
+                    "smaller values are for profiler captures only)")
+    ap.add_argument("--min-warm-seconds", type=float, default=1.5, help="minimum warm-up time under load")
     args = ap.parse_args()
+    CFG["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
