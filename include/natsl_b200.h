@@ -108,6 +108,19 @@ int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, co
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
                        int V, float scale, int use_l2norm, void* stream);
 
+/* Gated-delta-rule branch forward (prep -> recurrence -> output) that allocates nothing and asks
+ * the caller for no intermediate buffers: they live in a fixed NATSL_NOALLOC_SCRATCH_BYTES array
+ * inside the library, one per GPU, shared by all calls (overlapping calls on one GPU race; the
+ * first call on a device resolves the array's address and should be made outside stream capture).
+ * Shapes whose intermediates exceed the array are rejected with NATSL_ERR_TOO_LARGE.
+ * For hosts that may not allocate device memory (fixed memory plans, foreign-runtime callbacks).
+ * No counterpart in the reference: its Python ops allocate their intermediates through torch. */
+#define NATSL_NOALLOC_SCRATCH_BYTES (32u << 20)
+int natsl_gdn_fwd_noalloc(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                          int beta_dtype, const int32_t* types_i, const int32_t* indices, const int32_t* n_blocks,
+                          const float* h0, void* o, float* ht, int B, int T, int H, int HN, int K, int V, int nbs,
+                          float scale, int flags, int use_l2norm, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
