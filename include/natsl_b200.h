@@ -36,6 +36,7 @@ extern "C" {
 #define NATSL_FLAG_DECAY_SKIPPED 1      /* decay_for_non_gdn_blocks / decay_for_non_mamba_blocks      */
 #define NATSL_FLAG_ATTN_OWN_CHUNK 2     /* softmax branch also covers the query's own block ('all', 'attn') */
 #define NATSL_FLAG_NO_TRAILING_QUIRK 4  /* carry the decay also over skipped blocks after the last selected one */
+#define NATSL_FLAG_ATTN_MMA_SYNC 8      /* natsl_attn_fwd: use the mma.sync comparison kernel instead of tcgen05 */
 
 #define NATSL_ATTN_BT 128 /* query rows per attention tile; the attn_n_iters table is built for it */
 
@@ -49,6 +50,11 @@ extern "C" {
 
 const char* natsl_last_error(void);
 int natsl_abi_version(void);
+
+/* Synchronises the current device and returns (and clears) its status word: 0 = every kernel ran to
+ * completion; non-zero = a kernel gave up a bounded wait and its outputs are invalid.  The tensor-core
+ * kernels never spin forever; they record the failure here instead. */
+int natsl_device_status(void);
 
 /* Selection tables from the op types [B,TN,HN,2] (column 0 softmax, column 1 linear).
  * Replaces: round / index sort / block counts, src/nats/ops/mixed_ops/mixed_attn_gdn.py:88-100;

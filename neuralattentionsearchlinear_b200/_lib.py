@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libnatsl_b200.so")
 
 DT_BF16, DT_F32, DT_F16, DT_I32 = 0, 1, 2, 3
 RULE_GDN, RULE_MAMBA = 0, 1
-FLAG_DECAY_SKIPPED, FLAG_ATTN_OWN_CHUNK, FLAG_NO_TRAILING_QUIRK = 1, 2, 4
+FLAG_DECAY_SKIPPED, FLAG_ATTN_OWN_CHUNK, FLAG_NO_TRAILING_QUIRK, FLAG_ATTN_MMA_SYNC = 1, 2, 4, 8
 ATTN_BT = 128
 
 _p, _i, _f = C.c_void_p, C.c_int, C.c_float
@@ -20,6 +20,7 @@ _p, _i, _f = C.c_void_p, C.c_int, C.c_float
 # name -> argtypes; every function returns int except natsl_last_error
 PROTOTYPES = {
     "natsl_abi_version": [],
+    "natsl_device_status": [],
     "natsl_build_tables": [_p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "natsl_attn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_attn_dense_mask": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],

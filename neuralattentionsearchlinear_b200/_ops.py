@@ -14,7 +14,7 @@ def _need(cond: bool, msg: str, exc=ValueError):
         raise exc(msg)
 
 
-def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
+def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mma_sync: bool = False):
     """q [B,T,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16 -> (o [B,T,HQ,DV] bf16, lse [B,T,HQ] fp32 base-2)."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "softmax branch needs bf16 q/k/v", TypeError)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -23,7 +23,7 @@ def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
     HN = tables.types_i.shape[2]
     o = torch.empty(B, T, HQ, DV, dtype=BF16, device=q.device)
     lse = torch.empty(B, T, HQ, dtype=torch.float32, device=q.device)
-    flags = _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0
+    flags = (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_ATTN_MMA_SYNC if mma_sync else 0)
     _lib.call("natsl_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
               tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(),
               B, T, HQ, HKV, HN, DK, DV, tables.nats_block_size, float(scale), flags, current_stream_ptr(q.device))

@@ -13,47 +13,12 @@
 // The same tile walk and visibility predicate also drive a debug kernel that writes the dense
 // 0/1 mask, which is what the bit-exact mask check compares.
 #include "common.cuh"
+#include "attn_walk.cuh"
 #include "../../include/natsl_b200.h"
 
 namespace natsl {
 
 constexpr int ATT_THREADS = 256;
-constexpr int ATT_BM = 128;
-constexpr int ATT_BN = 64;
-
-struct TileWalk {
-    int n_past_tiles;   // unmasked tiles from selected past blocks
-    int n_tiles;        // total
-    int span_start;     // first key of the own span
-    int cpb;            // 64-key tiles per selection block
-};
-
-__device__ __forceinline__ TileWalk make_walk(int q0, int T, int nbs, int n_past_blocks) {
-    TileWalk w;
-    w.cpb = nbs / ATT_BN;
-    w.n_past_tiles = n_past_blocks * w.cpb;
-    w.span_start = (q0 / nbs) * nbs;
-    int span_end = min(q0 + ATT_BM, T);
-    w.n_tiles = w.n_past_tiles + (span_end - w.span_start + ATT_BN - 1) / ATT_BN;
-    return w;
-}
-
-// first key of tile j and whether the tile needs the per-element mask
-__device__ __forceinline__ int tile_start(const TileWalk& w, int j, const int* idx, long idx_stride, int nbs,
-                                          bool& masked) {
-    if (j < w.n_past_tiles) {
-        masked = false;
-        return idx[(long)(j / w.cpb) * idx_stride] * nbs + (j % w.cpb) * ATT_BN;
-    }
-    masked = true;
-    return w.span_start + (j - w.n_past_tiles) * ATT_BN;
-}
-
-__device__ __forceinline__ bool visible(int t, int s, int T, int blk_end, bool selb, bool own_chunk) {
-    if (s >= T) return false;
-    if (own_chunk) return s <= t && (selb || t < blk_end);
-    return selb && t >= blk_end;
-}
 
 template <int DK, int DV>
 struct AttSmem {
@@ -292,19 +257,11 @@ static int launch_attn(const void* q, const void* k, const void* v, const int* t
 
 }  // namespace natsl
 
-extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,
-                              const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B, int T,
-                              int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
-    using namespace natsl;
-    NATSL_REQUIRE(q && k && v && types_i && indices && attn_n_iters && o && lse, NATSL_ERR_NULL,
-                  "natsl_attn_fwd: null pointer");
-    NATSL_REQUIRE(B > 0 && T > 0 && HQ > 0 && HKV > 0 && HN > 0 && HQ % HKV == 0 && HQ % HN == 0, NATSL_ERR_BAD_SHAPE,
-                  "natsl_attn_fwd: bad shape B=%d T=%d HQ=%d HKV=%d HN=%d", B, T, HQ, HKV, HN);
-    NATSL_REQUIRE(HQ <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_attn_fwd: B and HQ must be <= 65535");
-    NATSL_REQUIRE(nbs >= 64 && nbs % 64 == 0, NATSL_ERR_UNSUPPORTED,
-                  "natsl_attn_fwd: nats_block_size must be a multiple of 64 (got %d)", nbs);
-    const int own = (flags & NATSL_FLAG_ATTN_OWN_CHUNK) ? 1 : 0;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+namespace natsl {
+// mma.sync implementation (kept as the comparison / debug path; selected with NATSL_FLAG_ATTN_MMA_SYNC)
+int attn_fwd_mma_sync(const void* q, const void* k, const void* v, const int32_t* types_i, const int32_t* indices,
+                      const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int DK,
+                      int DV, int nbs, float scale, int own, cudaStream_t st) {
 #define NATSL_ATT_ARGS q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, nbs, scale, own, st
     if (DK == 64 && DV == 64) return launch_attn<64, 64>(NATSL_ATT_ARGS);
     if (DK == 64 && DV == 128) return launch_attn<64, 128>(NATSL_ATT_ARGS);
@@ -314,6 +271,7 @@ extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const
     set_error("natsl_attn_fwd: unsupported head dims DK=%d DV=%d (each 64 or 128)", DK, DV);
     return NATSL_ERR_UNSUPPORTED;
 }
+}  // namespace natsl
 
 extern "C" int natsl_attn_dense_mask(const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters,
                                      uint8_t* mask, int B, int T, int HQ, int HN, int nbs, int flags, void* stream) {

@@ -1,0 +1,338 @@
+// Chunk-masked softmax attention forward on the 5th-generation tensor cores.
+//
+// One CTA = 128 queries of one softmax head; two CTAs share an SM (2 x 256 TMEM columns,
+// 2 x 112 KB shared memory), so one CTA's softmax overlaps the other's MMAs.  Warp roles:
+//   warp 0    TMA producer: Q once, then K/V tiles of the key-tile walk into a 2-stage ring
+//             (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the end of the sequence);
+//   warp 1    MMA issuer (one thread): S = Q K^T (tcgen05.mma, operands in shared memory, fp32
+//             accumulator in TMEM), then O += P V; completion is signalled with tcgen05.commit;
+//   warps 2-5 softmax, one thread per query row: tcgen05.ld of the row's 64 scores, mask, online
+//             softmax in base 2 with a lazily updated maximum (O in TMEM is only rescaled when
+//             the running maximum grows by more than 2^8), P (bf16) to shared memory for the
+//             second MMA; at the end O / l -> bf16 -> shared memory -> coalesced global stores.
+// Same key-tile walk, mask and output conventions as the mma.sync kernel (attn_walk.cuh):
+// src/nats/ops/attns/attns.py:62-353 is the reference kernel this replaces.
+// Every mbarrier wait has an iteration limit; on expiry the CTA records a status, stops issuing
+// work, still frees its TMEM and returns.
+#include "attn_walk.cuh"
+#include "tc_common.cuh"
+#include "../../include/natsl_b200.h"
+
+namespace natsl {
+
+int attn_fwd_mma_sync(const void* q, const void* k, const void* v, const int32_t* types_i, const int32_t* indices,
+                      const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int DK,
+                      int DV, int nbs, float scale, int own, cudaStream_t st);
+
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_TMEM_COLS = 256;      // S: columns [0,64), O: columns [64, 64+DV)
+constexpr float LAZY_RESCALE_LOG2 = 8.0f;
+
+template <int DK, int DV>
+struct TcSmem {
+    static constexpr int q = 0;                                  // DK/64 sub-tiles [128][64]
+    static constexpr int k = q + 128 * DK * 2;                   // 2 stages x DK/64 sub-tiles [64][64]
+    static constexpr int v = k + 2 * 64 * DK * 2;                // 2 stages x DV/64 sub-tiles [64][64]
+    static constexpr int p = v + 2 * 64 * DV * 2;                // [128][64]
+    static constexpr int bars = p + 128 * 64 * 2;
+    static constexpr int total = bars + 128;
+    static_assert(128 * DV * 2 <= 128 * DK * 2 + 2 * 64 * DK * 2, "output staging must fit over Q + K");
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ types_i,
+                   const int* __restrict__ indices, const int* __restrict__ attn_n_iters,
+                   __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int HQ, int HKV, int HN, int TN,
+                   int nbs, float scale_log2, int own_chunk, int* status) {
+    using L = TcSmem<DK, DV>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t sbase = smem_u32(smem);
+    if ((sbase & 1023u) != 0) {                       // swizzled tiles need 1024-byte alignment
+        if (tid == 0) atomicExch(status, 2);
+        return;
+    }
+    const int NTq = gridDim.x;
+    const int it = NTq - 1 - blockIdx.x;              // heaviest tiles first
+    const int hq = blockIdx.y, b = blockIdx.z;
+    const int hkv = hq / (HQ / HKV), hn = hq / (HQ / HN);
+    const int q0 = it * ATT_BM;
+    const int* idx = indices + ((long)b * TN * HN + hn) * 2;
+    const int* selp = types_i + ((long)b * TN * HN + hn) * 2;
+    const long tstride = (long)HN * 2;
+    const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
+    const int n_tiles = walk.n_tiles;
+
+    const uint32_t s_q = sbase + L::q, s_k = sbase + L::k, s_v = sbase + L::v, s_p = sbase + L::p;
+    const uint32_t bar0 = sbase + L::bars;
+    const uint32_t bar_q = bar0, bar_kv_full = bar0 + 8, bar_kv_empty = bar0 + 24, bar_s = bar0 + 40, bar_p = bar0 + 48,
+                   bar_o = bar0 + 56;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 64);
+
+    if (tid == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(bar_kv_full, 1);
+        mbar_init(bar_kv_full + 8, 1);
+        mbar_init(bar_kv_empty, 1);
+        mbar_init(bar_kv_empty + 8, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_p, 128);
+        mbar_init(bar_o, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            prefetch_tensormap(&map_q);
+            prefetch_tensormap(&map_k);
+            prefetch_tensormap(&map_v);
+            mbar_expect_tx(bar_q, 128 * DK * 2);
+#pragma unroll
+            for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0, b, bar_q);
+        }
+        for (int j = 0; j < n_tiles; ++j) {
+            const int stg = j & 1;
+            if (j >= 2) {
+                bool ok = mbar_wait(bar_kv_empty + stg * 8, ((j >> 1) - 1) & 1, status);
+                if (!__all_sync(0xffffffffu, ok)) break;
+            }
+            if (lane == 0) {
+                bool masked;
+                const int s0 = tile_start(walk, j, idx, tstride, nbs, masked);
+                const uint32_t full = bar_kv_full + stg * 8;
+                mbar_expect_tx(full, 64 * (DK + DV) * 2);
+#pragma unroll
+                for (int sub = 0; sub < DK / 64; ++sub)
+                    tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv, s0, b, full);
+#pragma unroll
+                for (int sub = 0; sub < DV / 64; ++sub)
+                    tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv, s0, b, full);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, DV, true);
+        bool ok = mbar_wait(bar_q, 0, status);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int stg = j & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_kv_full + stg * 8, (j >> 1) & 1, status));
+            if (!ok) break;
+            if (lane == 0) {
+                tc_fence_after();
+                const uint32_t kt = s_k + stg * (64 * DK * 2);
+#pragma unroll
+                for (int kk = 0; kk < DK / 16; ++kk) {
+                    const uint64_t ad = umma_desc(s_q + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bd = umma_desc(kt + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
+                    umma_ss(tmem, ad, bd, idesc_qk, kk > 0);
+                }
+                umma_commit(bar_s);
+            }
+            __syncwarp();
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_p, j & 1, status));
+            if (!ok) break;
+            if (lane == 0) {
+                tc_fence_after();
+                const uint32_t vt = s_v + stg * (64 * DV * 2);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t ad = umma_desc(s_p + kk * 32, 16, 1024);
+                    const uint64_t bd = umma_desc(vt + kk * 2048, 8192, 1024);
+                    umma_ss(tmem + 64, ad, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_kv_empty + stg * 8);
+                if (j == n_tiles - 1) umma_commit(bar_o);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue (128 threads)
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int t = q0 + row;
+        const uint32_t t_s = tmem + ((uint32_t)(quad * 32) << 16);
+        const uint32_t t_o = t_s + 64;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, status));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[64];
+            {
+                uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[0]);
+                uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[32]);
+                tmem_ld32(t_s, lo);
+                tmem_ld32(t_s + 32, hi);
+                tmem_ld_wait();
+            }
+            bool masked;
+            const int s0 = tile_start(walk, j, idx, tstride, nbs, masked);
+            bool selb = true;
+            int blk_end = 0;
+            if (masked) {
+                const int blk = s0 / nbs;
+                selb = selp[(long)blk * tstride] != 0;
+                blk_end = (blk + 1) * nbs;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float sv = __uint_as_float(sr[c]) * scale_log2;
+                if (masked && !visible(t, s0 + c, T, blk_end, selb, own_chunk != 0)) sv = -INFINITY;
+                sr[c] = __float_as_uint(sv);
+                mx = fmaxf(mx, sv);
+            }
+            const bool need = mx > m_used + LAZY_RESCALE_LOG2;
+            if (__any_sync(0xffffffffu, need)) {
+                const float m_new = need ? mx : m_used;
+                const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_used - m_new);
+                if (j > 0) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < DV; c0 += 32) {
+                        uint32_t orr[32];
+                        tmem_ld32(t_o + c0, orr);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st32(t_o + c0, orr);
+                    }
+                    tmem_st_wait();
+                }
+                l *= alpha;
+                m_used = m_new;
+            }
+            const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+            float rs = 0.f;
+            unsigned char* prow = smem + L::p;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint32_t w4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = ex2(__uint_as_float(sr[cc * 8 + 2 * i]) - m_eff);
+                    const float p1 = ex2(__uint_as_float(sr[cc * 8 + 2 * i + 1]) - m_eff);
+                    rs += p0 + p1;
+                    w4[i] = pack_bf16(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(prow + swz<128>(row, cc)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+            l += rs;
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar_p);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, 0, status));
+        unsigned char* stage = smem + L::q;
+        if (ok) {
+            tc_fence_after();
+            const bool has = l > 0.f;
+            const float inv = has ? 1.f / l : 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < DV; c0 += 32) {
+                uint32_t orr[32];
+                tmem_ld32(t_o + c0, orr);
+                tmem_ld_wait();
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w4[i] = pack_bf16(__uint_as_float(orr[cc * 8 + 2 * i]) * inv,
+                                          __uint_as_float(orr[cc * 8 + 2 * i + 1]) * inv);
+                    *reinterpret_cast<uint4*>(stage + swz<DV * 2>(row, (c0 >> 3) + cc)) =
+                        make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+            }
+            if (t < T) lse[((long)b * T + t) * HQ + hq] = has ? m_used + log2f(l) : 0.f;
+        }
+        // every softmax warp reaches this barrier, also after a failed wait (no warp may be left behind)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok) {
+            constexpr int CPR = DV / 8;
+            __nv_bfloat16* obase = o + (((long)b * T + q0) * HQ + hq) * DV;
+            const int st_tid = tid - 64;
+            for (int i = st_tid; i < 128 * CPR; i += 128) {
+                const int r = i / CPR, cch = i % CPR;
+                if (q0 + r < T) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(stage + swz<DV * 2>(r, cch));
+                    *reinterpret_cast<uint4*>(obase + (long)r * HQ * DV + cch * 8) = x;
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TC_TMEM_COLS);
+}
+
+template <int DK, int DV>
+static int launch_attn_tc(const void* q, const void* k, const void* v, const int* types_i, const int* indices,
+                          const int* n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int nbs,
+                          float scale, int own_chunk, cudaStream_t st) {
+    using L = TcSmem<DK, DV>;
+    auto kern = attn_fwd_tc_kernel<DK, DV>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+    if (e != cudaSuccess) {
+        set_error("natsl_attn_fwd: cannot reserve %d B of shared memory (%s)", L::total, cudaGetErrorString(e));
+        return NATSL_ERR_CUDA;
+    }
+    CUtensorMap mq, mk, mv;
+    int rc = encode_bthd_map(&mq, q, B, T, HQ, DK, 128, "natsl_attn_fwd(q)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T, HKV, DK, 64, "natsl_attn_fwd(k)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T, HKV, DV, 64, "natsl_attn_fwd(v)");
+    int* status = nullptr;
+    if (rc == NATSL_OK) rc = status_word_ptr(&status);
+    if (rc != NATSL_OK) return rc;
+    const int NTq = (T + ATT_BM - 1) / ATT_BM, TN = (T + nbs - 1) / nbs;
+    dim3 grid(NTq, HQ, B);
+    kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, types_i, indices, n_iters, reinterpret_cast<__nv_bfloat16*>(o),
+                                             lse, T, HQ, HKV, HN, TN, nbs, scale * 1.44269504f, own_chunk, status);
+    return check_launch("natsl_attn_fwd");
+}
+
+}  // namespace natsl
+
+extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,
+                              const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B, int T,
+                              int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(q && k && v && types_i && indices && attn_n_iters && o && lse, NATSL_ERR_NULL,
+                  "natsl_attn_fwd: null pointer");
+    NATSL_REQUIRE(B > 0 && T > 0 && HQ > 0 && HKV > 0 && HN > 0 && HQ % HKV == 0 && HQ % HN == 0, NATSL_ERR_BAD_SHAPE,
+                  "natsl_attn_fwd: bad shape B=%d T=%d HQ=%d HKV=%d HN=%d", B, T, HQ, HKV, HN);
+    NATSL_REQUIRE(HQ <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_attn_fwd: B and HQ must be <= 65535");
+    NATSL_REQUIRE(nbs >= 64 && nbs % 64 == 0, NATSL_ERR_UNSUPPORTED,
+                  "natsl_attn_fwd: nats_block_size must be a multiple of 64 (got %d)", nbs);
+    const int own = (flags & NATSL_FLAG_ATTN_OWN_CHUNK) ? 1 : 0;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (flags & NATSL_FLAG_ATTN_MMA_SYNC)
+        return attn_fwd_mma_sync(q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, DK, DV, nbs, scale,
+                                 own, st);
+#define NATSL_ATT_ARGS q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, nbs, scale, own, st
+    if (DK == 64 && DV == 64) return launch_attn_tc<64, 64>(NATSL_ATT_ARGS);
+    if (DK == 64 && DV == 128) return launch_attn_tc<64, 128>(NATSL_ATT_ARGS);
+    if (DK == 128 && DV == 64) return launch_attn_tc<128, 64>(NATSL_ATT_ARGS);
+    if (DK == 128 && DV == 128) return launch_attn_tc<128, 128>(NATSL_ATT_ARGS);
+#undef NATSL_ATT_ARGS
+    set_error("natsl_attn_fwd: unsupported head dims DK=%d DV=%d (each 64 or 128)", DK, DV);
+    return NATSL_ERR_UNSUPPORTED;
+}

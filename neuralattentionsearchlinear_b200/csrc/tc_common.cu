@@ -1,0 +1,97 @@
+// Host side of the tensor-core kernels' shared plumbing: the per-device status word that bounded
+// waits write when they give up, and TMA tensor-map encoding through the driver entry point
+// (resolved at run time, so the library does not link against libcuda).
+#include <mutex>
+
+#include "tc_common.cuh"
+#include "../../include/natsl_b200.h"
+
+namespace natsl {
+
+static __device__ int g_status_word = 0;
+
+constexpr int kMaxDev = 64;
+static std::mutex g_mu;
+static int* g_status_addr[kMaxDev] = {nullptr};
+
+int status_word_ptr(int** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+        set_error("cannot identify the current device (%s)", cudaGetErrorString(e));
+        return NATSL_ERR_CUDA;
+    }
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_status_addr[dev]) {
+        int* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word);
+        if (e != cudaSuccess || !p) {
+            set_error("cudaGetSymbolAddress(status word) failed on device %d (%s)", dev, cudaGetErrorString(e));
+            return NATSL_ERR_CUDA;
+        }
+        g_status_addr[dev] = p;
+    }
+    *out = g_status_addr[dev];
+    return NATSL_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int encode_bthd_map(CUtensorMap* out, const void* base, int B, int T, int H, int D, int box_rows, const char* who) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) {
+        set_error("%s: the driver does not provide cuTensorMapEncodeTiled", who);
+        return NATSL_ERR_CUDA;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || D % 64 != 0) {
+        set_error("%s: TMA needs a 16-byte aligned base and a head dim multiple of 64 (D=%d)", who, D);
+        return NATSL_ERR_UNSUPPORTED;
+    }
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2, (cuuint64_t)T * H * D * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("%s: cuTensorMapEncodeTiled failed (%d) for [B=%d,T=%d,H=%d,D=%d]", who, (int)r, B, T, H, D);
+        return NATSL_ERR_CUDA;
+    }
+    return NATSL_OK;
+}
+
+}  // namespace natsl
+
+extern "C" int natsl_device_status(void) {
+    using namespace natsl;
+    int* p = nullptr;
+    int rc = status_word_ptr(&p);
+    if (rc != NATSL_OK) return rc;
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);     // synchronises the device
+    if (e != cudaSuccess) {
+        set_error("natsl_device_status: %s", cudaGetErrorString(e));
+        return NATSL_ERR_CUDA;
+    }
+    if (v != 0) {
+        cudaMemset(p, 0, sizeof(int));
+        set_error("a kernel gave up a bounded wait (device status %d); its outputs are invalid", v);
+    }
+    return v;
+}

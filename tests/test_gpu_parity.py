@@ -93,6 +93,12 @@ def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own):
     o_ref, lse_ref = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask, DK ** -0.5)
     assert_close(o, o_ref, TOL, "o_attn")
     assert_close(lse, lse_ref, TOL, "lse")
+    from neuralattentionsearchlinear_b200 import _lib
+    assert _lib.load().natsl_device_status() == 0
+    # the mma.sync comparison kernel realises the same function
+    o2, lse2 = _ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), tb, DK ** -0.5, own, mma_sync=True)
+    assert_close(o2, o_ref, TOL, "o_attn (mma.sync)")
+    assert_close(lse2, lse_ref, TOL, "lse (mma.sync)")
 
 
 GDN_CASES = [  # B, T, H, HN, K, V, nbs, decay, use_h0
