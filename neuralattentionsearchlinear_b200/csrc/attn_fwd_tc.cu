@@ -1,15 +1,19 @@
 // Chunk-masked softmax attention forward on the 5th-generation tensor cores.
 //
 // One CTA = 128 queries of one softmax head; two CTAs share an SM (2 x 256 TMEM columns,
-// 2 x 112 KB shared memory), so one CTA's softmax overlaps the other's MMAs.  Warp roles:
-//   warp 0    TMA producer: Q once, then K/V tiles of the key-tile walk into a 2-stage ring
-//             (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the end of the sequence);
-//   warp 1    MMA issuer (one thread): S = Q K^T (tcgen05.mma, operands in shared memory, fp32
-//             accumulator in TMEM), then O += P V; completion is signalled with tcgen05.commit;
+// 2 x ~100 KB shared memory).  Warp roles:
+//   warp 0    TMA producer: Q once, then the K and V tiles of the key-tile walk into two separate
+//             2-stage rings (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the sequence end);
+//   warp 1    MMA issuer (one thread): S_j = Q K_j^T into one of two TMEM score buffers, issued two
+//             tiles ahead, and O += P_j V_j with P read straight from TMEM; completion is signalled
+//             with tcgen05.commit on mbarriers;
 //   warps 2-5 softmax, one thread per query row: tcgen05.ld of the row's 64 scores, mask, online
-//             softmax in base 2 with a lazily updated maximum (O in TMEM is only rescaled when
-//             the running maximum grows by more than 2^8), P (bf16) to shared memory for the
-//             second MMA; at the end O / l -> bf16 -> shared memory -> coalesced global stores.
+//             softmax in base 2 with a lazily updated maximum (O in TMEM is only rescaled when the
+//             running maximum grows by more than 2^8), P (bf16 pairs) written back with tcgen05.st
+//             over the score buffer it came from; at the end O / l -> bf16 -> shared memory ->
+//             coalesced global stores.
+// While the softmax warps work on tile j the tensor core runs Q K_{j+1}^T and P_{j-1} V_{j-1}.
+// The key-tile list (start key, masked, selected) is computed once per CTA into shared memory.
 // Same key-tile walk, mask and output conventions as the mma.sync kernel (attn_walk.cuh):
 // src/nats/ops/attns/attns.py:62-353 is the reference kernel this replaces.
 // Every mbarrier wait has an iteration limit; on expiry the CTA records a status, stops issuing
@@ -25,17 +29,19 @@ int attn_fwd_mma_sync(const void* q, const void* k, const void* v, const int32_t
                       int DV, int nbs, float scale, int own, cudaStream_t st);
 
 constexpr int TC_THREADS = 192;
-constexpr uint32_t TC_TMEM_COLS = 256;      // S: columns [0,64), O: columns [64, 64+DV)
+constexpr uint32_t TC_TMEM_COLS = 256;      // S0: [0,64), S1: [64,128), O: [128, 128+DV); P_j aliases S_{j&1}
+constexpr uint32_t TC_O_COL = 128;
 constexpr float LAZY_RESCALE_LOG2 = 8.0f;
+constexpr int TC_LIST_CAP = 1024;           // key tiles whose descriptors are kept in shared memory
 
 template <int DK, int DV>
 struct TcSmem {
     static constexpr int q = 0;                                  // DK/64 sub-tiles [128][64]
     static constexpr int k = q + 128 * DK * 2;                   // 2 stages x DK/64 sub-tiles [64][64]
     static constexpr int v = k + 2 * 64 * DK * 2;                // 2 stages x DV/64 sub-tiles [64][64]
-    static constexpr int p = v + 2 * 64 * DV * 2;                // [128][64]
-    static constexpr int bars = p + 128 * 64 * 2;
-    static constexpr int total = bars + 128;
+    static constexpr int list = v + 2 * 64 * DV * 2;             // int[TC_LIST_CAP]
+    static constexpr int bars = list + TC_LIST_CAP * 4;
+    static constexpr int total = bars + 256;
     static_assert(128 * DV * 2 <= 128 * DK * 2 + 2 * 64 * DK * 2, "output staging must fit over Q + K");
 };
 
@@ -43,6 +49,15 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// packed tile descriptor: bits [0,30) first key, bit 30 masked, bit 31 block selected
+__device__ __forceinline__ int pack_tile(const TileWalk& w, int j, const int* idx, const int* selp, long tstride, int nbs) {
+    bool masked;
+    int s0 = tile_start(w, j, idx, tstride, nbs, masked);
+    int sel = 1;
+    if (masked) sel = selp[(long)(s0 / nbs) * tstride] != 0;
+    return s0 | (masked ? (1 << 30) : 0) | (sel ? (1 << 31) : 0);
 }
 
 template <int DK, int DV>
@@ -71,28 +86,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
     const int n_tiles = walk.n_tiles;
 
-    const uint32_t s_q = sbase + L::q, s_k = sbase + L::k, s_v = sbase + L::v, s_p = sbase + L::p;
+    const uint32_t s_q = sbase + L::q, s_k = sbase + L::k, s_v = sbase + L::v;
+    int* tile_list = reinterpret_cast<int*>(smem + L::list);
     const uint32_t bar0 = sbase + L::bars;
-    const uint32_t bar_q = bar0, bar_kv_full = bar0 + 8, bar_kv_empty = bar0 + 24, bar_s = bar0 + 40, bar_p = bar0 + 48,
-                   bar_o = bar0 + 56;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 64);
+    // barrier slots (8 bytes each)
+    const uint32_t bar_q = bar0, bar_k_full = bar0 + 8, bar_k_empty = bar0 + 24, bar_v_full = bar0 + 40,
+                   bar_v_empty = bar0 + 56, bar_s_full = bar0 + 72, bar_p_full = bar0 + 88, bar_pv = bar0 + 104;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 128);
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_kv_full, 1);
-        mbar_init(bar_kv_full + 8, 1);
-        mbar_init(bar_kv_empty, 1);
-        mbar_init(bar_kv_empty + 8, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_p, 128);
-        mbar_init(bar_o, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_k_full + 8 * i, 1);
+            mbar_init(bar_k_empty + 8 * i, 1);
+            mbar_init(bar_v_full + 8 * i, 1);
+            mbar_init(bar_v_empty + 8 * i, 1);
+            mbar_init(bar_s_full + 8 * i, 1);
+            mbar_init(bar_p_full + 8 * i, 128);
+        }
+        mbar_init(bar_pv, 1);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
+    for (int j = tid; j < min(n_tiles, TC_LIST_CAP); j += TC_THREADS) tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    auto tile_desc = [&](int j) -> int {
+        return j < TC_LIST_CAP ? tile_list[j] : pack_tile(walk, j, idx, selp, tstride, nbs);
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -106,18 +129,25 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         for (int j = 0; j < n_tiles; ++j) {
             const int stg = j & 1;
+            const int s0 = tile_desc(j) & 0x3FFFFFFF;
             if (j >= 2) {
-                bool ok = mbar_wait(bar_kv_empty + stg * 8, ((j >> 1) - 1) & 1, status);
+                bool ok = mbar_wait(bar_k_empty + stg * 8, ((j >> 1) - 1) & 1, status);
                 if (!__all_sync(0xffffffffu, ok)) break;
             }
             if (lane == 0) {
-                bool masked;
-                const int s0 = tile_start(walk, j, idx, tstride, nbs, masked);
-                const uint32_t full = bar_kv_full + stg * 8;
-                mbar_expect_tx(full, 64 * (DK + DV) * 2);
+                const uint32_t full = bar_k_full + stg * 8;
+                mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
                 for (int sub = 0; sub < DK / 64; ++sub)
                     tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv, s0, b, full);
+            }
+            if (j >= 2) {
+                bool ok = mbar_wait(bar_v_empty + stg * 8, ((j >> 1) - 1) & 1, status);
+                if (!__all_sync(0xffffffffu, ok)) break;
+            }
+            if (lane == 0) {
+                const uint32_t full = bar_v_full + stg * 8;
+                mbar_expect_tx(full, 64 * DV * 2);
 #pragma unroll
                 for (int sub = 0; sub < DV / 64; ++sub)
                     tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv, s0, b, full);
@@ -128,51 +158,68 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, DV, true);
-        bool ok = mbar_wait(bar_q, 0, status);
-        ok = __all_sync(0xffffffffu, ok);
-        for (int j = 0; ok && j < n_tiles; ++j) {
+        auto issue_qk = [&](int j) {                  // S_{j&1} = Q K_j^T   (lane 0 only)
             const int stg = j & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_kv_full + stg * 8, (j >> 1) & 1, status));
-            if (!ok) break;
-            if (lane == 0) {
-                tc_fence_after();
-                const uint32_t kt = s_k + stg * (64 * DK * 2);
+            const uint32_t kt = s_k + stg * (64 * DK * 2);
 #pragma unroll
-                for (int kk = 0; kk < DK / 16; ++kk) {
-                    const uint64_t ad = umma_desc(s_q + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = umma_desc(kt + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
-                    umma_ss(tmem, ad, bd, idesc_qk, kk > 0);
-                }
-                umma_commit(bar_s);
+            for (int kk = 0; kk < DK / 16; ++kk) {
+                const uint64_t ad = umma_desc(s_q + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                const uint64_t bd = umma_desc(kt + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
+                umma_ss(tmem + stg * 64, ad, bd, idesc_qk, kk > 0);
+            }
+            umma_commit(bar_s_full + stg * 8);
+            umma_commit(bar_k_empty + stg * 8);
+        };
+        bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, status));
+        for (int j = 0; ok && j < min(2, n_tiles); ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + j * 8, 0, status));
+            if (ok && lane == 0) {
+                tc_fence_after();
+                issue_qk(j);
             }
             __syncwarp();
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_p, j & 1, status));
+        }
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int stg = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_v_full + stg * 8, ph, status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_p_full + stg * 8, ph, status));
             if (!ok) break;
             if (lane == 0) {
                 tc_fence_after();
                 const uint32_t vt = s_v + stg * (64 * DV * 2);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t ad = umma_desc(s_p + kk * 32, 16, 1024);
                     const uint64_t bd = umma_desc(vt + kk * 2048, 8192, 1024);
-                    umma_ss(tmem + 64, ad, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_ts(tmem + TC_O_COL, tmem + stg * 64 + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_kv_empty + stg * 8);
-                if (j == n_tiles - 1) umma_commit(bar_o);
+                umma_commit(bar_v_empty + stg * 8);
+                umma_commit(bar_pv);
             }
             __syncwarp();
+            if (j + 2 < n_tiles) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + stg * 8, ((j + 2) >> 1) & 1, status));
+                if (!ok) break;
+                if (lane == 0) {
+                    tc_fence_after();
+                    issue_qk(j + 2);
+                }
+                __syncwarp();
+            }
         }
     } else {
         // ------------------------------------------------------------ softmax + epilogue (128 threads)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int t = q0 + row;
-        const uint32_t t_s = tmem + ((uint32_t)(quad * 32) << 16);
-        const uint32_t t_o = t_s + 64;
+        const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+        const uint32_t t_o = t_lane + TC_O_COL;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, status));
+            const int sb = j & 1;
+            const uint32_t t_s = t_lane + sb * 64;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + sb * 8, (j >> 1) & 1, status));
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[64];
@@ -183,28 +230,39 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_ld32(t_s + 32, hi);
                 tmem_ld_wait();
             }
-            bool masked;
-            const int s0 = tile_start(walk, j, idx, tstride, nbs, masked);
-            bool selb = true;
-            int blk_end = 0;
-            if (masked) {
-                const int blk = s0 / nbs;
-                selb = selp[(long)blk * tstride] != 0;
-                blk_end = (blk + 1) * nbs;
-            }
+            const int td = tile_desc(j);
+            const bool masked = (td >> 30) & 1;
             float mx = -INFINITY;
+            if (masked) {
+                const int s0 = td & 0x3FFFFFFF;
+                const bool selb = (td >> 31) & 1;
+                const int blk_end = (s0 / nbs + 1) * nbs;
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float sv = __uint_as_float(sr[c]) * scale_log2;
-                if (masked && !visible(t, s0 + c, T, blk_end, selb, own_chunk != 0)) sv = -INFINITY;
-                sr[c] = __float_as_uint(sv);
-                mx = fmaxf(mx, sv);
+                for (int c = 0; c < 64; ++c) {
+                    float sv = __uint_as_float(sr[c]) * scale_log2;
+                    if (!visible(t, s0 + c, T, blk_end, selb, own_chunk != 0)) sv = -INFINITY;
+                    sr[c] = __float_as_uint(sv);
+                    mx = fmaxf(mx, sv);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const float sv = __uint_as_float(sr[c]) * scale_log2;
+                    sr[c] = __float_as_uint(sv);
+                    mx = fmaxf(mx, sv);
+                }
             }
             const bool need = mx > m_used + LAZY_RESCALE_LOG2;
+            bool pv_seen = (j == 0);                  // has this thread observed the completion of P_{j-1} V_{j-1}?
             if (__any_sync(0xffffffffu, need)) {
                 const float m_new = need ? mx : m_used;
                 const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_used - m_new);
                 if (j > 0) {
+                    // O must be at rest: wait until P_{j-1} V_{j-1} has completed
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, status));
+                    if (!ok) break;
+                    pv_seen = true;
+                    tc_fence_after();
 #pragma unroll 1
                     for (int c0 = 0; c0 < DV; c0 += 32) {
                         uint32_t orr[32];
@@ -214,32 +272,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
                         tmem_st32(t_o + c0, orr);
                     }
-                    tmem_st_wait();
                 }
                 l *= alpha;
                 m_used = m_new;
             }
             const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
             float rs = 0.f;
-            unsigned char* prow = smem + L::p;
+            uint32_t pk[32];
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
-                uint32_t w4[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = ex2(__uint_as_float(sr[cc * 8 + 2 * i]) - m_eff);
-                    const float p1 = ex2(__uint_as_float(sr[cc * 8 + 2 * i + 1]) - m_eff);
-                    rs += p0 + p1;
-                    w4[i] = pack_bf16(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(prow + swz<128>(row, cc)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = ex2(__uint_as_float(sr[2 * i]) - m_eff);
+                const float p1 = ex2(__uint_as_float(sr[2 * i + 1]) - m_eff);
+                rs += p0 + p1;
+                pk[i] = pack_bf16(p0, p1);
             }
             l += rs;
-            fence_async_smem();
+            if (!pv_seen) {
+                // every phase of the P V barrier is observed in order (a parity wait can only tell the
+                // current phase from the previous one); by now P_{j-1} V_{j-1} has normally long finished
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, status));
+                if (!ok) break;
+            }
+            tmem_st32(t_s, pk);                       // P_j over the first 32 columns of S_{j&1}
+            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p_full + sb * 8);
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, 0, status));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (n_tiles - 1) & 1, status));
         unsigned char* stage = smem + L::q;
         if (ok) {
             tc_fence_after();
