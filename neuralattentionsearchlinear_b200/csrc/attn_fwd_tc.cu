@@ -32,17 +32,20 @@ constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_TMEM_COLS = 256;      // S0: [0,64), S1: [64,128), O: [128, 128+DV); P_j aliases S_{j&1}
 constexpr uint32_t TC_O_COL = 128;
 constexpr float LAZY_RESCALE_LOG2 = 8.0f;
-constexpr int TC_LIST_CAP = 1024;           // key tiles whose descriptors are kept in shared memory
+constexpr int TC_LIST_CAP = 128;            // key tiles whose descriptors are kept in shared memory
+constexpr int TC_KST = 3;                   // K ring stages
+constexpr int TC_VST = 2;                   // V ring stages
 
 template <int DK, int DV>
 struct TcSmem {
     static constexpr int q = 0;                                  // DK/64 sub-tiles [128][64]
-    static constexpr int k = q + 128 * DK * 2;                   // 2 stages x DK/64 sub-tiles [64][64]
-    static constexpr int v = k + 2 * 64 * DK * 2;                // 2 stages x DV/64 sub-tiles [64][64]
-    static constexpr int list = v + 2 * 64 * DV * 2;             // int[TC_LIST_CAP]
+    static constexpr int k = q + 128 * DK * 2;                   // TC_KST stages x DK/64 sub-tiles [64][64]
+    static constexpr int v = k + TC_KST * 64 * DK * 2;           // TC_VST stages x DV/64 sub-tiles [64][64]
+    static constexpr int list = v + TC_VST * 64 * DV * 2;        // int[TC_LIST_CAP]
     static constexpr int bars = list + TC_LIST_CAP * 4;
     static constexpr int total = bars + 256;
-    static_assert(128 * DV * 2 <= 128 * DK * 2 + 2 * 64 * DK * 2, "output staging must fit over Q + K");
+    static_assert(128 * DV * 2 <= 128 * DK * 2 + TC_KST * 64 * DK * 2, "output staging must fit over Q + K");
+    static_assert(total <= 115712, "two CTAs per SM");
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -90,17 +93,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     int* tile_list = reinterpret_cast<int*>(smem + L::list);
     const uint32_t bar0 = sbase + L::bars;
     // barrier slots (8 bytes each)
-    const uint32_t bar_q = bar0, bar_k_full = bar0 + 8, bar_k_empty = bar0 + 24, bar_v_full = bar0 + 40,
-                   bar_v_empty = bar0 + 56, bar_s_full = bar0 + 72, bar_p_full = bar0 + 88, bar_pv = bar0 + 104;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 128);
+    const uint32_t bar_q = bar0, bar_k_full = bar0 + 8, bar_k_empty = bar0 + 40, bar_v_full = bar0 + 72,
+                   bar_v_empty = bar0 + 104, bar_s_full = bar0 + 136, bar_p_full = bar0 + 152, bar_pv = bar0 + 168;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 192);
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(bar_k_full + 8 * i, 1);
             mbar_init(bar_k_empty + 8 * i, 1);
             mbar_init(bar_v_full + 8 * i, 1);
             mbar_init(bar_v_empty + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
             mbar_init(bar_p_full + 8 * i, 128);
         }
@@ -127,30 +132,57 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0, b, bar_q);
         }
-        for (int j = 0; j < n_tiles; ++j) {
-            const int stg = j & 1;
-            const int s0 = tile_desc(j) & 0x3FFFFFFF;
-            if (j >= 2) {
-                bool ok = mbar_wait(bar_k_empty + stg * 8, ((j >> 1) - 1) & 1, status);
-                if (!__all_sync(0xffffffffu, ok)) break;
-            }
-            if (lane == 0) {
-                const uint32_t full = bar_k_full + stg * 8;
-                mbar_expect_tx(full, 64 * DK * 2);
+        // K and V rings advance independently: whichever ring has a free stage gets its next tile.
+        int jk = 0, jv = 0, idle = 0;
+        while (jk < n_tiles || jv < n_tiles) {
+            bool progressed = false;
+            if (jk < n_tiles) {
+                const int stg = jk % TC_KST;
+                bool ready = jk < TC_KST || mbar_try_wait(bar_k_empty + stg * 8, ((jk / TC_KST) - 1) & 1);
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (ready) {
+                    if (lane == 0) {
+                        const int s0 = tile_desc(jk) & 0x3FFFFFFF;
+                        const uint32_t full = bar_k_full + stg * 8;
+                        mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
-                for (int sub = 0; sub < DK / 64; ++sub)
-                    tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv, s0, b, full);
+                        for (int sub = 0; sub < DK / 64; ++sub)
+                            tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv, s0, b, full);
+                    }
+                    ++jk;
+                    progressed = true;
+                }
             }
-            if (j >= 2) {
-                bool ok = mbar_wait(bar_v_empty + stg * 8, ((j >> 1) - 1) & 1, status);
-                if (!__all_sync(0xffffffffu, ok)) break;
-            }
-            if (lane == 0) {
-                const uint32_t full = bar_v_full + stg * 8;
-                mbar_expect_tx(full, 64 * DV * 2);
+            if (jv < n_tiles) {
+                const int stg = jv % TC_VST;
+                bool ready = jv < TC_VST || mbar_try_wait(bar_v_empty + stg * 8, ((jv / TC_VST) - 1) & 1);
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (ready) {
+                    if (lane == 0) {
+                        const int s0 = tile_desc(jv) & 0x3FFFFFFF;
+                        const uint32_t full = bar_v_full + stg * 8;
+                        mbar_expect_tx(full, 64 * DV * 2);
 #pragma unroll
-                for (int sub = 0; sub < DV / 64; ++sub)
-                    tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv, s0, b, full);
+                        for (int sub = 0; sub < DV / 64; ++sub)
+                            tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv, s0, b, full);
+                        // warm L2 for the tile this ring will want next
+                        if (jv + TC_VST < n_tiles) {
+                            const int s1 = tile_desc(jv + TC_VST) & 0x3FFFFFFF;
+#pragma unroll
+                            for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(&map_v, sub * 64, hkv, s1, b);
+#pragma unroll
+                            for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(&map_k, sub * 64, hkv, s1, b);
+                        }
+                    }
+                    ++jv;
+                    progressed = true;
+                }
+            }
+            if (progressed) {
+                idle = 0;
+            } else if (++idle > kWaitLimit) {
+                if (lane == 0) atomicExch(status, NATSL_DEV_WAIT_TIMEOUT);
+                break;
             }
             __syncwarp();
         }
@@ -159,20 +191,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, DV, true);
         auto issue_qk = [&](int j) {                  // S_{j&1} = Q K_j^T   (lane 0 only)
-            const int stg = j & 1;
+            const int sb = j & 1, stg = j % TC_KST;
             const uint32_t kt = s_k + stg * (64 * DK * 2);
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
                 const uint64_t ad = umma_desc(s_q + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
                 const uint64_t bd = umma_desc(kt + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
-                umma_ss(tmem + stg * 64, ad, bd, idesc_qk, kk > 0);
+                umma_ss(tmem + sb * 64, ad, bd, idesc_qk, kk > 0);
             }
-            umma_commit(bar_s_full + stg * 8);
+            umma_commit(bar_s_full + sb * 8);
             umma_commit(bar_k_empty + stg * 8);
         };
         bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, status));
         for (int j = 0; ok && j < min(2, n_tiles); ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + j * 8, 0, status));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + (j % TC_KST) * 8, (j / TC_KST) & 1, status));
             if (ok && lane == 0) {
                 tc_fence_after();
                 issue_qk(j);
@@ -180,29 +212,29 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             __syncwarp();
         }
         for (int j = 0; ok && j < n_tiles; ++j) {
-            const int stg = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_v_full + stg * 8, ph, status));
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_p_full + stg * 8, ph, status));
+            const int sb = j & 1, vstg = j % TC_VST;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_v_full + vstg * 8, (j / TC_VST) & 1, status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_p_full + sb * 8, (j >> 1) & 1, status));
             if (!ok) break;
             if (lane == 0) {
                 tc_fence_after();
-                const uint32_t vt = s_v + stg * (64 * DV * 2);
+                const uint32_t vt = s_v + vstg * (64 * DV * 2);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const uint64_t bd = umma_desc(vt + kk * 2048, 8192, 1024);
-                    umma_ts(tmem + TC_O_COL, tmem + stg * 64 + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_ts(tmem + TC_O_COL, tmem + sb * 64 + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_v_empty + stg * 8);
+                umma_commit(bar_v_empty + vstg * 8);
                 umma_commit(bar_pv);
             }
             __syncwarp();
             if (j + 2 < n_tiles) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + stg * 8, ((j + 2) >> 1) & 1, status));
+                const int jn = j + 2;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + (jn % TC_KST) * 8, (jn / TC_KST) & 1, status));
                 if (!ok) break;
                 if (lane == 0) {
                     tc_fence_after();
-                    issue_qk(j + 2);
+                    issue_qk(jn);
                 }
                 __syncwarp();
             }
@@ -232,26 +264,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             const int td = tile_desc(j);
             const bool masked = (td >> 30) & 1;
-            float mx = -INFINITY;
             if (masked) {
+                // own-span tile: per row the visible keys are columns [0, c_limit] (attn_walk.cuh: visible())
                 const int s0 = td & 0x3FFFFFFF;
                 const bool selb = (td >> 31) & 1;
                 const int blk_end = (s0 / nbs + 1) * nbs;
-#pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    float sv = __uint_as_float(sr[c]) * scale_log2;
-                    if (!visible(t, s0 + c, T, blk_end, selb, own_chunk != 0)) sv = -INFINITY;
-                    sr[c] = __float_as_uint(sv);
-                    mx = fmaxf(mx, sv);
+                int c_limit = T - 1 - s0;
+                if (own_chunk) {
+                    c_limit = min(c_limit, t - s0);
+                    if (!(selb || t < blk_end)) c_limit = -1;
+                } else if (!(selb && t >= blk_end)) {
+                    c_limit = -1;
                 }
-            } else {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const float sv = __uint_as_float(sr[c]) * scale_log2;
-                    sr[c] = __float_as_uint(sv);
-                    mx = fmaxf(mx, sv);
-                }
+                for (int c = 0; c < 64; ++c) sr[c] = (c <= c_limit) ? sr[c] : 0xff800000u;   // -inf
             }
+            // row maximum of the raw scores (scale > 0, so max(scale * s) = scale * max(s)); four
+            // independent chains keep the dependent-issue latency short
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(sr[c + i]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             const bool need = mx > m_used + LAZY_RESCALE_LOG2;
             bool pv_seen = (j == 0);                  // has this thread observed the completion of P_{j-1} V_{j-1}?
             if (__any_sync(0xffffffffu, need)) {
@@ -276,16 +312,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 l *= alpha;
                 m_used = m_new;
             }
-            const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-            float rs = 0.f;
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const float p0 = ex2(__uint_as_float(sr[2 * i]) - m_eff);
-                const float p1 = ex2(__uint_as_float(sr[2 * i + 1]) - m_eff);
-                rs += p0 + p1;
+                const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), scale_log2, neg_m));
+                rs4[i & 3] += p0 + p1;
                 pk[i] = pack_bf16(p0, p1);
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l += rs;
             if (!pv_seen) {
                 // every phase of the P V barrier is observed in order (a parity wait can only tell the
