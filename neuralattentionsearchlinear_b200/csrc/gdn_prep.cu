@@ -3,30 +3,37 @@
 //   k_rstd = rsqrt(sum k^2 + 1e-6)                 (l2norm, src/nats/ops/mixed_ops/mixed_attn_gdn.py:119-121)
 //   gcs    = chunk-local inclusive cumsum of g      (src/nats/ops/gated_delta_rule/chunk.py:52-54)
 //   A      = strictLower(beta_i (kn_i . kn_j) e^{gcs_i - gcs_j})   (src/nats/ops/common/chunk_scaled_dot_kkt.py:105-126)
-//   Ai     = (I + A)^-1, fp32 forward substitution on the four 16x16 diagonal blocks, then
-//            block merge                            (src/nats/ops/utils/solve_tril.py:350-447)
-//   u = Ai (v beta),  w = Ai (kn beta e^{gcs})      (src/nats/ops/gated_delta_rule/wy_fast.py:123-153)
-// The decay carried over skipped blocks multiplies w by one scalar per chunk (the inverse
-// and A only see decay differences), so it is applied by the consumers and w here is
-// carry-free.  KK^T, u and w run on the tensor cores (bf16 in, fp32 accumulate); the
-// inverse stays in fp32 on the CUDA cores like the reference's ieee-precision default.
+//   [u | w] = (I + A)^-1 [v beta | kn beta e^{gcs}]                (src/nats/ops/utils/solve_tril.py:350-447,
+//                                                                  src/nats/ops/gated_delta_rule/wy_fast.py:123-153)
+// The reference forms (I + A)^-1 explicitly (16x16 diagonal blocks by forward substitution, then a
+// block merge) and multiplies.  Only the product is needed in the forward pass, so this kernel solves
+// the block-triangular system instead: with X_ii = (I + A_ii)^-1 (fp32 forward substitution, CUDA
+// cores) and G_ij = -X_ii A_ij (j < i), G_ii = X_ii (bf16),
+//     U_i = G_ii Z_i + sum_{j<i} G_ij U_j          for the four 16-row blocks i = 0..3,
+// where Z = [v beta | kn beta e^{gcs}] and U overwrites Z in place.  Each warp owns 64 columns of Z and
+// runs its four steps on the tensor cores without block-wide synchronisation; U_j is rounded to bf16
+// between steps, the same rounding the stored u, w get.
+// The decay carried over skipped blocks multiplies w by one scalar per chunk (A only sees decay
+// differences), so it is applied by the consumers and w here is carry-free.
 #include "common.cuh"
 #include "../../include/natsl_b200.h"
 
 namespace natsl {
 
 constexpr int PREP_THREADS = 128;
-constexpr int A_LD = 65;
+constexpr int A_LD = 68;            // fp32 row pitch of A: 16-byte aligned rows for float4 reads
+constexpr int X_LD = 17;            // pitch of the 16x16 diagonal-block inverses
 
 template <int K, int V>
 struct PrepSmem {
     static constexpr int ks = 0;
     static constexpr int vs = ks + 64 * K * 2;
-    static constexpr int As = vs + 64 * V * 2;                 // fp32 [64][65]; later Ai bf16 [64][64]
-    static constexpr int Xs = As + 64 * A_LD * 4;              // fp32 [64][65]; later output staging
-    static constexpr int Tm = Xs + 64 * A_LD * 4;              // fp32 [3][16][17]
-    static constexpr int vec = Tm + 3 * 16 * 17 * 4;           // gcs, beta, rstd, wscale: 4 x 64 floats
+    static constexpr int As = vs + 64 * V * 2;                 // fp32 [64][68]
+    static constexpr int Xs = As + 64 * A_LD * 4;              // fp32 [4][16][17]
+    static constexpr int Gs = Xs + 4 * 16 * X_LD * 4;          // bf16 [64][64] swizzled (128-byte rows)
+    static constexpr int vec = Gs + 64 * 64 * 2;               // gcs, beta, rstd, wscale: 4 x 64 floats
     static constexpr int total = vec + 4 * 64 * 4;
+    static_assert(Gs % 128 == 0, "G tile alignment");
 };
 
 template <int COLS>
@@ -47,48 +54,46 @@ __device__ __forceinline__ void scale_rows_inplace(unsigned char* tile, const fl
     }
 }
 
-// out[16w.., :] = Ai[16w.., :] * B  (B = [64 tokens][COLS] bf16 tile), 64 columns at a time,
-// staged per warp through `stage` and written to global with 16-byte stores.
+// Block forward substitution on 64 columns [col0, col0+64) of a [64][COLS] tile, in place, by one warp;
+// then the warp stores its 64x64 slice to global memory (row stride gstride elements).
 template <int COLS>
-__device__ __forceinline__ void tri_matmul_store(uint32_t ai, uint32_t bt, unsigned char* stage, __nv_bfloat16* gout,
-                                                 long gstride, int valid, int warp, int lane) {
-    const int r0 = warp * 16;
-    const uint32_t st = smem_u32(stage);
-#pragma unroll 1
-    for (int cg = 0; cg < COLS / 64; ++cg) {
+__device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsigned char* zptr, int col0,
+                                            __nv_bfloat16* gout, long gstride, int valid, int lane) {
+    const int g = lane >> 2, q = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
         float acc[8][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int a = 0; a < 8; ++a)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-        for (int kk = 0; kk <= warp; ++kk) {
-            uint32_t a[4];
-            load_a<128>(ai, r0, kk * 16, lane, a);
+            for (int e = 0; e < 4; ++e) acc[a][e] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk <= i; ++kk) {
+            uint32_t af[4];
+            load_a<128>(gtile, 16 * i, 16 * kk, lane, af);
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                uint32_t b[4];
-                load_b_kn<COLS * 2>(bt, kk * 16, cg * 64 + p * 16, lane, b);
-                mma_bf16(acc[2 * p], a, b[0], b[1]);
-                mma_bf16(acc[2 * p + 1], a, b[2], b[3]);
+                uint32_t bf[4];
+                load_b_kn<COLS * 2>(ztile, 16 * kk, col0 + 16 * p, lane, bf);
+                mma_bf16(acc[2 * p], af, bf[0], bf[1]);
+                mma_bf16(acc[2 * p + 1], af, bf[2], bf[3]);
             }
         }
-        const int g = lane >> 2, q = lane & 3;
+        __syncwarp();          // all lanes have read the rows of block i before they are overwritten
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            // column pair (nt*8 + 2q, +1) -> chunk nt, word q
-            *reinterpret_cast<uint32_t*>(stage + swz<128>(r0 + g, nt) + q * 4) = pack_bf16(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<uint32_t*>(stage + swz<128>(r0 + g + 8, nt) + q * 4) = pack_bf16(acc[nt][2], acc[nt][3]);
+            const int ch = (col0 >> 3) + nt;
+            *reinterpret_cast<uint32_t*>(zptr + swz<COLS * 2>(16 * i + g, ch) + q * 4) = pack_bf16(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<uint32_t*>(zptr + swz<COLS * 2>(16 * i + g + 8, ch) + q * 4) = pack_bf16(acc[nt][2], acc[nt][3]);
         }
         __syncwarp();
-        for (int i = lane; i < 16 * 8; i += 32) {
-            int r = r0 + i / 8, c = i % 8;
-            if (r < valid) {
-                uint4 x = *reinterpret_cast<const uint4*>(stage + swz<128>(r, c));
-                *reinterpret_cast<uint4*>(gout + (long)r * gstride + cg * 64 + c * 8) = x;
-            }
+    }
+    for (int it = lane; it < 64 * 8; it += 32) {
+        const int r = it >> 3, c = it & 7;
+        if (r < valid) {
+            const uint4 x = *reinterpret_cast<const uint4*>(zptr + swz<COLS * 2>(r, (col0 >> 3) + c));
+            *reinterpret_cast<uint4*>(gout + (long)r * gstride + col0 + c * 8) = x;
         }
-        __syncwarp();
-        (void)st;
     }
 }
 
@@ -108,14 +113,14 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
 
     unsigned char* ks_p = smem + L::ks;
     unsigned char* vs_p = smem + L::vs;
+    unsigned char* gs_p = smem + L::Gs;
     float* As = reinterpret_cast<float*>(smem + L::As);
     float* Xs = reinterpret_cast<float*>(smem + L::Xs);
-    float* Tm = reinterpret_cast<float*>(smem + L::Tm);
     float* s_gcs = reinterpret_cast<float*>(smem + L::vec);
     float* s_beta = s_gcs + 64;
     float* s_rstd = s_beta + 64;
     float* s_wsc = s_rstd + 64;
-    const uint32_t ks = smem_u32(ks_p), vs = smem_u32(vs_p);
+    const uint32_t ks = smem_u32(ks_p), vs = smem_u32(vs_p), gs = smem_u32(gs_p);
 
     load_tile_async<64, K, PREP_THREADS>(ks, k + (tok0 * H + h) * K, (long)H * K, valid, tid);
     load_tile_async<64, V, PREP_THREADS>(vs, v + (tok0 * H + h) * V, (long)H * V, valid, tid);
@@ -148,7 +153,7 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- l2norm of k rows (in place), rstd out
+    // ---- l2norm of k rows (in place), rstd out; v rows scaled by beta (in place)
     {
         constexpr int CPR = K / 8;                 // lanes per row
         constexpr int RPP = 32 / CPR > 0 ? 32 / CPR : 1;
@@ -181,6 +186,7 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
             }
         }
     }
+    scale_rows_inplace<V>(vs_p, s_beta, tid);
     __syncthreads();
 
     // ---- A = strictLower(beta_i (kn_i . kn_j) exp(gcs_i - gcs_j))
@@ -205,91 +211,74 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
         const int gq = lane >> 2, q = lane & 3;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
+            if (nt <= 2 * warp + 1) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                int i = r0 + gq + ((e >> 1) << 3);
-                int j = nt * 8 + q * 2 + (e & 1);
-                float val = 0.f;
-                if (i > j) val = s_beta[i] * acc[nt][e] * __expf(s_gcs[i] - s_gcs[j]);
-                As[i * A_LD + j] = val;
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = r0 + gq + hh * 8;
+                    const int j = nt * 8 + q * 2;
+                    float v0 = 0.f, v1 = 0.f;
+                    if (i > j) v0 = s_beta[i] * acc[nt][hh * 2] * __expf(s_gcs[i] - s_gcs[j]);
+                    if (i > j + 1) v1 = s_beta[i] * acc[nt][hh * 2 + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
+                    *reinterpret_cast<float2*>(&As[i * A_LD + j]) = make_float2(v0, v1);
+                }
             }
         }
     }
     __syncthreads();
+    // k rows -> kn beta e^{gcs} (the KK^T operand is no longer needed)
+    if (tid < 64) s_wsc[tid] = s_beta[tid] * __expf(s_gcs[tid]);
 
-    // ---- X = (I + A)^-1 : diagonal 16x16 blocks by forward substitution (one warp each)
+    // ---- X_dd = (I + A_dd)^-1 for the four 16x16 diagonal blocks: forward substitution, one warp each
     if (lane < 16) {
         const int d0 = warp * 16, cidx = lane;
         float xcol[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            float s = (i == cidx) ? 1.f : 0.f;
+            float sv = (i == cidx) ? 1.f : 0.f;
 #pragma unroll
-            for (int j = 0; j < i; ++j) s -= As[(d0 + i) * A_LD + d0 + j] * xcol[j];
-            xcol[i] = s;
+            for (int j = 0; j < i; ++j) sv -= As[(d0 + i) * A_LD + d0 + j] * xcol[j];
+            xcol[i] = sv;
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) Xs[(d0 + i) * A_LD + d0 + cidx] = xcol[i];
+        for (int i = 0; i < 16; ++i) Xs[(warp * 16 + i) * X_LD + cidx] = xcol[i];
     }
     __syncthreads();
-    // off-diagonal blocks, by distance from the diagonal: X_ij = -X_ii (sum_k A_ik X_kj)
-    for (int d = 1; d <= 3; ++d) {
-        const int nb = 4 - d;
-        for (int e = tid; e < nb * 256; e += PREP_THREADS) {
-            int blk = e >> 8, r = (e >> 4) & 15, cidx = e & 15;
-            int bi = blk + d, bj = blk;
-            float s = 0.f;
-            for (int kb = bj; kb < bi; ++kb) {
-#pragma unroll
-                for (int m = 0; m < 16; ++m)
-                    s += As[(bi * 16 + r) * A_LD + kb * 16 + m] * Xs[(kb * 16 + m) * A_LD + bj * 16 + cidx];
-            }
-            Tm[(blk * 16 + r) * 17 + cidx] = s;
-        }
-        __syncthreads();
-        for (int e = tid; e < nb * 256; e += PREP_THREADS) {
-            int blk = e >> 8, r = (e >> 4) & 15, cidx = e & 15;
-            int bi = blk + d, bj = blk;
-            float s = 0.f;
-#pragma unroll
-            for (int m = 0; m < 16; ++m) s -= Xs[(bi * 16 + r) * A_LD + bi * 16 + m] * Tm[(blk * 16 + m) * 17 + cidx];
-            Xs[(bi * 16 + r) * A_LD + bj * 16 + cidx] = s;
-        }
-        __syncthreads();
-    }
-
-    // ---- Ai (bf16, swizzled, over the A buffer); row scales for v and k
-    unsigned char* ai_p = smem + L::As;
-    {
-        int r = tid >> 1, half = tid & 1;
-#pragma unroll
-        for (int cch = 0; cch < 4; ++cch) {
-            int c0 = half * 32 + cch * 8;
-            uint32_t wv[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                int j0 = c0 + 2 * j;
-                float a0 = ((j0 >> 4) <= (r >> 4)) ? Xs[r * A_LD + j0] : 0.f;
-                float a1 = (((j0 + 1) >> 4) <= (r >> 4)) ? Xs[r * A_LD + j0 + 1] : 0.f;
-                if (j0 > r) a0 = 0.f;
-                if (j0 + 1 > r) a1 = 0.f;
-                wv[j] = pack_bf16(a0, a1);
-            }
-            // As and Ai alias: all reads of Xs above are from the other buffer, As itself is dead here
-            *reinterpret_cast<uint4*>(ai_p + swz<128>(r, c0 >> 3)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        }
-        if (tid < 64) s_wsc[tid] = s_beta[tid] * __expf(s_gcs[tid]);
-    }
-    __syncthreads();
-    scale_rows_inplace<V>(vs_p, s_beta, tid);
     scale_rows_inplace<K>(ks_p, s_wsc, tid);
+
+    // ---- G (bf16, A-operand layout): diagonal blocks X_dd, below-diagonal blocks -X_ii A_ij
+    for (int e = tid; e < 4 * 16 * 4; e += PREP_THREADS) {          // diagonal: (block, row, 4 columns)
+        const int d = e >> 6, r = (e >> 2) & 15, c4 = (e & 3) * 4;
+        const float* xr = &Xs[(d * 16 + r) * X_LD + c4];
+        const int row = d * 16 + r, col = d * 16 + c4;
+        *reinterpret_cast<uint2*>(gs_p + swz<128>(row, col >> 3) + (col & 7) * 2) =
+            make_uint2(pack_bf16(xr[0], xr[1]), pack_bf16(xr[2], xr[3]));
+    }
+    for (int e = tid; e < 6 * 16 * 4; e += PREP_THREADS) {          // below diagonal: (block pair, row, 4 columns)
+        const int blk = e >> 6, r = (e >> 2) & 15, c4 = (e & 3) * 4;
+        // block pairs (i, j): (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+        const int bi = blk < 1 ? 1 : (blk < 3 ? 2 : 3);
+        const int bj = blk - (bi == 1 ? 0 : (bi == 2 ? 1 : 3));
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+            const float xm = Xs[(bi * 16 + r) * X_LD + m];
+            const float4 av = *reinterpret_cast<const float4*>(&As[(bi * 16 + m) * A_LD + bj * 16 + c4]);
+            a0 -= xm * av.x; a1 -= xm * av.y; a2 -= xm * av.z; a3 -= xm * av.w;
+        }
+        const int row = bi * 16 + r, col = bj * 16 + c4;
+        *reinterpret_cast<uint2*>(gs_p + swz<128>(row, col >> 3) + (col & 7) * 2) =
+            make_uint2(pack_bf16(a0, a1), pack_bf16(a2, a3));
+    }
     __syncthreads();
 
-    // ---- u = Ai (v beta), w = Ai (kn beta e^{gcs})
-    const uint32_t ai = smem_u32(ai_p);
-    unsigned char* stage = smem + L::Xs;
-    tri_matmul_store<V>(ai, vs, stage, u + (tok0 * H + h) * V, (long)H * V, valid, warp, lane);
-    tri_matmul_store<K>(ai, ks, stage, w + (tok0 * H + h) * K, (long)H * K, valid, warp, lane);
+    // ---- [u | w] = block forward substitution, 64 columns per warp
+    constexpr int NCG = (K + V) / 64;
+    for (int cg = warp; cg < NCG; cg += 4) {
+        if (cg < V / 64)
+            solve_group<V>(gs, vs, vs_p, cg * 64, u + (tok0 * H + h) * V, (long)H * V, valid, lane);
+        else
+            solve_group<K>(gs, ks, ks_p, (cg - V / 64) * 64, w + (tok0 * H + h) * K, (long)H * K, valid, lane);
+    }
 }
 
 template <int K, int V>
