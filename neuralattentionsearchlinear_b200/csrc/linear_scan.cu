@@ -25,17 +25,23 @@ constexpr int SCAN_THREADS = 128;
 
 template <int K, int BV, bool GDN>
 struct ScanSmem {
-    static constexpr int w_bytes = GDN ? 64 * K * 2 : 0;
-    static constexpr int k_bytes = 64 * K * 2;
+    // Two 64xK tile buffers: [0] receives w_i, [1] receives k_i of the active chunk being processed; each is
+    // refilled for the next active chunk as soon as its product is done.  Small u / vector buffers alternate.
+    static constexpr int big_bytes = 64 * K * 2;
     static constexpr int u_bytes = 64 * BV * 2;
     static constexpr int vec_bytes = 2 * 64 * 4;
-    static constexpr int stage = w_bytes + k_bytes + u_bytes + vec_bytes;
-    static constexpr int sb = 2 * stage;                 // S as bf16 [K][BV]
+    static constexpr int big = 0;
+    static constexpr int ubuf = 2 * big_bytes;           // 2 x ([64][BV] bf16 + gcs[64] + rstd[64])
+    static constexpr int sb = ubuf + 2 * (u_bytes + vec_bytes);   // S as bf16 [K][BV]
     static constexpr int v2 = sb + K * BV * 2;           // scaled v_new [64][BV]
-    static constexpr int save = v2 + 64 * BV * 2;        // fp32 state backup (nats_block_size > 64 only)
-    static constexpr int total = save;
-    static constexpr int total_with_save = save + K * BV * 4;
+    static constexpr int meta = v2 + 64 * BV * 2;        // per chunk: g_last (float), active-list entry (int)
+    // then (nats_block_size > 64 only) the fp32 state backup [K][BV]
+    static int total(int NT, bool with_save) { return meta + NT * 8 + (with_save ? K * BV * 4 : 0); }
 };
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
 
 template <int K, int BV, bool GDN>
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -64,8 +70,32 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
 
     unsigned char* sb_p = smem + L::sb;
     unsigned char* v2_p = smem + L::v2;
-    float* save_p = reinterpret_cast<float*>(smem + L::save);
+    float* s_gl = reinterpret_cast<float*>(smem + L::meta);          // [NT] g_last per chunk
+    int* s_act = reinterpret_cast<int*>(smem + L::meta + NT * 4);    // [NT] bit 31: block selected; low bits: active list
+    float* save_p = reinterpret_cast<float*>(smem + L::meta + NT * 8);
     const uint32_t sb = smem_u32(sb_p), v2 = smem_u32(v2_p);
+
+    // ---- per-chunk metadata: decay total, selection flag, and the list of chunks that update the state
+    for (int c = tid; c < NT; c += SCAN_THREADS) {
+        const int last_tok = min(c * 64 + 63, T - 1);
+        s_gl[c] = gcs[((long)b * T + last_tok) * H + h];
+        s_act[c] = (sel_p[(long)(c / cpb) * sel_stride] != 0) ? (1 << 31) : 0;
+    }
+    __syncthreads();
+    __shared__ int s_nact;
+    if (tid == 0) {
+        int n = 0;
+        for (int c = 0; c < NT; ++c)
+            if (cpb > 1 || (s_act[c] < 0)) {
+                s_act[n] = (s_act[n] & (1 << 31)) | c;
+                ++n;
+            }
+        s_nact = n;
+    }
+    __syncthreads();
+    const int n_act = s_nact;
+    auto chunk_sel = [&](int c) -> bool { return s_act[c] < 0; };
+    auto act_chunk = [&](int i) -> int { return s_act[i] & 0x7FFFFFFF; };
 
     float S[MT][NTL][4];
     const int krow0 = warp * (K / 4);
@@ -84,35 +114,50 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
                 S[mt][nt][e] = val;
             }
 
-    auto is_active = [&](int c) -> bool { return cpb > 1 || sel_p[(long)(c / cpb) * sel_stride] != 0; };
-    auto issue_loads = [&](int c, int st) {
-        const int valid = min(64, T - c * 64);
-        const long tok0 = (long)b * T + (long)c * 64;
-        unsigned char* base = smem + st * L::stage;
-        if (GDN) load_tile_async<64, K, SCAN_THREADS>(smem_u32(base), w + (tok0 * H + h) * K, (long)H * K, valid, tid);
-        load_tile_async<64, K, SCAN_THREADS>(smem_u32(base + L::w_bytes), k + (tok0 * H + h) * K, (long)H * K, valid, tid);
-        load_tile_async<64, BV, SCAN_THREADS>(smem_u32(base + L::w_bytes + L::k_bytes), u + (tok0 * H + h) * V + v0,
-                                              (long)H * V, valid, tid);
-        float* vec = reinterpret_cast<float*>(base + L::w_bytes + L::k_bytes + L::u_bytes);
-        if (tid < 64) {
-            // padded rows repeat the last valid cumsum (their k, u rows are zero)
-            int r = min(tid, valid - 1);
-            vec[tid] = gcs[(tok0 + r) * H + h];
-            vec[64 + tid] = (krstd && tid < valid) ? krstd[(tok0 + tid) * H + h] : (krstd ? 0.f : 1.f);
+    // group A of the i-th active chunk: w tile -> big[0], u tile + gcs/rstd rows -> small buffer i & 1;
+    // group B: k tile -> big[1].  Each call commits exactly one group (possibly empty).
+    auto issue_a = [&](int i) {
+        if (i < n_act) {
+            const int c = act_chunk(i);
+            const int valid = min(64, T - c * 64);
+            const long tok0 = (long)b * T + (long)c * 64;
+            if (GDN) load_tile_async<64, K, SCAN_THREADS>(smem_u32(smem + L::big), w + (tok0 * H + h) * K, (long)H * K, valid, tid);
+            unsigned char* ub = smem + L::ubuf + (i & 1) * (L::u_bytes + L::vec_bytes);
+            load_tile_async<64, BV, SCAN_THREADS>(smem_u32(ub), u + (tok0 * H + h) * V + v0, (long)H * V, valid, tid);
+            const uint32_t vec = smem_u32(ub + L::u_bytes);
+            if (tid < 64) {
+                const bool okr = tid < valid;
+                cp_async4(vec + tid * 4, gcs + (tok0 + (okr ? tid : 0)) * H + h, okr ? 4 : 0);
+            } else if (krstd) {
+                const int r = tid - 64;
+                const bool okr = r < valid;
+                cp_async4(vec + 256 + r * 4, krstd + (tok0 + (okr ? r : 0)) * H + h, okr ? 4 : 0);
+            }
         }
         cp_async_commit();
     };
-
-    int next_active = 0;
-    while (next_active < NT && !is_active(next_active)) ++next_active;
-    if (next_active < NT) issue_loads(next_active, 0);
-    int st = 0;
+    auto issue_b = [&](int i) {
+        if (i < n_act) {
+            const int c = act_chunk(i);
+            const int valid = min(64, T - c * 64);
+            const long tok0 = (long)b * T + (long)c * 64;
+            load_tile_async<64, K, SCAN_THREADS>(smem_u32(smem + L::big + L::big_bytes), k + (tok0 * H + h) * K, (long)H * K,
+                                                 valid, tid);
+        }
+        cp_async_commit();
+    };
+    if (!krstd) {                          // Mamba2: no key normalisation
+        for (int i = tid; i < 2 * 64; i += SCAN_THREADS)
+            reinterpret_cast<float*>(smem + L::ubuf + (i / 64) * (L::u_bytes + L::vec_bytes) + L::u_bytes)[64 + (i % 64)] = 1.f;
+    }
+    issue_a(0);
+    int ia = 0;                            // index of the next active chunk
     float carry = 0.f, carry_save = 0.f, blk_g = 0.f;
     bool dirty = true;
 
     for (int c = 0; c < NT; ++c) {
         const int blk = c / cpb, sub = c % cpb;
-        const bool sel = sel_p[(long)blk * sel_stride] != 0;
+        const bool sel = chunk_sel(c) ;
         const bool active = cpb > 1 || sel;
         const bool may_carry = decay && (!trailing_quirk || blk < last_sel);
         if (cpb > 1 && sub == 0) {
@@ -141,22 +186,18 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
         }
         store_tile<K, BV, SCAN_THREADS>(sb_p, hout + ((((long)b * NT + c) * H + h) * K) * V + v0, V, K, tid);
         if (vsplit == 0 && tid == 0) carry_out[((long)b * NT + c) * H + h] = carry;
-        const int last_tok = min(c * 64 + 63, T - 1);
-        const float gl = gcs[((long)b * T + last_tok) * H + h];
+        const float gl = s_gl[c];
         blk_g += gl;
 
         if (active) {
-            cp_async_wait<0>();
+            // big[1] was last read by the k^T product of the previous active chunk, before the barriers above
+            issue_b(ia);
+            cp_async_wait<1>();            // group A of this chunk has landed (group B may still be in flight)
             __syncthreads();
-            // prefetch the next active chunk into the other stage
-            next_active = c + 1;
-            while (next_active < NT && !is_active(next_active)) ++next_active;
-            if (next_active < NT) issue_loads(next_active, st ^ 1);
-
-            unsigned char* base = smem + st * L::stage;
-            const uint32_t ws = smem_u32(base), ks = smem_u32(base + L::w_bytes);
-            const unsigned char* us_p = base + L::w_bytes + L::k_bytes;
-            const float* vec = reinterpret_cast<const float*>(base + L::w_bytes + L::k_bytes + L::u_bytes);
+            unsigned char* ub = smem + L::ubuf + (ia & 1) * (L::u_bytes + L::vec_bytes);
+            const uint32_t ws = smem_u32(smem + L::big), ks = smem_u32(smem + L::big + L::big_bytes);
+            const unsigned char* us_p = ub;
+            const float* vec = reinterpret_cast<const float*>(ub + L::u_bytes);
             const int r0 = warp * 16;
             float acc[NTL][4];
 #pragma unroll
@@ -164,7 +205,7 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
             if (GDN) {
-#pragma unroll 2
+#pragma unroll
                 for (int kk = 0; kk < K / 16; ++kk) {
                     uint32_t a[4];
                     load_a<K * 2>(ws, r0, kk * 16, lane, a);
@@ -179,10 +220,11 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
             }
             const float ec = __expf(carry);
             const int ra = r0 + gq, rb = ra + 8;
+            // rows past the end of a ragged last chunk have zero k/u; their (zero-filled) cumsum only has to stay finite
             float fa, fb;
             if (GDN) {
-                fa = vec[64 + ra] * __expf(gl - vec[ra]);
-                fb = vec[64 + rb] * __expf(gl - vec[rb]);
+                fa = vec[64 + ra] * __expf(fminf(gl - vec[ra], 80.f));
+                fb = vec[64 + rb] * __expf(fminf(gl - vec[rb], 80.f));
             } else {
                 fa = vec[64 + ra] * __expf(fminf(gl - vec[ra], 0.f));
                 fb = vec[64 + rb] * __expf(fminf(gl - vec[rb], 0.f));
@@ -196,7 +238,9 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
                 *reinterpret_cast<uint32_t*>(v2_p + swz<BV * 2>(ra, nt) + q * 4) = pack_bf16(va0 * fa, va1 * fa);
                 *reinterpret_cast<uint32_t*>(v2_p + swz<BV * 2>(rb, nt) + q * 4) = pack_bf16(vb0 * fb, vb1 * fb);
             }
-            __syncthreads();
+            cp_async_wait<0>();            // k tile of this chunk
+            __syncthreads();               // v2 and k visible; every warp is done with w, u of this chunk
+            issue_a(ia + 1);
             const float dec = __expf(gl + carry);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -221,7 +265,7 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
                 }
             }
             carry = 0.f;
-            st ^= 1;
+            ++ia;
             dirty = true;
         } else if (may_carry) {
             carry += gl;
@@ -237,6 +281,7 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
             dirty = true;
         }
     }
+    cp_async_wait<0>();
     if (ht) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -258,11 +303,16 @@ static int launch_scan(const void* k, const void* w, const void* u, const float*
                        cudaStream_t st) {
     using L = ScanSmem<K, BV, GDN>;
     auto kern = linear_scan_kernel<K, BV, GDN>;
-    const int smem = nbs > 64 ? L::total_with_save : L::total;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total_with_save);
+    const int NT = (T + 63) / 64;
+    const int smem = L::total(NT, nbs > 64);
+    if (smem > 227 * 1024) {
+        set_error("natsl_linear_fwd_h: T=%d needs %d B of shared memory for the per-chunk metadata (max %d)", T, smem,
+                  227 * 1024);
+        return NATSL_ERR_TOO_LARGE;
+    }
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
-        set_error("natsl_linear_fwd_h: cannot reserve %d B of shared memory (%s)", L::total_with_save,
-                  cudaGetErrorString(e));
+        set_error("natsl_linear_fwd_h: cannot reserve %d B of shared memory (%s)", smem, cudaGetErrorString(e));
         return NATSL_ERR_CUDA;
     }
     const int TN = (T + nbs - 1) / nbs;
