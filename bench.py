@@ -245,42 +245,47 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_step = ms_total / args.steps
     value = world * B * T / (ms_step * 1e-3)
 
-    # ---- per-kernel durations (CUDA events between the stages of the same step, same stream)
+    # ---- per-kernel durations: each stage launched `steps` times back to back on the same stream between two
+    # CUDA events (the queue stays full, so the events bracket device time, not host launch latency)
     names = ["tables", "attn_fwd", "gdn_prep", "scan_fwd_h", "out_fwd_o"]
-    acc = {n: 0.0 for n in names}
-    barrier()
-    for _ in range(args.steps):
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
-        ev[0].record(stream)
-        tb = nat.build_selection_tables(d["types"], T, nbs)
-        ev[1].record(stream)
-        _ops.attn_fwd(d["q"], d["k"], d["v"], tb, K ** -0.5, True)
-        ev[2].record(stream)
-        # the linear branch, stage by stage
-        gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
-        krs = torch.empty_like(gcs)
-        w = torch.empty(B, T, H, K, dtype=torch.bfloat16, device=dev)
-        u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
-        hbuf = torch.empty(B, T // 64, H, K, V, dtype=torch.bfloat16, device=dev)
-        carry = torch.empty(B, T // 64, H, dtype=torch.float32, device=dev)
-        ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
-        o = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
-        sp = stream.cuda_stream
-        _lib.call("natsl_gdn_chunk_prep", d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(), d["beta"].data_ptr(),
-                  _lib.DT_BF16, w.data_ptr(), u.data_ptr(), gcs.data_ptr(), krs.data_ptr(), B, T, H, K, V, 1, sp)
-        ev[3].record(stream)
-        _lib.call("natsl_linear_fwd_h", _lib.RULE_GDN, d["k"].data_ptr(), w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
-                  krs.data_ptr(), tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
-                  hbuf.data_ptr(), carry.data_ptr(), ht.data_ptr(), B, T, H, H, K, V, nbs, _lib.FLAG_DECAY_SKIPPED, sp)
-        ev[4].record(stream)
-        _lib.call("natsl_linear_fwd_o", _lib.RULE_GDN, d["q"].data_ptr(), d["k"].data_ptr(), w.data_ptr(), u.data_ptr(),
-                  gcs.data_ptr(), krs.data_ptr(), hbuf.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V,
-                  K ** -0.5, 1, sp)
-        ev[5].record(stream)
+    NT = T // 64
+    tb = nat.build_selection_tables(d["types"], T, nbs)
+    gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    krs = torch.empty_like(gcs)
+    w = torch.empty(B, T, H, K, dtype=torch.bfloat16, device=dev)
+    u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
+    hbuf = torch.empty(B, NT, H, K, V, dtype=torch.bfloat16, device=dev)
+    carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)
+    ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
+    o = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
+    sp = stream.cuda_stream
+    stages = {
+        "tables": lambda: nat.build_selection_tables(d["types"], T, nbs),
+        "attn_fwd": lambda: _ops.attn_fwd(d["q"], d["k"], d["v"], tb, K ** -0.5, True),
+        "gdn_prep": lambda: _lib.call("natsl_gdn_chunk_prep", d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(),
+                                      d["beta"].data_ptr(), _lib.DT_BF16, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
+                                      krs.data_ptr(), B, T, H, K, V, 1, sp),
+        "scan_fwd_h": lambda: _lib.call("natsl_linear_fwd_h", _lib.RULE_GDN, d["k"].data_ptr(), w.data_ptr(), u.data_ptr(),
+                                        gcs.data_ptr(), krs.data_ptr(), tb.types_i.data_ptr(), tb.indices.data_ptr(),
+                                        tb.n_blocks.data_ptr(), None, hbuf.data_ptr(), carry.data_ptr(), ht.data_ptr(),
+                                        B, T, H, H, K, V, nbs, _lib.FLAG_DECAY_SKIPPED, sp),
+        "out_fwd_o": lambda: _lib.call("natsl_linear_fwd_o", _lib.RULE_GDN, d["q"].data_ptr(), d["k"].data_ptr(),
+                                       w.data_ptr(), u.data_ptr(), gcs.data_ptr(), krs.data_ptr(), hbuf.data_ptr(),
+                                       carry.data_ptr(), o.data_ptr(), B, T, H, K, V, K ** -0.5, 1, sp),
+    }
+    kernel_ms = {}
+    for n in names:                      # in pipeline order, so every stage sees valid inputs
+        stages[n]()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            stages[n]()
+        ev1.record(stream)
         torch.cuda.synchronize(dev)
-        for i, n in enumerate(names):
-            acc[n] += ev[i].elapsed_time(ev[i + 1])
-    kernel_ms = {n: acc[n] / args.steps for n in names}
+        kernel_ms[n] = ev0.elapsed_time(ev1) / args.steps
+    if _lib.load().natsl_device_status() != 0:
+        raise RuntimeError("a kernel reported a failed bounded wait: " + _lib.load().natsl_last_error().decode())
 
     # ---- end to end: host (pinned) inputs -> device -> op -> host outputs, every step
     h2d = sum(t.numel() * t.element_size() for t in pinned.values())

@@ -114,6 +114,13 @@ int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, co
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
                        int V, float scale, int use_l2norm, void* stream);
 
+/* Output mixing: y = (x1 rstd1 w1 a + x2 rstd2 w2 b) * g * sigmoid(g) over rows of D (64/128/256) bf16
+ * elements; xw [rows,2] = (a, b) or NULL; w1, w2 [D] or NULL; activation 0 = swish, 1 = sigmoid.
+ * Replaces: FusedMultiInputRMSNormGated forward, src/nats/modules/fused_norm_gate.py:38-182, 1354-1429. */
+int natsl_norm_gate_mix(const void* x1, const void* x2, const void* g, const void* xw, int xw_dtype, const void* w1,
+                        const void* w2, int w_dtype, void* y, long rows, int D, float eps, int activation,
+                        void* stream);
+
 /* Gated-delta-rule branch forward (prep -> recurrence -> output) that allocates nothing and asks
  * the caller for no intermediate buffers: they live in a fixed NATSL_NOALLOC_SCRATCH_BYTES array
  * inside the library, one per GPU, shared by all calls (overlapping calls on one GPU race; the

@@ -14,4 +14,7 @@ from .mixed_attn_mamba import (  # noqa: F401
     nats_mixed_attn_mamba_chunk_inference,
 )
 
+from .natsl_attn_gdn import NeuralAttentionSearchLinearAttnGDN  # noqa: F401
+from .natsl_attn_mamba2 import NeuralAttentionSearchLinearAttnMamba  # noqa: F401
+
 __version__ = "0.1.0"

@@ -1,0 +1,99 @@
+// Output mixing of the hybrid layer: two-input RMSNorm with per-row mixing weights and a swish gate,
+//   y = (x1 * rstd1 * w1 * a + x2 * rstd2 * w2 * b) * g * sigmoid(g),   rstd = 1 / sqrt(mean(x^2) + eps)
+// (x1 = linear-branch output, x2 = softmax-branch output, (a, b) = learned per-(token, head) weights).
+// Replaces the forward of FusedMultiInputRMSNormGated, src/nats/modules/fused_norm_gate.py:38-182
+// (module :1354-1429).  Pure bandwidth: one warp per row of D elements, 16-byte loads and stores, fp32 math.
+#include "common.cuh"
+#include "../../include/natsl_b200.h"
+
+namespace natsl {
+
+__device__ __forceinline__ float load_scalar(const void* p, int dtype, long i) {
+    return dtype == NATSL_DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(256)
+norm_gate_mix_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __restrict__ x2,
+                     const __nv_bfloat16* __restrict__ g, const void* __restrict__ xw, int xw_dtype,
+                     const void* __restrict__ w1, const void* __restrict__ w2, int w_dtype,
+                     __nv_bfloat16* __restrict__ y, long rows, float eps, int activation) {
+    constexpr int EPL = D / 32;                       // elements per lane (2, 4 or 8)
+    const int lane = threadIdx.x & 31;
+    const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const long base = row * D + lane * EPL;
+    float a[EPL], b[EPL], gg[EPL];
+    auto load = [&](const __nv_bfloat16* p, float* out) {
+        if (EPL == 8) {
+            uint4 v = *reinterpret_cast<const uint4*>(p + base);
+            const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { float2 f = unpack_bf16(u[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+        } else if (EPL == 4) {
+            uint2 v = *reinterpret_cast<const uint2*>(p + base);
+            float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y);
+            out[0] = f0.x; out[1] = f0.y; out[2] = f1.x; out[3] = f1.y;
+        } else {
+            float2 f = unpack_bf16(*reinterpret_cast<const uint32_t*>(p + base));
+            out[0] = f.x; out[1] = f.y;
+        }
+    };
+    load(x1, a);
+    load(x2, b);
+    load(g, gg);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) { s1 += a[i] * a[i]; s2 += b[i] * b[i]; }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    const float r1 = rsqrtf(s1 / D + eps), r2 = rsqrtf(s2 / D + eps);
+    float m1 = 1.f, m2 = 1.f;
+    if (xw) { m1 = load_scalar(xw, xw_dtype, row * 2); m2 = load_scalar(xw, xw_dtype, row * 2 + 1); }
+    float out[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        const int d = lane * EPL + i;
+        const float ww1 = w1 ? load_scalar(w1, w_dtype, d) : 1.f, ww2 = w2 ? load_scalar(w2, w_dtype, d) : 1.f;
+        const float v = a[i] * r1 * ww1 * m1 + b[i] * r2 * ww2 * m2;
+        const float sg = 1.f / (1.f + __expf(-gg[i]));
+        out[i] = activation == 1 ? v * sg : v * gg[i] * sg;
+    }
+    if (EPL == 8) {
+        *reinterpret_cast<uint4*>(y + base) = make_uint4(pack_bf16(out[0], out[1]), pack_bf16(out[2], out[3]),
+                                                         pack_bf16(out[4 % EPL], out[5 % EPL]), pack_bf16(out[6 % EPL], out[7 % EPL]));
+    } else if (EPL == 4) {
+        *reinterpret_cast<uint2*>(y + base) = make_uint2(pack_bf16(out[0], out[1]), pack_bf16(out[2 % EPL], out[3 % EPL]));
+    } else {
+        *reinterpret_cast<uint32_t*>(y + base) = pack_bf16(out[0], out[1]);
+    }
+}
+
+}  // namespace natsl
+
+extern "C" int natsl_norm_gate_mix(const void* x1, const void* x2, const void* g, const void* xw, int xw_dtype,
+                                   const void* w1, const void* w2, int w_dtype, void* y, long rows, int D, float eps,
+                                   int activation, void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(x1 && x2 && g && y, NATSL_ERR_NULL, "natsl_norm_gate_mix: null pointer");
+    NATSL_REQUIRE(rows > 0, NATSL_ERR_BAD_SHAPE, "natsl_norm_gate_mix: empty input");
+    NATSL_REQUIRE(activation == 0 || activation == 1, NATSL_ERR_UNSUPPORTED, "natsl_norm_gate_mix: activation 0 (swish) or 1 (sigmoid)");
+    NATSL_REQUIRE((xw_dtype == NATSL_DT_BF16 || xw_dtype == NATSL_DT_F32) && (w_dtype == NATSL_DT_BF16 || w_dtype == NATSL_DT_F32),
+                  NATSL_ERR_UNSUPPORTED, "natsl_norm_gate_mix: weights must be bf16 or f32");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int wpb = 8;
+    const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+#define NATSL_NG(DD) norm_gate_mix_kernel<DD><<<grid, wpb * 32, 0, st>>>( \
+        reinterpret_cast<const __nv_bfloat16*>(x1), reinterpret_cast<const __nv_bfloat16*>(x2), \
+        reinterpret_cast<const __nv_bfloat16*>(g), xw, xw_dtype, w1, w2, w_dtype, reinterpret_cast<__nv_bfloat16*>(y), rows, eps, activation)
+    if (D == 64) NATSL_NG(64);
+    else if (D == 128) NATSL_NG(128);
+    else if (D == 256) NATSL_NG(256);
+    else {
+        set_error("natsl_norm_gate_mix: unsupported row width D=%d (64, 128 or 256)", D);
+        return NATSL_ERR_UNSUPPORTED;
+    }
+#undef NATSL_NG
+    return check_launch("natsl_norm_gate_mix");
+}

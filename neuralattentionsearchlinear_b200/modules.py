@@ -1,0 +1,136 @@
+"""Small host-side modules the NAtSL layers are built from, restated in plain PyTorch (the reference
+takes them from flash-linear-attention's Triton modules): RMSNorm, L2Norm, ShortConvolution,
+mean pooling, the hard selection, and the two-input gated norm whose forward runs the CUDA kernel
+``natsl_norm_gate_mix``.  Parameter names match the reference so state dicts load unchanged.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib
+from .nats_util import current_stream_ptr
+
+
+class RMSNorm(nn.Module):
+    """y = x * rsqrt(mean(x^2) + eps) * weight (call sites: src/nats/layers/natsl_attn_gdn.py:233-235)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+
+    def forward(self, x):
+        xf = x.float()
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()
+        return y.to(x.dtype)
+
+
+class L2Norm(nn.Module):
+    """y = x * rsqrt(sum(x^2) + eps) (src/nats/layers/natsl_attn_mamba2.py:193-194)."""
+
+    def __init__(self, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+
+    def forward(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + self.eps)).to(x.dtype)
+
+
+class ShortConvolution(nn.Conv1d):
+    """Depthwise causal conv1d over time followed by SiLU; returns (y, final_state)
+    (src/nats/layers/natsl_attn_gdn.py:329-348, 430-447).  x: [B, T, D]."""
+
+    def __init__(self, hidden_size: int, kernel_size: int, bias: bool = False, activation: Optional[str] = 'silu'):
+        super().__init__(hidden_size, hidden_size, kernel_size, groups=hidden_size, bias=bias, padding=kernel_size - 1)
+        self.hidden_size = hidden_size
+        self.activation = activation
+
+    def forward(self, x, cache=None, output_final_state=False, cu_seqlens=None):
+        if cu_seqlens is not None:
+            raise NotImplementedError("variable-length batches are not built")
+        B, T, D = x.shape
+        W = self.kernel_size[0]
+        xt = x.transpose(1, 2)
+        if cache is not None:
+            xt = torch.cat([cache.to(xt.dtype), xt], -1)
+            y = F.conv1d(xt, self.weight, self.bias, groups=D)[..., -T:]
+        else:
+            y = F.conv1d(xt, self.weight, self.bias, padding=W - 1, groups=D)[..., :T]
+        final = None
+        if output_final_state:
+            final = F.pad(xt, (max(0, W - xt.shape[-1]), 0))[..., -W:]
+        if self.activation in ('silu', 'swish'):
+            y = F.silu(y)
+        return y.transpose(1, 2).contiguous(), final
+
+
+def mean_pooling(x: torch.Tensor, chunk_size: int, cu_seqlens=None) -> torch.Tensor:
+    """Per-chunk mean over time of x [B, T, H, D] -> [B, cdiv(T, chunk), H, D], fp32 sum divided by the number
+    of tokens in the chunk (src/nats/ops/utils/pooling.py:51-57, call natsl_attn_gdn.py:412-416)."""
+    if cu_seqlens is not None:
+        raise NotImplementedError("variable-length batches are not built")
+    B, T, H, D = x.shape
+    NT = -(-T // chunk_size)
+    pad = NT * chunk_size - T
+    xf = F.pad(x.float(), (0, 0, 0, 0, 0, pad)).view(B, NT, chunk_size, H, D).sum(2)
+    cnt = torch.full((NT,), float(chunk_size), device=x.device)
+    if pad:
+        cnt[-1] = chunk_size - pad
+    return (xf / cnt.view(1, NT, 1, 1)).to(x.dtype)
+
+
+def hard_softmax(logits: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """One-hot of the first maximum of softmax(logits) with a straight-through gradient
+    (src/nats/layers/natsl_attn_gdn.py:47-61)."""
+    y_soft = logits.softmax(dim)
+    index = y_soft.max(dim, keepdim=True)[1]
+    y_hard = torch.zeros_like(logits, memory_format=torch.legacy_contiguous_format).scatter_(dim, index, 1.0)
+    return y_hard - y_soft.detach() + y_soft
+
+
+class FusedMultiInputRMSNormGated(nn.Module):
+    """y = (rms(x1) w1 a + rms(x2) w2 b) * g * sigmoid(g)  (src/nats/modules/fused_norm_gate.py:1354-1429).
+    Forward only: runs ``natsl_norm_gate_mix`` on CUDA bf16 inputs."""
+
+    def __init__(self, hidden_size: int, elementwise_affine: bool = True, eps: float = 1e-5, activation: str = 'swish',
+                 device=None, dtype=None):
+        super().__init__()
+        if activation not in ('swish', 'silu', 'sigmoid'):
+            raise ValueError(f"Unsupported activation: {activation}")
+        self.hidden_size, self.eps, self.activation = hidden_size, eps, activation
+        if elementwise_affine:
+            self.weight1 = nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
+            self.weight2 = nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
+        else:
+            self.register_parameter("weight1", None)
+            self.register_parameter("weight2", None)
+
+    def forward(self, x1, x2, g, x_weights_after_norm=None, residual=None, prenorm=False, residual_in_fp32=False):
+        if residual is not None or prenorm:
+            raise NotImplementedError("residual / prenorm variants are not built")
+        D = self.hidden_size
+        if not (x1.is_cuda and x1.dtype == torch.bfloat16):
+            raise TypeError("FusedMultiInputRMSNormGated needs CUDA bf16 inputs (there is no CPU path)")
+        shape = x1.shape
+        x1c, x2c, gc = (t.contiguous().view(-1, D) for t in (x1, x2, g.to(x1.dtype)))
+        rows = x1c.shape[0]
+        y = torch.empty_like(x1c)
+        xw = None
+        if x_weights_after_norm is not None:
+            xw = x_weights_after_norm.contiguous().view(-1, 2)
+            if xw.dtype not in (torch.bfloat16, torch.float32):
+                xw = xw.float()
+            assert xw.shape[0] == rows
+        w1, w2 = self.weight1, self.weight2
+        if w1 is not None and w1.dtype not in (torch.bfloat16, torch.float32):
+            w1, w2 = w1.float(), w2.float()
+        code = lambda t: _lib.DT_BF16 if (t is not None and t.dtype == torch.bfloat16) else _lib.DT_F32
+        _lib.call("natsl_norm_gate_mix", x1c.data_ptr(), x2c.data_ptr(), gc.data_ptr(), _lib.ptr(xw), code(xw),
+                  _lib.ptr(w1), _lib.ptr(w2), code(w1), y.data_ptr(), rows, D, float(self.eps),
+                  1 if self.activation == 'sigmoid' else 0, current_stream_ptr(x1.device))
+        return y.view(shape)
