@@ -75,6 +75,14 @@ int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* t
                    const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int DK,
                    int DV, int nbs, float scale, int flags, void* stream);
 
+/* Same, for a window of queries: q, o [B,Tq,HQ,.], lse [B,Tq,HQ] are the tokens [q_off, q_off+Tq) of the
+ * T-key sequence the tables describe (q_off a multiple of 128 and of nbs).  Used by the sequence-parallel
+ * path, where the keys are [gathered selected blocks of earlier ranks | own segment].  No reference
+ * counterpart (the reference has no sequence parallelism). */
+int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t* types_i, const int32_t* indices,
+                      const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int Tq, int q_off, int HQ,
+                      int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream);
+
 /* Debug/parity: dense 0/1 mask [B,HQ,T,T] (uint8) from the same tile walk as natsl_attn_fwd.
  * Counterpart: store_msk=True of the reference kernel, src/nats/ops/attns/attns.py:214-217,
  * 321-323, 1495-1498. */
@@ -113,6 +121,21 @@ int natsl_linear_fwd_h(int rule, const void* k, const void* w, const void* u, co
 int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, const void* u, const float* gcs,
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
                        int V, float scale, int use_l2norm, void* stream);
+
+/* Sequence-parallel helpers (no reference counterpart; the recurrence they split is
+ * src/nats/ops/mamba/chunk_h.py:139-218).
+ * natsl_sp_segment_decay: a [B,H] = exp(total log decay the carried state sees over this segment);
+ *   trail [B,H] = exp(log decay of the skipped blocks after the last selected block).
+ * natsl_sp_state_combine: h_in [B,H,K,V] = sum_{r<rank} (prod_{r<r'<rank} a[r']) S[r] from the all-gathered
+ *   a [world,B,H], S [world,B,H,K,V] (fp32).
+ * natsl_pack_selected_blocks: packed [B, cap_blocks*nbs, H, D] <- the selected blocks (column `op`) of
+ *   x [B,T,H,D] bf16 in index-table order, per head. */
+int natsl_sp_segment_decay(const float* gcs, const int32_t* types_i, float* a, float* trail, int B, int T, int H,
+                           int HN, int nbs, int flags, void* stream);
+int natsl_sp_state_combine(const float* a, const float* S, float* h_in, int rank, int world, int B, int H, int K, int V,
+                           void* stream);
+int natsl_pack_selected_blocks(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
+                               int T, int H, int HN, int D, int nbs, int op, int cap_blocks, void* stream);
 
 /* Output mixing: y = (x1 rstd1 w1 a + x2 rstd2 w2 b) * g * sigmoid(g) over rows of D (64/128/256) bf16
  * elements; xw [rows,2] = (a, b) or NULL; w1, w2 [D] or NULL; activation 0 = swish, 1 = sigmoid.

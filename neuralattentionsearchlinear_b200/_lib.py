@@ -23,6 +23,10 @@ PROTOTYPES = {
     "natsl_device_status": [],
     "natsl_build_tables": [_p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "natsl_attn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_attn_fwd_ex": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_sp_segment_decay": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_sp_state_combine": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_pack_selected_blocks": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "natsl_attn_dense_mask": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "natsl_chunk_local_cumsum": [_p, _p, _i, _i, _i, _p],
     "natsl_gdn_chunk_prep": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],

@@ -14,19 +14,22 @@ def _need(cond: bool, msg: str, exc=ValueError):
         raise exc(msg)
 
 
-def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mma_sync: bool = False):
-    """q [B,T,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16 -> (o [B,T,HQ,DV] bf16, lse [B,T,HQ] fp32 base-2)."""
+def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mma_sync: bool = False, q_off: int = 0):
+    """q [B,Tq,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16 -> (o [B,Tq,HQ,DV] bf16, lse [B,Tq,HQ] fp32 base-2).
+    The queries are the tokens [q_off, q_off+Tq) of the T-key sequence (q_off = 0 and Tq = T normally)."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "softmax branch needs bf16 q/k/v", TypeError)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    B, T, HQ, DK = q.shape
-    HKV, DV = k.shape[2], v.shape[3]
+    B, Tq, HQ, DK = q.shape
+    T, HKV, DV = k.shape[1], k.shape[2], v.shape[3]
+    _need(tables.T == T, f"tables were built for T={tables.T}, keys have T={T}")
     HN = tables.types_i.shape[2]
-    o = torch.empty(B, T, HQ, DV, dtype=BF16, device=q.device)
-    lse = torch.empty(B, T, HQ, dtype=torch.float32, device=q.device)
+    o = torch.empty(B, Tq, HQ, DV, dtype=BF16, device=q.device)
+    lse = torch.empty(B, Tq, HQ, dtype=torch.float32, device=q.device)
     flags = (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_ATTN_MMA_SYNC if mma_sync else 0)
-    _lib.call("natsl_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
+    _lib.call("natsl_attn_fwd_ex", q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
               tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(),
-              B, T, HQ, HKV, HN, DK, DV, tables.nats_block_size, float(scale), flags, current_stream_ptr(q.device))
+              B, T, Tq, int(q_off), HQ, HKV, HN, DK, DV, tables.nats_block_size, float(scale), flags,
+              current_stream_ptr(q.device))
     return o, lse
 
 
@@ -44,8 +47,9 @@ def attn_dense_mask(tables: SelectionTables, HQ: int, own_chunk: bool) -> torch.
 
 def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool,
                use_l2norm: bool, output_final_state: bool, trailing_quirk: bool = True,
-               return_intermediates: bool = False):
-    """Linear branch forward (prep -> state recurrence -> output).  Returns (o, ht, inter)."""
+               return_intermediates: bool = False, skip_out: bool = False):
+    """Linear branch forward (prep -> state recurrence -> output).  Returns (o, ht, inter); with ``skip_out``
+    only the recurrence runs (o is None)."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "linear branch needs bf16 q/k/v", TypeError)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
@@ -79,9 +83,11 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krstd),
               tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
               h.data_ptr(), carry.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, flags, st)
+    inter = dict(w=w, u=u, gcs=gcs, k_rstd=krstd, h=h, carry=carry) if return_intermediates else None
+    if skip_out:
+        return None, ht, inter
     o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
     _lib.call("natsl_linear_fwd_o", rule, q.data_ptr(), k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(),
               _lib.ptr(krstd), h.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V, float(scale),
               int(use_l2norm and rule == _lib.RULE_GDN), st)
-    inter = dict(w=w, u=u, gcs=gcs, k_rstd=krstd, h=h, carry=carry) if return_intermediates else None
     return o, ht, inter

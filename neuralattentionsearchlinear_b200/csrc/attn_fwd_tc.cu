@@ -68,8 +68,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const int* __restrict__ types_i,
                    const int* __restrict__ indices, const int* __restrict__ attn_n_iters,
-                   __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int HQ, int HKV, int HN, int TN,
-                   int nbs, float scale_log2, int own_chunk, int* status) {
+                   __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int Tq, int q_off, int HQ, int HKV,
+                   int HN, int TN, int nbs, float scale_log2, int own_chunk, int* status) {
+    // T = number of keys (and the length the tables were built for); the Tq queries are the tokens
+    // [q_off, q_off + Tq) of that sequence (q_off = 0, Tq = T except under sequence parallelism).
     using L = TcSmem<DK, DV>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -78,8 +80,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (tid == 0) atomicExch(status, 2);
         return;
     }
-    const int NTq = gridDim.x;
-    const int it = NTq - 1 - blockIdx.x;              // heaviest tiles first
+    const int NTq = (T + ATT_BM - 1) / ATT_BM;
+    const int it = q_off / ATT_BM + ((int)gridDim.x - 1 - (int)blockIdx.x);     // heaviest tiles first
     const int hq = blockIdx.y, b = blockIdx.z;
     const int hkv = hq / (HQ / HKV), hn = hq / (HQ / HN);
     const int q0 = it * ATT_BM;
@@ -130,7 +132,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             prefetch_tensormap(&map_v);
             mbar_expect_tx(bar_q, 128 * DK * 2);
 #pragma unroll
-            for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0, b, bar_q);
+            for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
         }
         // K and V rings advance independently: whichever ring has a free stage gets its next tile.
         int jk = 0, jv = 0, idle = 0;
@@ -357,17 +359,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         make_uint4(w4[0], w4[1], w4[2], w4[3]);
                 }
             }
-            if (t < T) lse[((long)b * T + t) * HQ + hq] = has ? m_used + log2f(l) : 0.f;
+            if (t - q_off < Tq) lse[((long)b * Tq + (t - q_off)) * HQ + hq] = has ? m_used + log2f(l) : 0.f;
         }
         // every softmax warp reaches this barrier, also after a failed wait (no warp may be left behind)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ok) {
             constexpr int CPR = DV / 8;
-            __nv_bfloat16* obase = o + (((long)b * T + q0) * HQ + hq) * DV;
+            __nv_bfloat16* obase = o + (((long)b * Tq + (q0 - q_off)) * HQ + hq) * DV;
             const int st_tid = tid - 64;
             for (int i = st_tid; i < 128 * CPR; i += 128) {
                 const int r = i / CPR, cch = i % CPR;
-                if (q0 + r < T) {
+                if (q0 - q_off + r < Tq) {
                     const uint4 x = *reinterpret_cast<const uint4*>(stage + swz<DV * 2>(r, cch));
                     *reinterpret_cast<uint4*>(obase + (long)r * HQ * DV + cch * 8) = x;
                 }
@@ -382,8 +384,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int DK, int DV>
 static int launch_attn_tc(const void* q, const void* k, const void* v, const int* types_i, const int* indices,
-                          const int* n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int nbs,
-                          float scale, int own_chunk, cudaStream_t st) {
+                          const int* n_iters, void* o, float* lse, int B, int T, int Tq, int q_off, int HQ, int HKV,
+                          int HN, int nbs, float scale, int own_chunk, cudaStream_t st) {
     using L = TcSmem<DK, DV>;
     auto kern = attn_fwd_tc_kernel<DK, DV>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
@@ -392,38 +394,47 @@ static int launch_attn_tc(const void* q, const void* k, const void* v, const int
         return NATSL_ERR_CUDA;
     }
     CUtensorMap mq, mk, mv;
-    int rc = encode_bthd_map(&mq, q, B, T, HQ, DK, 128, "natsl_attn_fwd(q)");
+    int rc = encode_bthd_map(&mq, q, B, Tq, HQ, DK, 128, "natsl_attn_fwd(q)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T, HKV, DK, 64, "natsl_attn_fwd(k)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T, HKV, DV, 64, "natsl_attn_fwd(v)");
     int* status = nullptr;
     if (rc == NATSL_OK) rc = status_word_ptr(&status);
     if (rc != NATSL_OK) return rc;
-    const int NTq = (T + ATT_BM - 1) / ATT_BM, TN = (T + nbs - 1) / nbs;
+    const int NTq = (Tq + ATT_BM - 1) / ATT_BM, TN = (T + nbs - 1) / nbs;
     dim3 grid(NTq, HQ, B);
     kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, types_i, indices, n_iters, reinterpret_cast<__nv_bfloat16*>(o),
-                                             lse, T, HQ, HKV, HN, TN, nbs, scale * 1.44269504f, own_chunk, status);
+                                             lse, T, Tq, q_off, HQ, HKV, HN, TN, nbs, scale * 1.44269504f, own_chunk,
+                                             status);
     return check_launch("natsl_attn_fwd");
 }
 
 }  // namespace natsl
 
-extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,
-                              const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B, int T,
-                              int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
+extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t* types_i,
+                                 const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B,
+                                 int T, int Tq, int q_off, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
+                                 int flags, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(q && k && v && types_i && indices && attn_n_iters && o && lse, NATSL_ERR_NULL,
                   "natsl_attn_fwd: null pointer");
     NATSL_REQUIRE(B > 0 && T > 0 && HQ > 0 && HKV > 0 && HN > 0 && HQ % HKV == 0 && HQ % HN == 0, NATSL_ERR_BAD_SHAPE,
                   "natsl_attn_fwd: bad shape B=%d T=%d HQ=%d HKV=%d HN=%d", B, T, HQ, HKV, HN);
+    NATSL_REQUIRE(Tq > 0 && q_off >= 0 && q_off + Tq <= T, NATSL_ERR_BAD_SHAPE,
+                  "natsl_attn_fwd: queries [%d, %d) do not lie inside the %d keys", q_off, q_off + Tq, T);
     NATSL_REQUIRE(HQ <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_attn_fwd: B and HQ must be <= 65535");
     NATSL_REQUIRE(nbs >= 64 && nbs % 64 == 0, NATSL_ERR_UNSUPPORTED,
                   "natsl_attn_fwd: nats_block_size must be a multiple of 64 (got %d)", nbs);
+    NATSL_REQUIRE(q_off % 128 == 0 && q_off % nbs == 0, NATSL_ERR_UNSUPPORTED,
+                  "natsl_attn_fwd: the query offset must be a multiple of 128 and of nats_block_size (got %d)", q_off);
     const int own = (flags & NATSL_FLAG_ATTN_OWN_CHUNK) ? 1 : 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (flags & NATSL_FLAG_ATTN_MMA_SYNC)
+    if (flags & NATSL_FLAG_ATTN_MMA_SYNC) {
+        NATSL_REQUIRE(q_off == 0 && Tq == T, NATSL_ERR_UNSUPPORTED,
+                      "natsl_attn_fwd: the mma.sync comparison kernel has no query offset");
         return attn_fwd_mma_sync(q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, DK, DV, nbs, scale,
                                  own, st);
-#define NATSL_ATT_ARGS q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, nbs, scale, own, st
+    }
+#define NATSL_ATT_ARGS q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, Tq, q_off, HQ, HKV, HN, nbs, scale, own, st
     if (DK == 64 && DV == 64) return launch_attn_tc<64, 64>(NATSL_ATT_ARGS);
     if (DK == 64 && DV == 128) return launch_attn_tc<64, 128>(NATSL_ATT_ARGS);
     if (DK == 128 && DV == 64) return launch_attn_tc<128, 64>(NATSL_ATT_ARGS);
@@ -431,4 +442,11 @@ extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const
 #undef NATSL_ATT_ARGS
     set_error("natsl_attn_fwd: unsupported head dims DK=%d DV=%d (each 64 or 128)", DK, DV);
     return NATSL_ERR_UNSUPPORTED;
+}
+
+extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,
+                              const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B, int T,
+                              int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
+    return natsl_attn_fwd_ex(q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, T, 0, HQ, HKV, HN, DK, DV, nbs, scale,
+                             flags, stream);
 }
