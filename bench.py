@@ -353,6 +353,84 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------- long-context Mamba2 (optional)
+MAMBA_LONG = dict(T=65536, H=32, K=128, V=64, nbs=256, p_attn=0.10)
+
+
+def run_mamba_long(args, rank: int, world: int, local_rank: int):
+    """NAtSL-Mamba2 hybrid layer, B=1, T=65536, H=32, state dim 128, head dim 64, block 256, ~10 % softmax blocks,
+    sequence-parallel over the ranks (strong scaling: the sequence is split, one contiguous segment per rank)."""
+    import neuralattentionsearchlinear_b200 as nat
+    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200.sequence_parallel import nats_mixed_attn_mamba_sp
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    c = MAMBA_LONG
+    T, H, K, V, nbs = c["T"], c["H"], c["K"], c["V"], c["nbs"]
+    T_loc = T // world
+    gen = torch.Generator().manual_seed(4000 + rank)
+    x = torch.randn(1, T_loc, H, V, generator=gen)
+    dt = torch.nn.functional.softplus(torch.randn(1, T_loc, H, generator=gen) - 2.0)
+    A = -torch.exp(torch.rand(H, generator=torch.Generator().manual_seed(4)) * torch.log(torch.tensor(16.0)))
+    k = torch.randn(1, T_loc, H, K, generator=gen) * K ** -0.5
+    q = torch.randn(1, T_loc, H, K, generator=gen) * K ** -0.5
+    v = (x * dt[..., None]).bfloat16().to(dev)
+    g = (A.view(1, 1, H) * dt).to(dev)
+    q, k = q.bfloat16().to(dev), k.bfloat16().to(dev)
+    logits = torch.randn(1, T_loc // nbs, H, 2, generator=gen)
+    logits[..., 0] += (2.0 ** 0.5) * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(c["p_attn"])).item()
+    types = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
+    if rank == world - 1:
+        types[:, -1] = 1
+    types = types.to(dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def step():
+        if world == 1:
+            return nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5, nats_block_size=nbs,
+                                             ops_for_incomplete_chunks="all", output_final_state_mamba=True,
+                                             decay_for_non_mamba_blocks=True)
+        return nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
+                                        decay_for_non_mamba_blocks=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    status = _lib.load().natsl_device_status()
+    if rank == 0:
+        print(json.dumps({"metric": "prefill_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic (seeded, generated per rank)",
+                          "config": {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 "
+                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} (contiguous segments)"},
+                          "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,6 +440,9 @@ def main():
     ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (default: the benchmark's 8; "
                     "smaller values are for profiler captures only)")
     ap.add_argument("--min-warm-seconds", type=float, default=1.5, help="minimum warm-up time under load")
+    ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long"],
+                    help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
+                         "Mamba2 layer, sequence-parallel over the ranks")
     args = ap.parse_args()
     CFG["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
@@ -370,6 +451,8 @@ def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if args.impl == "reference":
         run_reference(args, rank)
+    elif args.workload == "mamba_long":
+        run_mamba_long(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
