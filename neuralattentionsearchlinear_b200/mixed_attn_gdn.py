@@ -19,6 +19,17 @@ all_incomplete_ops = {
 }
 
 
+_attn_streams: dict = {}
+
+
+def _get_attn_stream(device: torch.device) -> torch.cuda.Stream:
+    """One side stream per device for the softmax branch (mixed_attn_gdn.py:19-26 of the reference)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _attn_streams:
+        _attn_streams[idx] = torch.cuda.Stream(device=idx)
+    return _attn_streams[idx]
+
+
 def _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn, table):
     if ops_for_incomplete_chunks not in table:
         raise KeyError(ops_for_incomplete_chunks)
@@ -53,10 +64,19 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
             raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
         T = q_lattn.shape[1]
         tables = build_selection_tables(nats_block_types, T, nats_block_size)
-        o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        # the two branches are independent: the softmax branch runs on a side stream (as the reference does for
+        # its Mamba2 / DeltaNet ops, src/nats/ops/mixed_ops/mixed_attn_mamba.py:114-124) and joins before returning
+        cur = torch.cuda.current_stream(q_attn.device)
+        side = _get_attn_stream(q_attn.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
         o_gdn, ht, _ = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
                                        initial_state_gated_delta, decay_for_non_gdn_blocks,
                                        lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta)
+        cur.wait_stream(side)
+        for t_ in (q_attn, k_attn, v_attn, o_attn, lse):
+            t_.record_stream(side)
         ctx.mark_non_differentiable(o_gdn, o_attn)
         return o_gdn, o_attn, ht
 
