@@ -122,6 +122,31 @@ int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, co
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
                        int V, float scale, int use_l2norm, void* stream);
 
+/* State recurrence and chunk output in one walk on tcgen05 (state kept in TMEM, never written to memory):
+ * same inputs as natsl_linear_fwd_h + natsl_linear_fwd_o for the gated delta rule, outputs o [B,T,H,V] bf16
+ * and ht [B,H,K,V] fp32 (or NULL).  Built for K = V = 128 and nats_block_size = 64.
+ * Replaces: chunk_gated_delta_rule_nats_fwd_h + chunk_fwd_nats_o (src/nats/ops/common/chunk_delta_h.py:638-732,
+ * src/nats/ops/common/chunk_o.py:1176-1259) and chunk_cumsum_non_gated_chunks (src/nats/ops/utils/cumsum.py:136-180). */
+int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void* u, const float* gcs,
+                         const float* k_rstd, const int32_t* types_i, const int32_t* indices, const int32_t* n_blocks,
+                         const float* h0, void* o, float* ht, int B, int T, int H, int HN, int K, int V, int nbs,
+                         float scale, int flags, int use_l2norm, void* stream);
+
+/* Reference-precision (fp32 math, CUDA cores) path for fp32 or bf16 tensors (dtype = NATSL_DT_F32 / _BF16 for
+ * q, k, v, beta, o): token-by-token linear recurrence with re-roll to the block-start state, and plain masked
+ * softmax attention.  ht = state after the last selected block, hstart = block-start state at the end (both
+ * [B,H,K,V] fp32, may be NULL).
+ * Replaces: fused_recurrent_gated_delta_rule_fwd_nats_kernel src/nats/ops/gated_delta_rule/fused_recurrent.py:28-358,
+ * fused_recurrent_mamba_fwd_nats_kernel src/nats/ops/mamba/fused_recurrent.py:28-322, and the masked SDPA of the
+ * recurrent ops (src/nats/ops/mixed_ops/mixed_attn_gdn.py:475-504). */
+int natsl_linear_recurrent_fwd(int rule, int dtype, const void* q, const void* k, const void* v, const float* g,
+                               const void* beta, const int32_t* types_i, const float* h0, void* o, float* ht,
+                               float* hstart, int B, int T, int H, int HN, int K, int V, int nbs, float scale,
+                               int flags, int use_l2norm, void* stream);
+int natsl_attn_fwd_fp32(int dtype, const void* q, const void* k, const void* v, const int32_t* types_i, void* o,
+                        float* lse, int B, int T, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
+                        int flags, void* stream);
+
 /* Sequence-parallel helpers (no reference counterpart; the recurrence they split is
  * src/nats/ops/mamba/chunk_h.py:139-218).
  * natsl_sp_segment_decay: a [B,H] = exp(total log decay the carried state sees over this segment);

@@ -7,6 +7,7 @@ from . import _lib
 from .nats_util import SelectionTables, cdiv, current_stream_ptr
 
 BF16 = torch.bfloat16
+USE_FUSED_WALK = True        # K = V = 128, block 64: recurrence + output fused on tcgen05 (natsl_gdn_walk_fused)
 
 
 def _need(cond: bool, msg: str, exc=ValueError):
@@ -73,13 +74,23 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     else:
         w, u, krstd = None, v, None
         _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
-    h = torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
-    carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)
     ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
     if h0 is not None:
         h0 = h0.float().contiguous()
         _need(tuple(h0.shape) == (B, H, K, V), f"initial state must be [B,H,K,V], got {tuple(h0.shape)}")
     flags = (_lib.FLAG_DECAY_SKIPPED if decay else 0) | (0 if trailing_quirk else _lib.FLAG_NO_TRAILING_QUIRK)
+    fused = (rule == _lib.RULE_GDN and K == 128 and V == 128 and nbs == 64 and NT <= 1024 and not return_intermediates
+             and not skip_out and USE_FUSED_WALK)
+    if fused:
+        # recurrence + output in one tcgen05 walk; the per-chunk states are never materialised
+        o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
+        _lib.call("natsl_gdn_walk_fused", q.data_ptr(), k.data_ptr(), w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
+                  krstd.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
+                  _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, float(scale), flags,
+                  int(use_l2norm), st)
+        return o, ht, None
+    h = torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
+    carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)
     _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krstd),
               tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
               h.data_ptr(), carry.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, flags, st)
@@ -91,3 +102,51 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
               _lib.ptr(krstd), h.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V, float(scale),
               int(use_l2norm and rule == _lib.RULE_GDN), st)
     return o, ht, inter
+
+
+def _dt_code(t):
+    if t.dtype == torch.float32:
+        return _lib.DT_F32
+    if t.dtype == BF16:
+        return _lib.DT_BF16
+    raise TypeError(f"unsupported dtype {t.dtype} (fp32 or bf16)")
+
+
+def linear_recurrent(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool,
+                     use_l2norm: bool):
+    """Reference-precision linear branch: token recurrence with re-roll (fp32 math; fp32 or bf16 tensors).
+    Returns (o, ht, hstart): output, state after the last selected block, block-start state at the end."""
+    _need(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype", TypeError)
+    code = _dt_code(q)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, T, H, K = q.shape
+    V = v.shape[3]
+    dev = q.device
+    g = g.float().contiguous()
+    if beta is not None:
+        beta = beta.to(q.dtype).contiguous()
+    if h0 is not None:
+        h0 = h0.float().contiguous()
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
+    hstart = torch.empty_like(ht)
+    _lib.call("natsl_linear_recurrent_fwd", rule, code, q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(),
+              _lib.ptr(beta), tables.types_i.data_ptr(), _lib.ptr(h0), o.data_ptr(), ht.data_ptr(), hstart.data_ptr(),
+              B, T, H, tables.types_i.shape[2], K, V, tables.nats_block_size, float(scale),
+              _lib.FLAG_DECAY_SKIPPED if decay else 0, int(use_l2norm), current_stream_ptr(dev))
+    return o, ht, hstart
+
+
+def attn_fwd_fp32(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
+    """Reference-precision softmax branch (fp32 math; fp32 or bf16 tensors).  Returns (o, lse base-2)."""
+    _need(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype", TypeError)
+    code = _dt_code(q)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, T, HQ, DK = q.shape
+    HKV, DV = k.shape[2], v.shape[3]
+    o = torch.empty(B, T, HQ, DV, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, T, HQ, dtype=torch.float32, device=q.device)
+    _lib.call("natsl_attn_fwd_fp32", code, q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
+              o.data_ptr(), lse.data_ptr(), B, T, HQ, HKV, tables.types_i.shape[2], DK, DV, tables.nats_block_size,
+              float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0, current_stream_ptr(q.device))
+    return o, lse

@@ -64,6 +64,14 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
             raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
         T = q_lattn.shape[1]
         tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        if q_lattn.dtype == torch.float32:
+            # fp32 tensors take the reference-precision kernels (token recurrence with re-roll, fp32 softmax)
+            o_attn, lse = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+            o_gdn, ht, _ = _ops.linear_recurrent(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
+                                                 initial_state_gated_delta, decay_for_non_gdn_blocks,
+                                                 lattn_use_qk_l2norm_in_kernel)
+            ctx.mark_non_differentiable(o_gdn, o_attn)
+            return o_gdn, o_attn, (ht if output_final_state_gated_delta else None)
         # the two branches are independent: the softmax branch runs on a side stream (as the reference does for
         # its Mamba2 / DeltaNet ops, src/nats/ops/mixed_ops/mixed_attn_mamba.py:114-124) and joins before returning
         cur = torch.cuda.current_stream(q_attn.device)

@@ -51,6 +51,11 @@ def nats_mixed_attn_mamba(
     T = q_lattn.shape[1]
     with torch.no_grad():
         tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        if q_lattn.dtype == torch.float32:
+            o_attn, _ = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+            o_m, ht, _ = _ops.linear_recurrent(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
+                                               initial_state_mamba, decay_for_non_mamba_blocks, False)
+            return o_m, o_attn, (ht if output_final_state_mamba else None)
         o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
         o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
                                      initial_state_mamba, decay_for_non_mamba_blocks, False,

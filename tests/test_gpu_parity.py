@@ -207,3 +207,60 @@ def test_full_size_layer_config(nat):
     sub = {n: t[3:5].contiguous() for n, t in d.items()}
     o_l2, o_a2, ht2 = run(sub)
     assert torch.equal(o_l2, o_l[3:5]) and torch.equal(o_a2, o_a[3:5]) and torch.equal(ht2, ht[3:5])
+
+
+@pytest.mark.parametrize("B,T,H,HN,decay,use_h0", [(2, 512, 4, 4, True, False), (1, 700, 4, 2, True, True),
+                                                    (2, 384, 2, 2, False, True), (1, 64, 2, 2, True, True),
+                                                    (1, 50, 2, 1, True, False), (1, 2048, 2, 2, True, True)])
+def test_gdn_fused_walk(nat, B, T, H, HN, decay, use_h0):
+    """Recurrence + output fused on tcgen05 (K = V = 128, block 64) against the oracle, and against the
+    two-kernel path it replaces."""
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    K = V = 128
+    q, k, v, g, beta, h0 = synth_gdn_inputs(B, T, H, K, V, seed=T + 5, normalize_qk=False)
+    if not use_h0:
+        h0 = None
+    types = otab.synth_types(B, -(-T // 64), HN, 0.35, seed=T + 2)
+    tb = nat.build_selection_tables(types.cuda(), T, 64)
+    args = (_lib.RULE_GDN, q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), tb, K ** -0.5,
+            None if h0 is None else h0.cuda(), decay, True, True)
+    assert _ops.USE_FUSED_WALK
+    o, ht, inter = _ops.linear_fwd(*args)
+    assert inter is None                                   # fused path: no per-chunk states
+    assert _lib.load().natsl_device_status() == 0
+    o_ref, s_ref = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, beta.float(), types[..., 1], nbs=64, h0=h0,
+                                     decay=decay)
+    assert_close(o, o_ref, TOL, "o_gdn (fused walk)")
+    assert_close(ht, s_ref, 2 * TOL, "final_state (fused walk)")
+    o2, ht2, _ = _ops.linear_fwd(*args, return_intermediates=True)      # scan + out kernels
+    assert_close(o, o2.float(), TOL, "fused vs two-kernel o")
+    assert_close(ht, ht2, 2 * TOL, "fused vs two-kernel state")
+
+
+@pytest.mark.parametrize("nbs,decay,T", [(64, True, 512), (128, False, 400), (64, True, 100)])
+def test_fp32_path_matches_naive_recurrent_form(nat, nbs, decay, T):
+    """fp32 tensors (the CPU-sized configuration: B=2, H=4, d=64): the reference-precision kernels against the
+    naive recurrent form within 1e-4, through the public op."""
+    B, H, K, V = 2, 4, 64, 64
+    q, k, v, g, beta, h0 = synth_gdn_inputs(B, T, H, K, V, seed=0, dtype=torch.float32)
+    types = otab.synth_types(B, -(-T // nbs), H, 0.5, seed=0)
+    cu = lambda x: x.cuda()
+    o_l, o_a, ht = nat.nats_mixed_attn_gdn(cu(q), cu(k), cu(v), cu(q), cu(k), cu(v), cu(h0), cu(g), cu(beta), cu(types),
+                                           None, nats_block_size=nbs, ops_for_incomplete_chunks='all',
+                                           output_final_state_gated_delta=True, decay_for_non_gdn_blocks=decay)
+    assert o_l.dtype == torch.float32
+    o_ref, s_ref = ogdn.linear_recurrent(q.double(), k.double(), v.double(), g.double(), beta.double(), types[..., 1],
+                                         nbs=nbs, h0=h0.double(), decay=decay)
+    mask = oattn.attn_mask(types[..., 0], T, nbs, H)
+    oa_ref, _ = oattn.attn_sdpa(q.double(), k.double(), v.double(), mask)
+    assert_close(o_l, o_ref.float(), 1e-4, "o_gdn fp32")
+    assert_close(o_a, oa_ref.float(), 1e-4, "o_attn fp32")
+    assert_close(ht, s_ref.float(), 1e-4, "final_state fp32")
+    # Mamba2 rule
+    o_m, o_a2, htm = nat.nats_mixed_attn_mamba(cu(q), cu(k), cu(v), cu(q), cu(k), cu(v), cu(h0), cu(g), cu(types), None,
+                                               nats_block_size=nbs, ops_for_incomplete_chunks='all',
+                                               output_final_state_mamba=True, decay_for_non_mamba_blocks=decay)
+    om_ref, sm_ref = ogdn.linear_recurrent(q.double(), k.double(), v.double(), g.double(), None, types[..., 1], nbs=nbs,
+                                           scale=1.0, h0=h0.double(), decay=decay, use_l2norm=False, rule="mamba")
+    assert_close(o_m, om_ref.float(), 1e-4, "o_mamba fp32")
+    assert_close(htm, sm_ref.float(), 1e-4, "mamba final_state fp32")
