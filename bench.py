@@ -247,11 +247,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- per-kernel durations: each stage launched `steps` times back to back on the same stream between two
     # CUDA events (the queue stays full, so the events bracket device time, not host launch latency)
-    names = ["tables", "attn_fwd", "gdn_prep", "scan_fwd_h", "out_fwd_o"]
+    names = ["tables", "attn_fwd", "gdn_prep", "walk_fused", "scan_fwd_h", "out_fwd_o"]
     NT = T // 64
     tb = nat.build_selection_tables(d["types"], T, nbs)
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     krs = torch.empty_like(gcs)
+    qrs = torch.empty_like(gcs)
+    pmat = torch.empty(B, T, H, 64, dtype=torch.bfloat16, device=dev)
     w = torch.empty(B, T, H, K, dtype=torch.bfloat16, device=dev)
     u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=dev)
     hbuf = torch.empty(B, NT, H, K, V, dtype=torch.bfloat16, device=dev)
@@ -262,9 +264,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     stages = {
         "tables": lambda: nat.build_selection_tables(d["types"], T, nbs),
         "attn_fwd": lambda: _ops.attn_fwd(d["q"], d["k"], d["v"], tb, K ** -0.5, True),
-        "gdn_prep": lambda: _lib.call("natsl_gdn_chunk_prep", d["k"].data_ptr(), d["v"].data_ptr(), d["g"].data_ptr(),
-                                      d["beta"].data_ptr(), _lib.DT_BF16, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
-                                      krs.data_ptr(), B, T, H, K, V, 1, sp),
+        "gdn_prep": lambda: _lib.call("natsl_gdn_chunk_prep_ex", d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+                                      d["g"].data_ptr(), d["beta"].data_ptr(), _lib.DT_BF16, w.data_ptr(), u.data_ptr(),
+                                      gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(), pmat.data_ptr(), B, T, H, K, V, 1, sp),
+        "walk_fused": lambda: _lib.call("natsl_gdn_walk_fused", d["q"].data_ptr(), d["k"].data_ptr(), w.data_ptr(),
+                                        u.data_ptr(), pmat.data_ptr(), gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(),
+                                        tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
+                                        o.data_ptr(), ht.data_ptr(), B, T, H, H, K, V, nbs, K ** -0.5,
+                                        _lib.FLAG_DECAY_SKIPPED, sp),
         "scan_fwd_h": lambda: _lib.call("natsl_linear_fwd_h", _lib.RULE_GDN, d["k"].data_ptr(), w.data_ptr(), u.data_ptr(),
                                         gcs.data_ptr(), krs.data_ptr(), tb.types_i.data_ptr(), tb.indices.data_ptr(),
                                         tb.n_blocks.data_ptr(), None, hbuf.data_ptr(), carry.data_ptr(), ht.data_ptr(),
@@ -328,10 +335,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     state_bytes = B * NT * H * K * V * 2
     # ncu dram__bytes_read+write per launch, captured at B=4 (profiles/ncu_full_current_kernels_B4.md), scaled by B/4:
     # traffic grows in proportion to the batch (independent (batch, head) units)
-    ncu_traffic_b4 = {"attn_fwd": 248.5e6, "gdn_prep": 223.8e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6}
+    ncu_traffic_b4 = {"attn_fwd": 248.5e6, "gdn_prep": 223.8e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
+                      "walk_fused": None}
+    # the step runs tables, attn_fwd, gdn_prep, walk_fused; scan_fwd_h + out_fwd_o are the two-kernel path the fused
+    # walk replaces at this shape (still used for other head dims / block sizes) and are timed for comparison
+    in_step = ("attn_fwd", "gdn_prep", "walk_fused")
     work = {
+        # reads q, k, w, u, P once, writes o
+        "walk_fused": ("hbm", n_tok * (3 * K + V + 64) * 2 + n_tok * V * 2, "gdn_walk_tc_kernel"),
         "attn_fwd": ("tensor", attention_tile_flops(host["types"], H, K, V), "attn_fwd_tc_kernel<128,128>"),
-        "gdn_prep": ("hbm", n_tok * (K + V) * 2 * 2 + n_tok * 14, "gdn_prep_kernel<128,128>"),
+        "gdn_prep": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (K + V + 64) * 2 + n_tok * 18, "gdn_prep_kernel<128,128>"),
         "scan_fwd_h": ("hbm", frac_lin * n_tok * (2 * K + V) * 2 + state_bytes, "linear_scan_kernel<128,32,gdn>"),
         "out_fwd_o": ("hbm", n_tok * (3 * K + V) * 2 + state_bytes + n_tok * V * 2, "linear_out_kernel<128,128,gdn>"),
     }
@@ -343,9 +356,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         else:
             ach, peak, unit = amount / sec / 1e9, peak_bw, "GB/s"
         roofs[n] = {"kernel": kname, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-                    "traffic": ncu_traffic_b4[n] * B / 4.0, "algorithmic_per_launch": amount,
+                    "traffic": (ncu_traffic_b4[n] * B / 4.0) if ncu_traffic_b4[n] else None, "algorithmic_per_launch": amount,
                     "ms_per_launch": kernel_ms[n]}
-    dom = max(work, key=lambda n: kernel_ms[n])
+    dom = max(in_step, key=lambda n: kernel_ms[n])
     roofline = dict(roofs[dom], peak_source=peak_src, dominant_stage=dom)
     # ---- CPU baseline (oracle port) on a bounded sample
     cpu_val, cpu_sample, _ = time_cpu_baseline({n: t for n, t in host.items()}, budget_s=15.0)
@@ -355,7 +368,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, generated on the host)",
         "config": {"workload": WORKLOAD.format(B=B), "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)",
                    "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"},
-        "clocks": clk, "gpu_launches": 6 * args.steps,
+        "clocks": clk, "gpu_launches": 5 * args.steps,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps},
         "kernel_ms": kernel_ms, "roofline": roofline, "roofline_all": roofs,

@@ -122,15 +122,23 @@ int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, co
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
                        int V, float scale, int use_l2norm, void* stream);
 
+/* Chunk preparation that also emits what the fused walk needs: q_rstd [B,T,H] fp32 and the intra-chunk score
+ * matrix P = tril(qn kn^T e^{gcs_i - gcs_j}) [B,T,H,64] bf16 (q, q_rstd, pmat may all be NULL = natsl_gdn_chunk_prep).
+ * Replaces in addition: l2norm_fwd(q) src/nats/ops/mixed_ops/mixed_attn_gdn.py:119-120 and the q k^T part of
+ * chunk_fwd_kernel_o src/nats/ops/common/chunk_o.py:166,188,202-203. */
+int natsl_gdn_chunk_prep_ex(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                            int beta_dtype, void* w, void* u, float* gcs, float* k_rstd, float* q_rstd, void* pmat,
+                            int B, int T, int H, int K, int V, int use_l2norm, void* stream);
+
 /* State recurrence and chunk output in one walk on tcgen05 (state kept in TMEM, never written to memory):
- * same inputs as natsl_linear_fwd_h + natsl_linear_fwd_o for the gated delta rule, outputs o [B,T,H,V] bf16
- * and ht [B,H,K,V] fp32 (or NULL).  Built for K = V = 128 and nats_block_size = 64.
+ * inputs from natsl_gdn_chunk_prep_ex, outputs o [B,T,H,V] bf16 and ht [B,H,K,V] fp32 (or NULL).
+ * Built for K = V = 128 and nats_block_size = 64.
  * Replaces: chunk_gated_delta_rule_nats_fwd_h + chunk_fwd_nats_o (src/nats/ops/common/chunk_delta_h.py:638-732,
  * src/nats/ops/common/chunk_o.py:1176-1259) and chunk_cumsum_non_gated_chunks (src/nats/ops/utils/cumsum.py:136-180). */
-int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void* u, const float* gcs,
-                         const float* k_rstd, const int32_t* types_i, const int32_t* indices, const int32_t* n_blocks,
-                         const float* h0, void* o, float* ht, int B, int T, int H, int HN, int K, int V, int nbs,
-                         float scale, int flags, int use_l2norm, void* stream);
+int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void* u, const void* pmat,
+                         const float* gcs, const float* k_rstd, const float* q_rstd, const int32_t* types_i,
+                         const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht, int B,
+                         int T, int H, int HN, int K, int V, int nbs, float scale, int flags, void* stream);
 
 /* Reference-precision (fp32 math, CUDA cores) path for fp32 or bf16 tensors (dtype = NATSL_DT_F32 / _BF16 for
  * q, k, v, beta, o): token-by-token linear recurrence with re-roll to the block-start state, and plain masked

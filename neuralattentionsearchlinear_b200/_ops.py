@@ -62,15 +62,19 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     st = current_stream_ptr(dev)
     g = g.float().contiguous()
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    fused = (rule == _lib.RULE_GDN and K == 128 and V == 128 and nbs == 64 and NT <= 1024 and not return_intermediates
+             and not skip_out and USE_FUSED_WALK)
     if rule == _lib.RULE_GDN:
         beta = beta.contiguous()
         _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
         w = torch.empty(B, T, H, K, dtype=BF16, device=dev)
         u = torch.empty(B, T, H, V, dtype=BF16, device=dev)
         krstd = torch.empty(B, T, H, dtype=torch.float32, device=dev)
-        _lib.call("natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
-                  _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
-                  krstd.data_ptr(), B, T, H, K, V, int(use_l2norm), st)
+        qrstd = torch.empty(B, T, H, dtype=torch.float32, device=dev) if fused else None
+        pmat = torch.empty(B, T, H, 64, dtype=BF16, device=dev) if fused else None
+        _lib.call("natsl_gdn_chunk_prep_ex", q.data_ptr() if fused else None, k.data_ptr(), v.data_ptr(), g.data_ptr(),
+                  beta.data_ptr(), _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(),
+                  gcs.data_ptr(), krstd.data_ptr(), _lib.ptr(qrstd), _lib.ptr(pmat), B, T, H, K, V, int(use_l2norm), st)
     else:
         w, u, krstd = None, v, None
         _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
@@ -79,15 +83,13 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
         h0 = h0.float().contiguous()
         _need(tuple(h0.shape) == (B, H, K, V), f"initial state must be [B,H,K,V], got {tuple(h0.shape)}")
     flags = (_lib.FLAG_DECAY_SKIPPED if decay else 0) | (0 if trailing_quirk else _lib.FLAG_NO_TRAILING_QUIRK)
-    fused = (rule == _lib.RULE_GDN and K == 128 and V == 128 and nbs == 64 and NT <= 1024 and not return_intermediates
-             and not skip_out and USE_FUSED_WALK)
     if fused:
         # recurrence + output in one tcgen05 walk; the per-chunk states are never materialised
         o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
-        _lib.call("natsl_gdn_walk_fused", q.data_ptr(), k.data_ptr(), w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
-                  krstd.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
-                  _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, float(scale), flags,
-                  int(use_l2norm), st)
+        _lib.call("natsl_gdn_walk_fused", q.data_ptr(), k.data_ptr(), w.data_ptr(), u.data_ptr(), pmat.data_ptr(),
+                  gcs.data_ptr(), krstd.data_ptr(), qrstd.data_ptr(), tables.types_i.data_ptr(),
+                  tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht),
+                  B, T, H, HN, K, V, nbs, float(scale), flags, st)
         return o, ht, None
     h = torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
     carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)

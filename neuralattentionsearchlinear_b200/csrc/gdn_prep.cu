@@ -31,8 +31,9 @@ struct PrepSmem {
     static constexpr int As = vs + 64 * V * 2;                 // fp32 [64][68]
     static constexpr int Xs = As + 64 * A_LD * 4;              // fp32 [4][16][17]
     static constexpr int Gs = Xs + 4 * 16 * X_LD * 4;          // bf16 [64][64] swizzled (128-byte rows)
-    static constexpr int vec = Gs + 64 * 64 * 2;               // gcs, beta, rstd, wscale: 4 x 64 floats
-    static constexpr int total = vec + 4 * 64 * 4;
+    static constexpr int vec = Gs + 64 * 64 * 2;               // gcs, beta, rstd, wscale, q rstd: 5 x 64 floats
+    static constexpr int total = vec + 5 * 64 * 4;
+    static_assert(64 * K * 2 <= 64 * A_LD * 4, "the q tile is staged in the A buffer");
     static_assert(Gs % 128 == 0, "G tile alignment");
 };
 
@@ -99,10 +100,14 @@ __device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsi
 
 template <int K, int V>
 __global__ void __launch_bounds__(PREP_THREADS)
-gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
-                const void* __restrict__ beta, int beta_dtype, __nv_bfloat16* __restrict__ w,
-                __nv_bfloat16* __restrict__ u, float* __restrict__ gcs_out, float* __restrict__ krstd_out, int T, int H,
-                int use_l2norm) {
+gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const void* __restrict__ beta,
+                int beta_dtype, __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ u,
+                float* __restrict__ gcs_out, float* __restrict__ krstd_out, float* __restrict__ qrstd_out,
+                __nv_bfloat16* __restrict__ p_out, int T, int H, int use_l2norm) {
+    // q, qrstd_out, p_out may be null; when given the kernel also emits the intra-chunk score matrix
+    //   P = tril(qn kn^T e^{gcs_i - gcs_j})  [B,T,H,64] bf16  (src/nats/ops/common/chunk_o.py:166,188,202-203)
+    // and q's l2 norm factors, for the fused recurrence + output walk.
     using L = PrepSmem<K, V>;
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -120,8 +125,11 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
     float* s_beta = s_gcs + 64;
     float* s_rstd = s_beta + 64;
     float* s_wsc = s_rstd + 64;
-    const uint32_t ks = smem_u32(ks_p), vs = smem_u32(vs_p), gs = smem_u32(gs_p);
+    float* s_qr = s_wsc + 64;
+    unsigned char* qs_p = smem + L::As;                       // q tile, until A is written
+    const uint32_t ks = smem_u32(ks_p), vs = smem_u32(vs_p), gs = smem_u32(gs_p), qs = smem_u32(qs_p);
 
+    if (q) load_tile_async<64, K, PREP_THREADS>(qs, q + (tok0 * H + h) * K, (long)H * K, valid, tid);
     load_tile_async<64, K, PREP_THREADS>(ks, k + (tok0 * H + h) * K, (long)H * K, valid, tid);
     load_tile_async<64, V, PREP_THREADS>(vs, v + (tok0 * H + h) * V, (long)H * V, valid, tid);
     cp_async_commit();
@@ -186,6 +194,29 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
             }
         }
     }
+    if (q) {
+        constexpr int CPR = K / 8;
+        constexpr int RPP = 32 / CPR > 0 ? 32 / CPR : 1;
+        const int sub = lane / CPR, cc = lane % CPR;
+        for (int rr = 0; rr < 16; rr += RPP) {
+            int r = warp * 16 + rr + sub;
+            uint4 xv = *reinterpret_cast<const uint4*>(qs_p + swz<K * 2>(r, cc));
+            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv);
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 t = unpack_bf16(xw[j]);
+                ss += t.x * t.x + t.y * t.y;
+            }
+#pragma unroll
+            for (int o = CPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (cc == 0) {
+                const float rs = use_l2norm ? rsqrtf(ss + 1e-6f) : 1.0f;
+                s_qr[r] = rs;
+                if (r < valid && qrstd_out) qrstd_out[(tok0 + r) * H + h] = rs;
+            }
+        }
+    }
     scale_rows_inplace<V>(vs_p, s_beta, tid);
     __syncthreads();
 
@@ -208,14 +239,53 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
                 mma_bf16(acc[2 * p + 1], a, bb[2], bb[3]);
             }
         }
-        const int gq = lane >> 2, q = lane & 3;
+        const int gq = lane >> 2, qd = lane & 3;
+        if (q) {
+            // ---- P = tril(qn kn^T e^{gcs_i - gcs_j}), staged through the (still unused) G tile
+            float accp[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) accp[i][j] = 0.f;
+#pragma unroll 2
+            for (int kk = 0; kk < K / 16; ++kk) {
+                uint32_t a[4];
+                load_a<K * 2>(qs, r0, kk * 16, lane, a);
+                for (int p = 0; p <= warp; ++p) {
+                    uint32_t bb[4];
+                    load_b_nk<K * 2>(ks, p * 16, kk * 16, lane, bb);
+                    mma_bf16(accp[2 * p], a, bb[0], bb[1]);
+                    mma_bf16(accp[2 * p + 1], a, bb[2], bb[3]);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = r0 + gq + hh * 8;
+                    const int j = nt * 8 + qd * 2;
+                    float v0 = 0.f, v1 = 0.f;
+                    if (j <= i && j < valid) v0 = accp[nt][hh * 2] * s_qr[i] * __expf(s_gcs[i] - s_gcs[j]);
+                    if (j + 1 <= i && j + 1 < valid) v1 = accp[nt][hh * 2 + 1] * s_qr[i] * __expf(s_gcs[i] - s_gcs[j + 1]);
+                    *reinterpret_cast<uint32_t*>(gs_p + swz<128>(i, nt) + qd * 4) = pack_bf16(v0, v1);
+                }
+            }
+            __syncwarp();
+            for (int it = lane; it < 16 * 8; it += 32) {
+                const int r = r0 + (it >> 3), cch = it & 7;
+                if (r < valid)
+                    *reinterpret_cast<uint4*>(p_out + ((tok0 + r) * H + h) * 64 + cch * 8) =
+                        *reinterpret_cast<const uint4*>(gs_p + swz<128>(r, cch));
+            }
+            __syncthreads();          // every warp is done with the q tile before A overwrites it
+        }
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
             if (nt <= 2 * warp + 1) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = r0 + gq + hh * 8;
-                    const int j = nt * 8 + q * 2;
+                    const int j = nt * 8 + qd * 2;
                     float v0 = 0.f, v1 = 0.f;
                     if (i > j) v0 = s_beta[i] * acc[nt][hh * 2] * __expf(s_gcs[i] - s_gcs[j]);
                     if (i > j + 1) v1 = s_beta[i] * acc[nt][hh * 2 + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
@@ -282,8 +352,9 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
 }
 
 template <int K, int V>
-static int launch_prep(const void* k, const void* v, const float* g, const void* beta, int beta_dtype, void* w, void* u,
-                       float* gcs, float* krstd, int B, int T, int H, int use_l2norm, cudaStream_t st) {
+static int launch_prep(const void* q, const void* k, const void* v, const float* g, const void* beta, int beta_dtype,
+                       void* w, void* u, float* gcs, float* krstd, float* qrstd, void* pmat, int B, int T, int H,
+                       int use_l2norm, cudaStream_t st) {
     using L = PrepSmem<K, V>;
     auto kern = gdn_prep_kernel<K, V>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
@@ -294,25 +365,29 @@ static int launch_prep(const void* k, const void* v, const float* g, const void*
     const int NT = (T + 63) / 64;
     dim3 grid(NT, H, B);
     kern<<<grid, PREP_THREADS, L::total, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(k), reinterpret_cast<const __nv_bfloat16*>(v), g, beta, beta_dtype,
-        reinterpret_cast<__nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(u), gcs, krstd, T, H, use_l2norm);
+        reinterpret_cast<const __nv_bfloat16*>(q), reinterpret_cast<const __nv_bfloat16*>(k),
+        reinterpret_cast<const __nv_bfloat16*>(v), g, beta, beta_dtype, reinterpret_cast<__nv_bfloat16*>(w),
+        reinterpret_cast<__nv_bfloat16*>(u), gcs, krstd, qrstd, reinterpret_cast<__nv_bfloat16*>(pmat), T, H, use_l2norm);
     return check_launch("natsl_gdn_chunk_prep");
 }
 
 }  // namespace natsl
 
-extern "C" int natsl_gdn_chunk_prep(const void* k, const void* v, const float* g, const void* beta, int beta_dtype,
-                                    void* w, void* u, float* gcs, float* k_rstd, int B, int T, int H, int K, int V,
-                                    int use_l2norm, void* stream) {
+extern "C" int natsl_gdn_chunk_prep_ex(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                       int beta_dtype, void* w, void* u, float* gcs, float* k_rstd, float* q_rstd,
+                                       void* pmat, int B, int T, int H, int K, int V, int use_l2norm, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(k && v && g && beta && w && u && gcs && k_rstd, NATSL_ERR_NULL, "natsl_gdn_chunk_prep: null pointer");
+    NATSL_REQUIRE((q == nullptr) == (pmat == nullptr), NATSL_ERR_NULL,
+                  "natsl_gdn_chunk_prep: q and the score-matrix output go together");
     NATSL_REQUIRE(B > 0 && T > 0 && H > 0, NATSL_ERR_BAD_SHAPE, "natsl_gdn_chunk_prep: empty shape");
     NATSL_REQUIRE(H <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_gdn_chunk_prep: B and H must be <= 65535");
     NATSL_REQUIRE(beta_dtype == NATSL_DT_BF16 || beta_dtype == NATSL_DT_F32, NATSL_ERR_UNSUPPORTED,
                   "natsl_gdn_chunk_prep: beta must be bf16 or f32");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define NATSL_PREP_CASE(KK, VV) \
-    if (K == KK && V == VV) return launch_prep<KK, VV>(k, v, g, beta, beta_dtype, w, u, gcs, k_rstd, B, T, H, use_l2norm, st);
+    if (K == KK && V == VV)     \
+        return launch_prep<KK, VV>(q, k, v, g, beta, beta_dtype, w, u, gcs, k_rstd, q_rstd, pmat, B, T, H, use_l2norm, st);
     NATSL_PREP_CASE(64, 64)
     NATSL_PREP_CASE(64, 128)
     NATSL_PREP_CASE(128, 64)
@@ -321,4 +396,11 @@ extern "C" int natsl_gdn_chunk_prep(const void* k, const void* v, const float* g
 #undef NATSL_PREP_CASE
     set_error("natsl_gdn_chunk_prep: unsupported head dims K=%d V=%d (K in {64,128}, V in {64,128,256})", K, V);
     return NATSL_ERR_UNSUPPORTED;
+}
+
+extern "C" int natsl_gdn_chunk_prep(const void* k, const void* v, const float* g, const void* beta, int beta_dtype,
+                                    void* w, void* u, float* gcs, float* k_rstd, int B, int T, int H, int K, int V,
+                                    int use_l2norm, void* stream) {
+    return natsl_gdn_chunk_prep_ex(nullptr, k, v, g, beta, beta_dtype, w, u, gcs, k_rstd, nullptr, nullptr, B, T, H, K, V,
+                                   use_l2norm, stream);
 }

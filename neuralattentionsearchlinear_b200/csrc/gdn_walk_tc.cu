@@ -2,26 +2,29 @@
 // (head dims K = V = 128, nats_block_size = 64).  One CTA per (batch, head) walks the 64-token chunks in
 // order; the K x V state lives in TMEM (fp32) and is never written to global memory.  Per chunk c
 // (S = state the chunk reads, carry = decay of the skipped blocks before it):
-//     [w S ; q S] and [. ; q k^T]   one stacked 128-row A operand [w ; q] against S (bf16 copy in shared
-//                                   memory) and against the chunk's keys                     (MMA 0, 1)
-//     v' = u - e^{carry} w S,   P = tril(qn kn^T e^{g_i - g_j})                              (warps, from TMEM)
-//     o  = scale (rstd_q e^{g+carry} q S + P v')                                             (MMA 2 + warps)
-//     S <- e^{g_last+carry} S + k^T (v' rstd_k e^{g_last-g})       only if the block is selected   (MMA 3)
+//     [w S ; q S]       one stacked 128-row A operand [w ; q] against S (bf16 copy in shared memory)   (MMA 1)
+//     v' = u - e^{carry} w S                                                                           (warps, from TMEM)
+//     o  = scale (rstd_q e^{g+carry} q S + P v')      P = tril(qn kn^T e^{g_i-g_j}) from the prep kernel   (MMA 2 + warps)
+//     S <- e^{g_last+carry} S + k^T (v' rstd_k e^{g_last-g})       only if the block is selected        (MMA 3)
 // which is src/nats/ops/common/chunk_delta_h.py:189-324 (recurrence) fused with
 // src/nats/ops/common/chunk_o.py:124-215 (output) and the carry of src/nats/ops/utils/cumsum.py:85-133.
 // The decay of the state is applied when the state is copied to shared memory for the next chunk
 // (one TMEM pass per update: bf16 copy out, multiply by the next update's decay, write back), so the
-// accumulating MMA 3 needs no separate rescale.
-// Warp roles: warp 0 TMA producer (w, q, k, u tiles, two stages), warp 1 MMA issuer, warps 2-5 one thread
-// per TMEM lane.  All mbarrier waits are bounded (status word + clean teardown on expiry).
+// accumulating MMA 3 needs no separate rescale.  P is padded to 128 rows (rows 0-63 zero) so that
+// P v' lands in the TMEM lanes of the q rows.
+// Warp roles: warp 0 TMA producer (w, q, k, u tiles in two stages, P single-buffered), warp 1 MMA issuer,
+// warps 2-9 two threads per TMEM lane (64 columns each).  All mbarrier waits are bounded (status word +
+// clean teardown on expiry).
 #include "tc_common.cuh"
 #include "../../include/natsl_b200.h"
 
 namespace natsl {
 
-constexpr int WK_THREADS = 192;
+constexpr int WK_THREADS = 320;
+constexpr int WK_EPI = 256;
 constexpr uint32_t WK_TMEM_COLS = 512;
-constexpr uint32_t WK_S = 0, WK_D1 = 128, WK_D2 = 256, WK_DP = 384;     // TMEM column offsets
+constexpr uint32_t WK_S = 0, WK_D1 = 128, WK_D2 = 256;     // TMEM column offsets
+constexpr int WK_MAX_NT = 1024;
 
 struct WkSmem {
     // stage: [w;q] 2 sub-tiles [128][64] (32 KB), k 2 x [64][64] (16 KB), u 2 x [64][64] (16 KB)
@@ -30,22 +33,20 @@ struct WkSmem {
     static constexpr int vp = sbf + 32768;                // v'  : 2 sub-tiles [64 tok][64]                16 KB
     static constexpr int vs = vp + 16384;                 // v'' : same layout                              16 KB
     static constexpr int pp = vs + 16384;                 // P padded to 128 rows: [128][64 tok]            16 KB
-    static constexpr int vec = pp + 16384;                // 2 stages x (gcs[64], k_rstd[64]) floats         1 KB
-    static constexpr int meta = vec + 1024;               // per chunk: carry (float), dec (float), sel (int)
-    static constexpr int bars = meta + 3 * 4 * 1024;      // NT <= 1024
+    static constexpr int meta = pp + 16384;               // per chunk: carry, dec, g_last (float), sel (int)
+    static constexpr int bars = meta + 4 * 4 * WK_MAX_NT;
     static constexpr int total = bars + 256;
 };
-
-__device__ __forceinline__ float ex2f_(float x) { return exp2f(x); }
 
 template <bool kDummy>
 __global__ void __launch_bounds__(WK_THREADS, 1)
 gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_u,
-                   const float* __restrict__ gcs, const float* __restrict__ krstd, const int* __restrict__ types_i,
+                   const __grid_constant__ CUtensorMap map_p, const float* __restrict__ gcs,
+                   const float* __restrict__ krstd, const float* __restrict__ qrstd, const int* __restrict__ types_i,
                    const int* __restrict__ indices, const int* __restrict__ n_blocks, const float* __restrict__ h0,
                    __nv_bfloat16* __restrict__ o, float* __restrict__ ht, int T, int H, int HN, int TN, float scale,
-                   int decay, int trailing_quirk, int use_l2norm, int* status) {
+                   int decay, int trailing_quirk, int* status) {
     using L = WkSmem;
     constexpr int K = 128, V = 128;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -59,12 +60,14 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int hn = h / (H / HN);
     const int NT = (T + 63) / 64;
     float* m_carry = reinterpret_cast<float*>(smem + L::meta);
-    float* m_dec = m_carry + 1024;
-    int* m_sel = reinterpret_cast<int*>(m_dec + 1024);
+    float* m_dec = m_carry + WK_MAX_NT;
+    float* m_gl = m_dec + WK_MAX_NT;
+    int* m_sel = reinterpret_cast<int*>(m_gl + WK_MAX_NT);
     const uint32_t bar0 = sbase + L::bars;
-    // barriers: full[2], empty[2] (tile stages), d1 (MMA0+1 done), pv (v', v'', P written), d2 (MMA2+3 done), sready
-    const uint32_t bar_full = bar0, bar_empty = bar0 + 16, bar_d1 = bar0 + 32, bar_pv = bar0 + 40, bar_d2 = bar0 + 48,
-                   bar_sready = bar0 + 56;
+    // barriers: full[2] / empty[2] tile stages; pfull / pfree the P tile; d1 (MMA 1 done); pv (v', v'' written);
+    // d2 (MMA 2 done); s3 (MMA 3 done); sready (state copy published, D1/D2 free)
+    const uint32_t bar_full = bar0, bar_empty = bar0 + 16, bar_pfull = bar0 + 32, bar_pfree = bar0 + 40, bar_d1 = bar0 + 48,
+                   bar_pv = bar0 + 56, bar_d2 = bar0 + 64, bar_s3 = bar0 + 72, bar_sready = bar0 + 80;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 128);
 
     if (tid == 0) {
@@ -72,17 +75,20 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 1);
         }
+        mbar_init(bar_pfull, 1);
+        mbar_init(bar_pfree, 1);
         mbar_init(bar_d1, 1);
-        mbar_init(bar_pv, 128);
+        mbar_init(bar_pv, WK_EPI);
         mbar_init(bar_d2, 1);
-        mbar_init(bar_sready, 128);
+        mbar_init(bar_s3, 1);
+        mbar_init(bar_sready, WK_EPI);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), WK_TMEM_COLS);
     // ---- per-chunk metadata: selection, carry before the chunk, decay factor of the chunk's update
     for (int c = tid; c < NT; c += WK_THREADS) {
         m_sel[c] = types_i[(((long)b * TN + c) * HN + hn) * 2 + 1] != 0;
-        m_dec[c] = gcs[((long)b * T + min(c * 64 + 63, T - 1)) * H + h];      // g_last for now
+        m_gl[c] = gcs[((long)b * T + min(c * 64 + 63, T - 1)) * H + h];
     }
     // the P operand is padded to 128 rows; rows 0-63 stay zero
     for (int i = tid; i < 8192 / 16; i += WK_THREADS) reinterpret_cast<uint4*>(smem + L::pp)[i] = make_uint4(0, 0, 0, 0);
@@ -92,7 +98,7 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int last_sel = nsel > 0 ? indices[(((long)b * TN + (nsel - 1)) * HN + hn) * 2 + 1] : -1;
         float carry = 0.f;
         for (int c = 0; c < NT; ++c) {
-            const float gl = m_dec[c];
+            const float gl = m_gl[c];
             m_carry[c] = carry;
             if (m_sel[c]) {
                 m_dec[c] = __expf(gl + carry);
@@ -112,17 +118,18 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            prefetch_tensormap(&map_w); prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_u);
+            prefetch_tensormap(&map_w); prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
+            prefetch_tensormap(&map_u); prefetch_tensormap(&map_p);
         }
         for (int c = 0; c < NT; ++c) {
             const int stg = c & 1;
+            const int t0 = c * 64;
             if (c >= 2) {
                 bool ok = mbar_wait(bar_empty + stg * 8, ((c >> 1) - 1) & 1, status);
                 if (!__all_sync(0xffffffffu, ok)) break;
             }
             if (lane == 0) {
                 const uint32_t full = bar_full + stg * 8, base = sbase + stg * L::stage;
-                const int t0 = c * 64;
                 mbar_expect_tx(full, 65536);
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
@@ -132,11 +139,18 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     tma_load_4d(base + L::u + sub * 8192, &map_u, sub * 64, h, t0, b, full);
                 }
             }
+            if (c >= 1) {
+                bool ok = mbar_wait(bar_pfree, (c - 1) & 1, status);       // P of the previous chunk consumed
+                if (!__all_sync(0xffffffffu, ok)) break;
+            }
+            if (lane == 0) {
+                mbar_expect_tx(bar_pfull, 8192);
+                tma_load_4d(sbase + L::pp + 8192, &map_p, 0, h, t0, b, bar_pfull);                      // rows 64-127
+            }
             __syncwarp();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t id_p = umma_idesc_bf16(128, 64, false);                       // [w;q] k^T
         constexpr uint32_t id_1 = umma_idesc_bf16(128, 128, true);                       // [w;q] S
         constexpr uint32_t id_2 = umma_idesc_bf16(128, 128, true);                       // P v'
         constexpr uint32_t id_3 = umma_idesc_bf16(128, 128, true) | (1u << 15);          // k^T v'' (A MN-major)
@@ -152,19 +166,14 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint64_t ad = umma_desc(base + L::wq + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bk = umma_desc(base + L::k + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
-                    umma_ss(tmem + WK_DP, ad, bk, id_p, kk > 0);
-                }
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t ad = umma_desc(base + L::wq + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
                     const uint64_t bs = umma_desc(sbase + L::sbf + kk * 2048, 16384, 1024);
                     umma_ss(tmem + WK_D1, ad, bs, id_1, kk > 0);
                 }
                 umma_commit(bar_d1);
             }
             __syncwarp();
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, c & 1, status));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_pfull, c & 1, status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, c & 1, status));
             if (!ok) break;
             if (lane == 0) {
                 tc_fence_after();
@@ -174,6 +183,8 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     const uint64_t bv = umma_desc(sbase + L::vp + kk * 2048, 8192, 1024);
                     umma_ss(tmem + WK_D2, ad, bv, id_2, kk > 0);
                 }
+                umma_commit(bar_d2);
+                umma_commit(bar_pfree);
                 if (m_sel[c]) {
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
@@ -182,25 +193,26 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         umma_ss(tmem + WK_S, ak, bv, id_3, 1u);
                     }
                 }
-                umma_commit(bar_d2);
+                umma_commit(bar_s3);
                 umma_commit(bar_empty + stg * 8);
             }
             __syncwarp();
         }
     } else {
-        // ------------------------------------------------------------ one thread per TMEM lane
+        // ------------------------------------------------------------ two threads per TMEM lane (64 columns each)
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quad * 32 + lane;                 // TMEM lane: S row (k index); w row (0-63) or q row (64-127)
+        const int cb = half * 64;                         // this thread's first column
         const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-        float* s_vec = reinterpret_cast<float*>(smem + L::vec);
         const bool is_q = row >= 64;
         const int tr = row & 63;                          // token row inside the chunk
         bool ok = true;
 
-        // writes this lane's S row as bf16 into the shared copy and leaves S * mul in TMEM
+        // copies columns [cb, cb+64) of this lane's S row as bf16 into the shared copy and leaves S * mul in TMEM
         auto publish_state = [&](float mul, const float* init_row) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < V; c0 += 32) {
+            for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                 uint32_t r[32];
                 if (init_row) {
 #pragma unroll
@@ -234,72 +246,55 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             return 1.f;
         };
         {   // initial state
-            float zero_row[1];
-            (void)zero_row;
             const float* init = h0 ? h0 + (((long)b * H + h) * K + row) * V : nullptr;
             if (init) {
                 publish_state(next_dec(0), init);
             } else {
 #pragma unroll 1
-                for (int c0 = 0; c0 < V; c0 += 32) {
+                for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                     uint32_t r[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = 0u;
                     tmem_st32(t_lane + WK_S + c0, r);
                 }
                 tmem_st_wait();
-                for (int i = 0; i < 16; ++i)
-                    *reinterpret_cast<uint4*>(smem + L::sbf + (i >> 3) * 16384 + swz<128>(row, i & 7)) = make_uint4(0, 0, 0, 0);
+                for (int i = 0; i < 8; ++i)
+                    *reinterpret_cast<uint4*>(smem + L::sbf + half * 16384 + swz<128>(row, i)) = make_uint4(0, 0, 0, 0);
             }
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar_sready);
         }
+        // per-row scalars of the chunk: cumsum g and the l2 norm factor (k rows for w lanes, q rows for q lanes)
+        auto load_scalars = [&](int c, float& gg, float& rr) {
+            const int valid = min(64, T - c * 64);
+            const long tok0 = (long)b * T + (long)c * 64;
+            gg = gcs[(tok0 + min(tr, valid - 1)) * H + h];
+            const float* rs = is_q ? qrstd : krstd;
+            rr = (tr < valid) ? rs[(tok0 + tr) * H + h] : 0.f;
+        };
+        float g_cur, r_cur, g_nxt = 0.f, r_nxt = 0.f;
+        load_scalars(0, g_cur, r_cur);
 
         for (int c = 0; c < NT; ++c) {
             const int stg = c & 1;
             const int valid = min(64, T - c * 64);
             const long tok0 = (long)b * T + (long)c * 64;
             unsigned char* stage = smem + stg * L::stage;
-            float* vg = s_vec + stg * 128;
-            float* vr = vg + 64;
-            // chunk vectors (cumsum, key rstd); rows past the end repeat the last valid cumsum
-            if (row < 64) {
-                vg[row] = gcs[(tok0 + min(row, valid - 1)) * H + h];
-            } else {
-                vr[tr] = (tr < valid) ? krstd[(tok0 + tr) * H + h] : 0.f;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (c + 1 < NT) load_scalars(c + 1, g_nxt, r_nxt);          // prefetch; consumed next iteration
             const float carry = m_carry[c];
-            const float gl = vg[valid - 1];
+            const float gl = m_gl[c];
             const bool sel = m_sel[c] != 0;
-            // After a failed (bounded) wait the loop still runs to its end so that every warp keeps meeting the
-            // named barrier above; all remaining work is skipped.
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_full + stg * 8, (c >> 1) & 1, status));   // q tile for rstd_q
-            float rq = 1.f;
-            if (ok && is_q && use_l2norm) {
-                float ss = 0.f;
-#pragma unroll
-                for (int ch = 0; ch < 16; ++ch) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(stage + L::wq + (ch >> 3) * 16384 + swz<128>(row, ch & 7));
-                    const uint32_t* xw = reinterpret_cast<const uint32_t*>(&x);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = unpack_bf16(xw[i]);
-                        ss += f.x * f.x + f.y * f.y;
-                    }
-                }
-                rq = rsqrtf(ss + 1e-6f);
-            }
+            // After a failed (bounded) wait the remaining work is skipped; the loop still runs to its end.
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d1, c & 1, status));
             if (ok) {
                 tc_fence_after();
                 if (!is_q) {
-                    // ---- v' = u - e^{carry} w S ; v'' = v' rstd_k e^{g_last - g}
+                    // ---- v' = u - e^{carry} w S ; v'' = v' rstd_k e^{g_last - g}   (the u tile arrived with the stage)
                     const float ec = __expf(carry);
-                    const float f2 = vr[tr] * __expf(fminf(gl - vg[tr], 80.f));
+                    const float f2 = r_cur * __expf(fminf(gl - g_cur, 80.f));
 #pragma unroll 1
-                    for (int c0 = 0; c0 < V; c0 += 32) {
+                    for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                         uint32_t r[32];
                         tmem_ld32(t_lane + WK_D1 + c0, r);
                         tmem_ld_wait();
@@ -322,45 +317,20 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             *reinterpret_cast<uint4*>(smem + L::vs + off) = make_uint4(b4[0], b4[1], b4[2], b4[3]);
                         }
                     }
-                } else {
-                    // ---- P row: tril(qn kn^T e^{g_i - g_j})
-                    uint32_t r[64];
-                    {
-                        uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
-                        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
-                        tmem_ld32(t_lane + WK_DP, lo);
-                        tmem_ld32(t_lane + WK_DP + 32, hi);
-                        tmem_ld_wait();
-                    }
-                    const float gi = vg[tr];
-                    const int lim = min(tr, valid - 1);
-#pragma unroll
-                    for (int cc = 0; cc < 8; ++cc) {
-                        uint32_t w4[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int j0 = cc * 8 + 2 * i;
-                            float p0 = 0.f, p1 = 0.f;
-                            if (j0 <= lim) p0 = __uint_as_float(r[j0]) * rq * vr[j0] * __expf(gi - vg[j0]);
-                            if (j0 + 1 <= lim) p1 = __uint_as_float(r[j0 + 1]) * rq * vr[j0 + 1] * __expf(gi - vg[j0 + 1]);
-                            w4[i] = pack_bf16(p0, p1);
-                        }
-                        *reinterpret_cast<uint4*>(smem + L::pp + swz<128>(row, cc)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                    }
+                    fence_async_smem();
                 }
-                fence_async_smem();
                 tc_fence_before();
                 mbar_arrive(bar_pv);
-                // ---- o = scale (rstd_q e^{g+carry} q S + P v')   (q rows), after MMA 2 (+3)
+                // ---- o = scale (rstd_q e^{g+carry} q S + P v')   (q rows), after MMA 2
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_d2, c & 1, status));
             }
             if (ok) {
                 tc_fence_after();
                 if (is_q) {
-                    const float fq = rq * __expf(vg[tr] + carry);
+                    const float fq = r_cur * __expf(g_cur + carry);
                     __nv_bfloat16* orow = o + ((tok0 + tr) * H + h) * V;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < V; c0 += 32) {
+                    for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                         uint32_t r1[32], r2[32];
                         tmem_ld32(t_lane + WK_D1 + c0, r1);
                         tmem_ld32(t_lane + WK_D2 + c0, r2);
@@ -381,18 +351,28 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                 }
                 // ---- publish the updated state for the next chunk (and pre-apply the next update's decay)
-                if (sel) publish_state(next_dec(c + 1), nullptr);
-                fence_async_smem();
-                tc_fence_before();
-                mbar_arrive(bar_sready);
+                if (sel) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_s3, c & 1, status));
+                    if (ok) {
+                        tc_fence_after();
+                        publish_state(next_dec(c + 1), nullptr);
+                        fence_async_smem();
+                    }
+                }
+                if (ok) {
+                    tc_fence_before();
+                    mbar_arrive(bar_sready);
+                }
             }
+            g_cur = g_nxt;
+            r_cur = r_nxt;
         }
         if (ok && ht) {
             // every update's decay was pre-applied except after the last one: TMEM holds the final state
             tc_fence_after();
             float* hrow = ht + (((long)b * H + h) * K + row) * V;
 #pragma unroll 1
-            for (int c0 = 0; c0 < V; c0 += 32) {
+            for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(t_lane + WK_S + c0, r);
                 tmem_ld_wait();
@@ -411,19 +391,19 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 }  // namespace natsl
 
-extern "C" int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void* u, const float* gcs,
-                                    const float* k_rstd, const int32_t* types_i, const int32_t* indices,
-                                    const int32_t* n_blocks, const float* h0, void* o, float* ht, int B, int T, int H,
-                                    int HN, int K, int V, int nbs, float scale, int flags, int use_l2norm,
+extern "C" int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void* u, const void* pmat,
+                                    const float* gcs, const float* k_rstd, const float* q_rstd, const int32_t* types_i,
+                                    const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht,
+                                    int B, int T, int H, int HN, int K, int V, int nbs, float scale, int flags,
                                     void* stream) {
     using namespace natsl;
-    NATSL_REQUIRE(q && k && w && u && gcs && k_rstd && types_i && indices && n_blocks && o, NATSL_ERR_NULL,
+    NATSL_REQUIRE(q && k && w && u && pmat && gcs && k_rstd && q_rstd && types_i && indices && n_blocks && o, NATSL_ERR_NULL,
                   "natsl_gdn_walk_fused: null pointer");
     NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && HN > 0 && H % HN == 0, NATSL_ERR_BAD_SHAPE, "natsl_gdn_walk_fused: bad shape");
     NATSL_REQUIRE(K == 128 && V == 128 && nbs == 64, NATSL_ERR_UNSUPPORTED,
                   "natsl_gdn_walk_fused: built for K = V = 128 and nats_block_size = 64 (got K=%d V=%d nbs=%d); use "
                   "natsl_linear_fwd_h + natsl_linear_fwd_o", K, V, nbs);
-    NATSL_REQUIRE((T + 63) / 64 <= 1024, NATSL_ERR_TOO_LARGE, "natsl_gdn_walk_fused: T <= 65536");
+    NATSL_REQUIRE((T + 63) / 64 <= WK_MAX_NT, NATSL_ERR_TOO_LARGE, "natsl_gdn_walk_fused: T <= 65536");
     NATSL_REQUIRE(H <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_gdn_walk_fused: B, H <= 65535");
     auto kern = gdn_walk_tc_kernel<true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WkSmem::total);
@@ -431,18 +411,19 @@ extern "C" int natsl_gdn_walk_fused(const void* q, const void* k, const void* w,
         set_error("natsl_gdn_walk_fused: cannot reserve %d B of shared memory (%s)", WkSmem::total, cudaGetErrorString(e));
         return NATSL_ERR_CUDA;
     }
-    CUtensorMap mw, mq, mk, mu;
+    CUtensorMap mw, mq, mk, mu, mp;
     int rc = encode_bthd_map(&mw, w, B, T, H, K, 64, "natsl_gdn_walk_fused(w)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mq, q, B, T, H, K, 64, "natsl_gdn_walk_fused(q)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T, H, K, 64, "natsl_gdn_walk_fused(k)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mu, u, B, T, H, V, 64, "natsl_gdn_walk_fused(u)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mp, pmat, B, T, H, 64, 64, "natsl_gdn_walk_fused(P)");
     int* status = nullptr;
     if (rc == NATSL_OK) rc = status_word_ptr(&status);
     if (rc != NATSL_OK) return rc;
     const int TN = (T + nbs - 1) / nbs;
     dim3 grid(H, B);
     kern<<<grid, WK_THREADS, WkSmem::total, reinterpret_cast<cudaStream_t>(stream)>>>(
-        mw, mq, mk, mu, gcs, k_rstd, types_i, indices, n_blocks, h0, reinterpret_cast<__nv_bfloat16*>(o), ht, T, H, HN, TN,
-        scale, (flags & NATSL_FLAG_DECAY_SKIPPED) ? 1 : 0, (flags & NATSL_FLAG_NO_TRAILING_QUIRK) ? 0 : 1, use_l2norm, status);
+        mw, mq, mk, mu, mp, gcs, k_rstd, q_rstd, types_i, indices, n_blocks, h0, reinterpret_cast<__nv_bfloat16*>(o), ht, T, H,
+        HN, TN, scale, (flags & NATSL_FLAG_DECAY_SKIPPED) ? 1 : 0, (flags & NATSL_FLAG_NO_TRAILING_QUIRK) ? 0 : 1, status);
     return check_launch("natsl_gdn_walk_fused");
 }

@@ -42,6 +42,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Busy-polling variant of mbar_wait for the latency-critical hand-offs (no suspension inside the instruction).
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 26); ++i)
+        if (mbar_test_wait(bar, parity)) return true;
+    atomicExch(status, 1);
+    return false;
+}
 // Wait with an iteration limit.  On expiry the status word is set and false is returned; callers
 // then skip their remaining work and fall through to the common teardown (never spin forever).
 constexpr int kWaitLimit = 1 << 22;
