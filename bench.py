@@ -399,22 +399,29 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
         dist.init_process_group("nccl", device_id=dev)
     c = MAMBA_LONG
     T, H, K, V, nbs = c["T"], c["H"], c["K"], c["V"], c["nbs"]
-    T_loc = T // world
-    gen = torch.Generator().manual_seed(4000 + rank)
-    x = torch.randn(1, T_loc, H, V, generator=gen)
-    dt = torch.nn.functional.softplus(torch.randn(1, T_loc, H, generator=gen) - 2.0)
+    from neuralattentionsearchlinear_b200.sequence_parallel import segment_ids
+    layout = args.sp_layout if world > 1 else "contiguous"
+    ids = segment_ids(rank, world, layout)
+    n_glob = world * len(ids)
+    L = T // n_glob
     A = -torch.exp(torch.rand(H, generator=torch.Generator().manual_seed(4)) * torch.log(torch.tensor(16.0)))
-    k = torch.randn(1, T_loc, H, K, generator=gen) * K ** -0.5
-    q = torch.randn(1, T_loc, H, K, generator=gen) * K ** -0.5
-    v = (x * dt[..., None]).bfloat16().to(dev)
-    g = (A.view(1, 1, H) * dt).to(dev)
-    q, k = q.bfloat16().to(dev), k.bfloat16().to(dev)
-    logits = torch.randn(1, T_loc // nbs, H, 2, generator=gen)
-    logits[..., 0] += (2.0 ** 0.5) * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(c["p_attn"])).item()
-    types = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
-    if rank == world - 1:
-        types[:, -1] = 1
-    types = types.to(dev)
+    shift = (2.0 ** 0.5) * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(c["p_attn"])).item()
+    parts = {n: [] for n in ("q", "k", "v", "g", "types")}
+    for sid in ids:                                     # every segment is generated from its own seed
+        gen = torch.Generator().manual_seed(4000 + sid)
+        x = torch.randn(1, L, H, V, generator=gen)
+        dt = torch.nn.functional.softplus(torch.randn(1, L, H, generator=gen) - 2.0)
+        parts["k"].append((torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16())
+        parts["q"].append((torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16())
+        parts["v"].append((x * dt[..., None]).bfloat16())
+        parts["g"].append(A.view(1, 1, H) * dt)
+        logits = torch.randn(1, L // nbs, H, 2, generator=gen)
+        logits[..., 0] += shift
+        ty = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
+        if sid == n_glob - 1:
+            ty[:, -1] = 1
+        parts["types"].append(ty)
+    q, k, v, g, types = (torch.cat(parts[n], 1).to(dev) for n in ("q", "k", "v", "g", "types"))
     stream = torch.cuda.current_stream(dev)
 
     def step():
@@ -423,7 +430,7 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
                                              ops_for_incomplete_chunks="all", output_final_state_mamba=True,
                                              decay_for_non_mamba_blocks=True)
         return nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
-                                        decay_for_non_mamba_blocks=True)
+                                        decay_for_non_mamba_blocks=True, layout=layout)
 
     def barrier():
         if dist is not None:
@@ -452,7 +459,7 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                           "data": "synthetic (seeded, generated per rank)",
                           "config": {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 "
-                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} (contiguous segments)"},
+                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({layout} segments)"},
                           "device_status": status}))
     if dist is not None:
         dist.destroy_process_group()
@@ -467,6 +474,8 @@ def main():
     ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (default: the benchmark's 8; "
                     "smaller values are for profiler captures only)")
     ap.add_argument("--min-warm-seconds", type=float, default=1.5, help="minimum warm-up time under load")
+    ap.add_argument("--sp-layout", default="zigzag", choices=["contiguous", "zigzag"],
+                    help="segment layout of the sequence-parallel workload (mamba_long)")
     ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long"],
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
                          "Mamba2 layer, sequence-parallel over the ranks")

@@ -91,13 +91,28 @@ def virtual_attn_types(n_all: torch.Tensor, rank: int, cap: int, types_local: to
     return torch.stack([attn_col, torch.zeros_like(attn_col)], -1).contiguous()
 
 
+def segment_ids(rank: int, world: int, layout: str) -> list:
+    """Global indices of the segments a rank holds, in the order they are laid out in its tensors.
+    'contiguous': one segment per rank.  'zigzag': the sequence is cut into 2*world segments and rank r holds
+    segments r and 2*world-1-r, which balances the softmax branch (a query sees about a fixed fraction of all
+    earlier keys, so late segments are expensive)."""
+    if layout == 'contiguous':
+        return [rank]
+    if layout == 'zigzag':
+        return [rank, 2 * world - 1 - rank]
+    raise ValueError(f"unknown layout {layout!r}")
+
+
 def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g, nats_block_types, *,
                              nats_block_size: int = 256, scale_attn=None, scale_lattn=1.0,
                              ops_for_incomplete_chunks: str = 'all', decay_for_non_mamba_blocks: bool = True,
-                             group=None, backend=None):
+                             layout: str = 'contiguous', group=None, backend=None):
     """One rank's share of ``nats_mixed_attn_mamba`` on a sequence split over the ranks of ``group``.
-    All tensors are this rank's segment ([B, T_local, ...]; block types [B, TN_local, HN, 2]).
-    -> (o_mamba [B,T_local,H,V], o_attn [B,T_local,HQ,V_attn], final_state [B,H,K,V] fp32)."""
+    All tensors hold this rank's segment(s) along the time axis ([B, T_local, ...]; block types
+    [B, TN_local, HN, 2]); with ``layout='zigzag'`` T_local covers the rank's two equally long segments one after
+    the other (see ``segment_ids``).
+    -> (o_mamba [B,T_local,H,V], o_attn [B,T_local,HQ,V_attn], final_state [B,H,K,V] fp32 on the rank that holds
+    the last segment, else None)."""
     if ops_for_incomplete_chunks not in ('all', 'mamba'):
         raise NotImplementedError("only own-block linear attention ('all', 'mamba') is built")
     be = backend or CudaSegmentOps()
@@ -108,42 +123,76 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
     V = v_lattn.shape[-1]
     if scale_attn is None:
         scale_attn = k_attn.shape[-1] ** -0.5
-    if rank < world - 1 and T_loc % max(nbs, 128):
-        raise ValueError("every segment but the last must be a multiple of the block size (and of 128)")
     own = ops_for_incomplete_chunks == 'all'
-    tb = be.tables(nats_block_types, T_loc, nbs)
+    seg = segment_ids(rank, world, layout)
+    n_seg = len(seg)
+    n_glob = world * n_seg
+    last_holder = (n_glob - 1) in seg
+    if n_seg > 1 or not last_holder:
+        if T_loc % (n_seg * max(nbs, 128)):
+            raise ValueError("every segment but the last of the sequence must be a multiple of the block size (and of 128)")
+    if world == 1:
+        tb = be.tables(nats_block_types, T_loc, nbs)
+        o_lin, ht, _ = be.linear(q_lattn, k_lattn, v_lattn, g, tb, scale_lattn, None, decay_for_non_mamba_blocks, False)
+        o_attn = be.attn(q_attn, k_attn, v_attn, tb, scale_attn, own, 0)
+        return o_lin, o_attn, ht
+    L = T_loc // n_seg
+
+    def split(x):                       # [B, n_seg*n, ...] -> [n_seg*B, n, ...]   (segment-major batch)
+        if n_seg == 1:
+            return x.contiguous()
+        n = x.shape[1] // n_seg
+        return x.reshape(B, n_seg, n, *x.shape[2:]).transpose(0, 1).reshape(n_seg * B, n, *x.shape[2:]).contiguous()
+
+    def merge(x):                       # inverse of split
+        if n_seg == 1:
+            return x
+        n = x.shape[1]
+        return x.reshape(n_seg, B, n, *x.shape[2:]).transpose(0, 1).reshape(B, n_seg * n, *x.shape[2:]).contiguous()
+
+    TNs = nats_block_types.shape[1] // n_seg
+    types_s = split(nats_block_types) if n_seg > 1 else nats_block_types.contiguous()
+    assert types_s.shape[1] == TNs
+    qa, ka, va, ql, kl, vl, gs = (split(x) for x in (q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g))
+    tb = be.tables(types_s, L, nbs)
+    # global order of the gathered segments: entry [r', j] of a gathered [world, n_seg, ...] array is segment
+    # segment_ids(r', world, layout)[j]; `order` lists (r', j) flat indices by increasing global segment index
+    flat_ids = [sid for r in range(world) for sid in segment_ids(r, world, layout)]
+    order = sorted(range(n_glob), key=lambda i: flat_ids[i])
+
+    def to_global(x_all):               # [world, n_seg*B, ...] -> [n_glob, B, ...] in sequence order
+        y = x_all.reshape(world * n_seg, B, *x_all.shape[2:])
+        return y[torch.tensor(order, device=y.device)].contiguous()
 
     # ---- linear branch
-    if world == 1:
-        o_lin, ht, _ = be.linear(q_lattn, k_lattn, v_lattn, g, tb, scale_lattn, None, decay_for_non_mamba_blocks, False)
-    else:
-        _, S_loc, gcs = be.linear(q_lattn, k_lattn, v_lattn, g, tb, scale_lattn, None, decay_for_non_mamba_blocks, True)
-        a, trail = be.segment_decay(gcs, tb, decay_for_non_mamba_blocks)
-        S_end = (S_loc * trail[..., None, None]).contiguous()
-        a_all, S_all = _all_gather(a, world, group), _all_gather(S_end, world, group)
-        h_in = be.state_combine(a_all, S_all, rank)
-        o_lin, ht, _ = be.linear(q_lattn, k_lattn, v_lattn, g, tb, scale_lattn, h_in, decay_for_non_mamba_blocks, False)
+    _, S_loc, gcs = be.linear(ql, kl, vl, gs, tb, scale_lattn, None, decay_for_non_mamba_blocks, True)
+    a, trail = be.segment_decay(gcs, tb, decay_for_non_mamba_blocks)
+    S_end = (S_loc * trail[..., None, None]).contiguous()
+    a_glob, S_glob = to_global(_all_gather(a, world, group)), to_global(_all_gather(S_end, world, group))
+    h_in = torch.cat([be.state_combine(a_glob, S_glob, sid) for sid in seg], 0)          # [n_seg*B, H, K, V]
+    o_lin, ht, _ = be.linear(ql, kl, vl, gs, tb, scale_lattn, h_in, decay_for_non_mamba_blocks, False)
+    final = ht[(seg.index(n_glob - 1)) * B:(seg.index(n_glob - 1) + 1) * B] if last_holder else None
 
     # ---- softmax branch
-    if world == 1:
-        o_attn = be.attn(q_attn, k_attn, v_attn, tb, scale_attn, own, 0)
+    n_loc = be.n_attn_blocks(tb)                                                         # [n_seg*B, HN]
+    n_glob_t = to_global(_all_gather(n_loc, world, group))                               # [n_glob, B, HN]
+    cap = int(n_glob_t[:n_glob - 1].max().item())            # one host sync: capacity of the gather
+    step = max(1, 128 // nbs)
+    cap = -(-cap // step) * step                             # keep the query offset a multiple of 128
+    if cap == 0:
+        o_attn = be.attn(qa, ka, va, tb, scale_attn, own, 0)
     else:
-        n_loc = be.n_attn_blocks(tb)
-        n_all = _all_gather(n_loc, world, group)
-        cap = int(n_all[:world - 1].max().item()) if world > 1 else 0       # one host sync: capacity of the gather
-        step = max(1, 128 // nbs)
-        cap = -(-cap // step) * step                                          # keep the query offset a multiple of 128
-        if cap == 0:
-            o_attn = be.attn(q_attn, k_attn, v_attn, tb, scale_attn, own, 0)
-        else:
-            k_pack, v_pack = be.pack(k_attn.contiguous(), tb, cap), be.pack(v_attn.contiguous(), tb, cap)
-            k_all, v_all = _all_gather(k_pack, world, group), _all_gather(v_pack, world, group)
-            # [R, B, cap*nbs, H, D] -> [B, R*cap*nbs, H, D], own keys behind
-            cat = lambda allp, own_x: torch.cat([allp.permute(1, 0, 2, 3, 4).reshape(B, world * cap * nbs, *own_x.shape[2:]),
-                                                 own_x], 1).contiguous()
-            k_virt, v_virt = cat(k_all, k_attn), cat(v_all, v_attn)
-            types_virt = virtual_attn_types(n_all.to(torch.int64), rank, cap, nats_block_types)
-            q_off = world * cap * nbs
-            tb_v = be.tables(types_virt, q_off + T_loc, nbs)
-            o_attn = be.attn(q_attn, k_virt, v_virt, tb_v, scale_attn, own, q_off)
-    return o_lin, o_attn, (ht if rank == world - 1 else None)
+        k_glob = to_global(_all_gather(be.pack(ka, tb, cap), world, group))              # [n_glob, B, cap*nbs, H, D]
+        v_glob = to_global(_all_gather(be.pack(va, tb, cap), world, group))
+        q_off = n_glob * cap * nbs
+        flat = lambda x: x.permute(1, 0, 2, 3, 4).reshape(B, q_off, *x.shape[3:])
+        k_rem, v_rem = flat(k_glob), flat(v_glob)
+        outs = []
+        for j, sid in enumerate(seg):
+            sl = slice(j * B, (j + 1) * B)
+            k_virt, v_virt = torch.cat([k_rem, ka[sl]], 1).contiguous(), torch.cat([v_rem, va[sl]], 1).contiguous()
+            types_virt = virtual_attn_types(n_glob_t.to(torch.int64), sid, cap, types_s[sl])
+            tb_v = be.tables(types_virt, q_off + L, nbs)
+            outs.append(be.attn(qa[sl].contiguous(), k_virt, v_virt, tb_v, scale_attn, own, q_off))
+        o_attn = torch.cat(outs, 0)
+    return merge(o_lin), merge(o_attn), final

@@ -31,7 +31,7 @@ def _inputs(B, T, H, K, V, nbs, seed):
     return q, k, v, g, types
 
 
-def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret):
+def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret, layout="contiguous"):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -39,13 +39,22 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret):
         from tests.sp_helpers import OracleSegmentOps
         q, k, v, g, types = _inputs(B, T, H, K, V, nbs, seed)
         TN = types.shape[1]
-        per = -(-TN // world)                      # blocks per rank (the last rank takes the rest, maybe ragged)
-        b0, b1 = rank * per, min(TN, (rank + 1) * per)
-        sl = slice(b0 * nbs, min(T, b1 * nbs))
-        o_l, o_a, ht = nats_mixed_attn_mamba_sp(q[:, sl], k[:, sl], v[:, sl], q[:, sl], k[:, sl], v[:, sl], g[:, sl],
-                                                types[:, b0:b1].contiguous(), nats_block_size=nbs,
-                                                decay_for_non_mamba_blocks=decay, backend=OracleSegmentOps())
-        ret[rank] = (o_l, o_a, ht)
+        if layout == "contiguous":
+            per = -(-TN // world)                  # blocks per rank (the last rank takes the rest, maybe ragged)
+            b0, b1 = rank * per, min(TN, (rank + 1) * per)
+            tsel = torch.arange(b0 * nbs, min(T, b1 * nbs))
+            bsel = torch.arange(b0, b1)
+        else:
+            from neuralattentionsearchlinear_b200.sequence_parallel import segment_ids
+            per = TN // (2 * world)                # blocks per segment
+            ids = segment_ids(rank, world, "zigzag")
+            tsel = torch.cat([torch.arange(s * per * nbs, (s + 1) * per * nbs) for s in ids])
+            bsel = torch.cat([torch.arange(s * per, (s + 1) * per) for s in ids])
+        c = lambda x: x[:, tsel].contiguous()
+        o_l, o_a, ht = nats_mixed_attn_mamba_sp(c(q), c(k), c(v), c(q), c(k), c(v), c(g), types[:, bsel].contiguous(),
+                                                nats_block_size=nbs, decay_for_non_mamba_blocks=decay, layout=layout,
+                                                backend=OracleSegmentOps())
+        ret[rank] = (o_l, o_a, ht, tsel)
     finally:
         dist.destroy_process_group()
 
@@ -61,13 +70,31 @@ def test_sp_matches_single_process_oracle(world, T, nbs, decay):
                                          use_l2norm=False, rule="mamba")
     mask = oattn.attn_mask(types[..., 0], T, nbs, H)
     oa_ref, _ = oattn.attn_sdpa(q, k, v, mask)
-    o_l = torch.cat([ret[r][0] for r in range(world)], 1)
-    o_a = torch.cat([ret[r][1] for r in range(world)], 1)
-    assert (o_l - o_ref).abs().max() < 1e-9
-    assert (o_a - oa_ref).abs().max() < 1e-9
-    # the final state is defined when the last block is selected (the layers force it)
-    assert ret[world - 1][2] is not None and all(ret[r][2] is None for r in range(world - 1))
-    assert (ret[world - 1][2] - s_ref).abs().max() < 1e-9
+    _check(ret, world, o_ref, oa_ref, s_ref, holder=world - 1)
+
+
+def _check(ret, world, o_ref, oa_ref, s_ref, holder):
+    for r in range(world):
+        o_l, o_a, ht, tsel = ret[r]
+        assert (o_l - o_ref[:, tsel]).abs().max() < 1e-9
+        assert (o_a - oa_ref[:, tsel]).abs().max() < 1e-9
+        # the final state is defined when the last block is selected (the layers force it)
+        assert (ht is not None) == (r == holder)
+    assert (ret[holder][2] - s_ref).abs().max() < 1e-9
+
+
+@pytest.mark.parametrize("world,T,nbs", [(2, 1024, 128), (3, 1536, 128)])
+def test_sp_zigzag_matches_single_process_oracle(world, T, nbs):
+    B, H, K, V, seed = 2, 2, 16, 8, 5
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, True, seed, ret, "zigzag"), nprocs=world, join=True)
+    q, k, v, g, types = _inputs(B, T, H, K, V, nbs, seed)
+    o_ref, s_ref = ogdn.linear_recurrent(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=True,
+                                         use_l2norm=False, rule="mamba")
+    mask = oattn.attn_mask(types[..., 0], T, nbs, H)
+    oa_ref, _ = oattn.attn_sdpa(q, k, v, mask)
+    _check(ret, world, o_ref, oa_ref, s_ref, holder=0)          # rank 0 holds segments 0 and 2*world-1
 
 
 def test_virtual_types_layout():
