@@ -425,12 +425,13 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
     stream = torch.cuda.current_stream(dev)
 
     def step():
-        if world == 1:
+        if args.sp_plain_op and world == 1:               # the layer's plain op: serial recurrence over the whole sequence
             return nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5, nats_block_size=nbs,
                                              ops_for_incomplete_chunks="all", output_final_state_mamba=True,
                                              decay_for_non_mamba_blocks=True)
         return nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
-                                        decay_for_non_mamba_blocks=True, layout=layout)
+                                        decay_for_non_mamba_blocks=True, layout=layout,
+                                        linear_splits=args.sp_linear_splits or None)
 
     def barrier():
         if dist is not None:
@@ -476,6 +477,10 @@ def main():
     ap.add_argument("--min-warm-seconds", type=float, default=1.5, help="minimum warm-up time under load")
     ap.add_argument("--sp-layout", default="zigzag", choices=["contiguous", "zigzag"],
                     help="segment layout of the sequence-parallel workload (mamba_long)")
+    ap.add_argument("--sp-linear-splits", type=int, default=0,
+                    help="sub-segments per segment in the linear branch of mamba_long (0: about 1024 tokens each)")
+    ap.add_argument("--sp-plain-op", action="store_true",
+                    help="mamba_long on one GPU through nats_mixed_attn_mamba (no sub-segment split, one stream)")
     ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long"],
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
                          "Mamba2 layer, sequence-parallel over the ranks")

@@ -83,6 +83,15 @@ int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t
                       const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int Tq, int q_off, int HQ,
                       int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream);
 
+/* Same, with the T keys held in two pairs of tensors: keys [0, k_split) in k_rem, v_rem [B_rem, k_split, HKV, .]
+ * (batch index b % B_rem: blocks gathered from other segments, shared by the B / B_rem local segments that sit
+ * segment-major in the batch), keys [k_split, T) in k, v [B, T - k_split, HKV, .].  k_split is a multiple of nbs
+ * and <= q_off; k_split = 0 ignores k_rem, v_rem.  No reference counterpart (sequence parallelism). */
+int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
+                         const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse,
+                         int B, int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV, int HN, int DK, int DV,
+                         int nbs, float scale, int flags, void* stream);
+
 /* Debug/parity: dense 0/1 mask [B,HQ,T,T] (uint8) from the same tile walk as natsl_attn_fwd.
  * Counterpart: store_msk=True of the reference kernel, src/nats/ops/attns/attns.py:214-217,
  * 321-323, 1495-1498. */
@@ -104,7 +113,8 @@ int natsl_gdn_chunk_prep(const void* k, const void* v, const float* g, const voi
                          void* stream);
 
 /* State recurrence.  h [B,cdiv(T,64),H,K,V] bf16 = the state each chunk reads; carry
- * [B,cdiv(T,64),H] fp32 = decay of skipped blocks before each chunk; ht [B,H,K,V] fp32 or NULL;
+ * [B,cdiv(T,64),H] fp32 = decay of skipped blocks before each chunk (h and carry may both be NULL when only
+ * the final state is wanted); ht [B,H,K,V] fp32 or NULL;
  * h0 [B,H,K,V] fp32 or NULL.  For NATSL_RULE_MAMBA pass w = NULL, u = v, k_rstd = NULL.
  * Replaces: chunk_gated_delta_rule_nats_fwd_h src/nats/ops/common/chunk_delta_h.py:638-732
  * (kernel :40-324), chunk_mamaba_nats_fwd_h src/nats/ops/mamba/chunk_h.py:220-290 (kernel :35-218)
@@ -114,13 +124,14 @@ int natsl_linear_fwd_h(int rule, const void* k, const void* w, const void* u, co
                        void* h, float* carry, float* ht, int B, int T, int H, int HN, int K, int V, int nbs, int flags,
                        void* stream);
 
-/* Output of every chunk, o [B,T,H,V] bf16.
+/* Output of every chunk, o [B,T,H,V] bf16.  mode: bit 0 = l2-normalise q (k through k_rstd); bit 1 = leave out
+ * the own-chunk term, o = scale e^{g} q S only (ops_for_incomplete_chunks='attn', chunk_o.py:210-211).
  * Replaces: l2norm_fwd(q) src/nats/ops/mixed_ops/mixed_attn_gdn.py:119-120; chunk_fwd_nats_o
  * src/nats/ops/common/chunk_o.py:1176-1259 (kernel :35-215); chunk_mamba_fwd_nats_o
  * src/nats/ops/mamba/chunk_o.py:200-277 (kernel :34-198). */
 int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, const void* u, const float* gcs,
                        const float* k_rstd, const void* h, const float* carry, void* o, int B, int T, int H, int K,
-                       int V, float scale, int use_l2norm, void* stream);
+                       int V, float scale, int mode, void* stream);
 
 /* Chunk preparation that also emits what the fused walk needs: q_rstd [B,T,H] fp32 and the intra-chunk score
  * matrix P = tril(qn kn^T e^{gcs_i - gcs_j}) [B,T,H,64] bf16 (q, q_rstd, pmat may all be NULL = natsl_gdn_chunk_prep).
@@ -161,12 +172,17 @@ int natsl_attn_fwd_fp32(int dtype, const void* q, const void* k, const void* v, 
  *   trail [B,H] = exp(log decay of the skipped blocks after the last selected block).
  * natsl_sp_state_combine: h_in [B,H,K,V] = sum_{r<rank} (prod_{r<r'<rank} a[r']) S[r] from the all-gathered
  *   a [world,B,H], S [world,B,H,K,V] (fp32).
+ * natsl_sp_prefix_states: for N consecutive segments (a [N,B,H], S [N,B,H,K,V] fp32) and the state h0 [B,H,K,V]
+ *   (or NULL = zero) the first one starts from: P[0] = h0, P[i+1] = a[i] P[i] + S[i]; writes prefix [N,B,H,K,V] = P[0..N)
+ *   (or NULL), total_S [B,H,K,V] = P[N] (or NULL) and total_a [B,H] = prod a (or NULL).
  * natsl_pack_selected_blocks: packed [B, cap_blocks*nbs, H, D] <- the selected blocks (column `op`) of
- *   x [B,T,H,D] bf16 in index-table order, per head. */
+ *   x [B,T,H,D] bf16 in index-table order, per head; slots past the number of selected blocks are left untouched. */
 int natsl_sp_segment_decay(const float* gcs, const int32_t* types_i, float* a, float* trail, int B, int T, int H,
                            int HN, int nbs, int flags, void* stream);
 int natsl_sp_state_combine(const float* a, const float* S, float* h_in, int rank, int world, int B, int H, int K, int V,
                            void* stream);
+int natsl_sp_prefix_states(const float* a, const float* S, const float* h0, float* prefix, float* total_S,
+                           float* total_a, int N, int B, int H, int K, int V, void* stream);
 int natsl_pack_selected_blocks(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
                                int T, int H, int HN, int D, int nbs, int op, int cap_blocks, void* stream);
 

@@ -34,6 +34,24 @@ def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mm
     return o, lse
 
 
+def attn_fwd_split(q, k_rem, v_rem, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
+    """Softmax branch over a key sequence held in two parts: keys [0, S) in k_rem, v_rem [B_rem, S, HKV, .] (shared by
+    the B / B_rem segments that sit segment-major in the batch of q, k, v) and keys [S, S+L) in k, v [B, L, HKV, .];
+    the queries q [B, L, HQ, DK] are the tokens [S, S+L).  -> o [B, L, HQ, DV] bf16."""
+    for t_ in (q, k_rem, v_rem, k, v):
+        _need(t_.dtype == BF16 and t_.is_contiguous(), "softmax branch needs contiguous bf16 tensors", TypeError)
+    B, L, HQ, DK = q.shape
+    B_rem, S, HKV, DV = v_rem.shape
+    _need(tables.T == S + L, f"tables were built for T={tables.T}, keys have T={S + L}")
+    o = torch.empty(B, L, HQ, DV, dtype=BF16, device=q.device)
+    lse = torch.empty(B, L, HQ, dtype=torch.float32, device=q.device)
+    _lib.call("natsl_attn_fwd_split", q.data_ptr(), k_rem.data_ptr(), v_rem.data_ptr(), k.data_ptr(), v.data_ptr(),
+              tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(),
+              lse.data_ptr(), B, B_rem, S + L, L, S, S, HQ, HKV, tables.types_i.shape[2], DK, DV, tables.nats_block_size,
+              float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0, current_stream_ptr(q.device))
+    return o
+
+
 def attn_dense_mask(tables: SelectionTables, HQ: int, own_chunk: bool) -> torch.Tensor:
     """Debug: the dense boolean mask [B,HQ,T,T] the attention kernel realises."""
     B, TN, HN, _ = tables.types_i.shape
@@ -91,14 +109,15 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
                   tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht),
                   B, T, H, HN, K, V, nbs, float(scale), flags, st)
         return o, ht, None
-    h = torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
-    carry = torch.empty(B, NT, H, dtype=torch.float32, device=dev)
+    state_only = skip_out and ht is not None and not return_intermediates
+    h = None if state_only else torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
+    carry = None if state_only else torch.empty(B, NT, H, dtype=torch.float32, device=dev)
     _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krstd),
               tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
-              h.data_ptr(), carry.data_ptr(), _lib.ptr(ht), B, T, H, HN, K, V, nbs, flags, st)
+              _lib.ptr(h), _lib.ptr(carry), _lib.ptr(ht), B, T, H, HN, K, V, nbs, flags, st)
     inter = dict(w=w, u=u, gcs=gcs, k_rstd=krstd, h=h, carry=carry) if return_intermediates else None
     if skip_out:
-        return None, ht, inter
+        return None, ht, (inter or dict(gcs=gcs))
     o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
     _lib.call("natsl_linear_fwd_o", rule, q.data_ptr(), k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(),
               _lib.ptr(krstd), h.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V, float(scale),

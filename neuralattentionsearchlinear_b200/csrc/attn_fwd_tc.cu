@@ -66,12 +66,15 @@ __device__ __forceinline__ int pack_tile(const TileWalk& w, int j, const int* id
 template <int DK, int DV>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ types_i,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kr,
+                   const __grid_constant__ CUtensorMap map_vr, int k_split, int B_rem, const int* __restrict__ types_i,
                    const int* __restrict__ indices, const int* __restrict__ attn_n_iters,
                    __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int Tq, int q_off, int HQ, int HKV,
                    int HN, int TN, int nbs, float scale_log2, int own_chunk, int* status) {
     // T = number of keys (and the length the tables were built for); the Tq queries are the tokens
     // [q_off, q_off + Tq) of that sequence (q_off = 0, Tq = T except under sequence parallelism).
+    // Keys [0, k_split) live in a second pair of tensors (map_kr / map_vr, batch index b % B_rem: the
+    // gathered blocks of other segments, shared by the local segments), keys [k_split, T) in map_k / map_v.
     using L = TcSmem<DK, DV>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -130,12 +133,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             prefetch_tensormap(&map_q);
             prefetch_tensormap(&map_k);
             prefetch_tensormap(&map_v);
+            if (k_split > 0) {
+                prefetch_tensormap(&map_kr);
+                prefetch_tensormap(&map_vr);
+            }
             mbar_expect_tx(bar_q, 128 * DK * 2);
 #pragma unroll
             for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
         }
         // K and V rings advance independently: whichever ring has a free stage gets its next tile.
         int jk = 0, jv = 0, idle = 0;
+        const int b_rem = b % B_rem;
         while (jk < n_tiles || jv < n_tiles) {
             bool progressed = false;
             if (jk < n_tiles) {
@@ -145,11 +153,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (ready) {
                     if (lane == 0) {
                         const int s0 = tile_desc(jk) & 0x3FFFFFFF;
+                        const bool rem = s0 < k_split;
+                        const CUtensorMap* mk = rem ? &map_kr : &map_k;
+                        const int ts = rem ? s0 : s0 - k_split, bs = rem ? b_rem : b;
                         const uint32_t full = bar_k_full + stg * 8;
                         mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
                         for (int sub = 0; sub < DK / 64; ++sub)
-                            tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv, s0, b, full);
+                            tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hkv, ts, bs, full);
                     }
                     ++jk;
                     progressed = true;
@@ -162,18 +173,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (ready) {
                     if (lane == 0) {
                         const int s0 = tile_desc(jv) & 0x3FFFFFFF;
+                        const bool rem = s0 < k_split;
                         const uint32_t full = bar_v_full + stg * 8;
                         mbar_expect_tx(full, 64 * DV * 2);
 #pragma unroll
                         for (int sub = 0; sub < DV / 64; ++sub)
-                            tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv, s0, b, full);
+                            tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, hkv,
+                                        rem ? s0 : s0 - k_split, rem ? b_rem : b, full);
                         // warm L2 for the tile this ring will want next
                         if (jv + TC_VST < n_tiles) {
                             const int s1 = tile_desc(jv + TC_VST) & 0x3FFFFFFF;
+                            const bool rem1 = s1 < k_split;
+                            const int t1 = rem1 ? s1 : s1 - k_split, b1 = rem1 ? b_rem : b;
 #pragma unroll
-                            for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(&map_v, sub * 64, hkv, s1, b);
+                            for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, hkv, t1, b1);
 #pragma unroll
-                            for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(&map_k, sub * 64, hkv, s1, b);
+                            for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, hkv, t1, b1);
                         }
                     }
                     ++jv;
@@ -383,9 +398,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 template <int DK, int DV>
-static int launch_attn_tc(const void* q, const void* k, const void* v, const int* types_i, const int* indices,
-                          const int* n_iters, void* o, float* lse, int B, int T, int Tq, int q_off, int HQ, int HKV,
-                          int HN, int nbs, float scale, int own_chunk, cudaStream_t st) {
+static int launch_attn_tc(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
+                          const int* types_i, const int* indices, const int* n_iters, void* o, float* lse, int B,
+                          int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV, int HN, int nbs, float scale,
+                          int own_chunk, cudaStream_t st) {
     using L = TcSmem<DK, DV>;
     auto kern = attn_fwd_tc_kernel<DK, DV>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
@@ -393,16 +409,25 @@ static int launch_attn_tc(const void* q, const void* k, const void* v, const int
         set_error("natsl_attn_fwd: cannot reserve %d B of shared memory (%s)", L::total, cudaGetErrorString(e));
         return NATSL_ERR_CUDA;
     }
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mkr, mvr;
     int rc = encode_bthd_map(&mq, q, B, Tq, HQ, DK, 128, "natsl_attn_fwd(q)");
-    if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T, HKV, DK, 64, "natsl_attn_fwd(k)");
-    if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T, HKV, DV, 64, "natsl_attn_fwd(v)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T - k_split, HKV, DK, 64, "natsl_attn_fwd(k)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T - k_split, HKV, DV, 64, "natsl_attn_fwd(v)");
+    if (k_split > 0) {
+        if (rc == NATSL_OK) rc = encode_bthd_map(&mkr, k_rem, B_rem, k_split, HKV, DK, 64, "natsl_attn_fwd(k_rem)");
+        if (rc == NATSL_OK) rc = encode_bthd_map(&mvr, v_rem, B_rem, k_split, HKV, DV, 64, "natsl_attn_fwd(v_rem)");
+    } else {
+        mkr = mk;
+        mvr = mv;
+        B_rem = B;
+    }
     int* status = nullptr;
     if (rc == NATSL_OK) rc = status_word_ptr(&status);
     if (rc != NATSL_OK) return rc;
     const int NTq = (Tq + ATT_BM - 1) / ATT_BM, TN = (T + nbs - 1) / nbs;
     dim3 grid(NTq, HQ, B);
-    kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, types_i, indices, n_iters, reinterpret_cast<__nv_bfloat16*>(o),
+    kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, mkr, mvr, k_split, B_rem, types_i, indices, n_iters,
+                                             reinterpret_cast<__nv_bfloat16*>(o),
                                              lse, T, Tq, q_off, HQ, HKV, HN, TN, nbs, scale * 1.44269504f, own_chunk,
                                              status);
     return check_launch("natsl_attn_fwd");
@@ -410,10 +435,10 @@ static int launch_attn_tc(const void* q, const void* k, const void* v, const int
 
 }  // namespace natsl
 
-extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t* types_i,
-                                 const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B,
-                                 int T, int Tq, int q_off, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
-                                 int flags, void* stream) {
+extern "C" int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
+                                    const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters, void* o,
+                                    float* lse, int B, int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV,
+                                    int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(q && k && v && types_i && indices && attn_n_iters && o && lse, NATSL_ERR_NULL,
                   "natsl_attn_fwd: null pointer");
@@ -426,15 +451,21 @@ extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, co
                   "natsl_attn_fwd: nats_block_size must be a multiple of 64 (got %d)", nbs);
     NATSL_REQUIRE(q_off % 128 == 0 && q_off % nbs == 0, NATSL_ERR_UNSUPPORTED,
                   "natsl_attn_fwd: the query offset must be a multiple of 128 and of nats_block_size (got %d)", q_off);
+    NATSL_REQUIRE(k_split >= 0 && k_split <= q_off && k_split % nbs == 0, NATSL_ERR_BAD_SHAPE,
+                  "natsl_attn_fwd: the key split %d must be a multiple of nats_block_size and <= the query offset %d",
+                  k_split, q_off);
+    NATSL_REQUIRE(k_split == 0 || (k_rem && v_rem && B_rem > 0 && B % B_rem == 0), NATSL_ERR_BAD_SHAPE,
+                  "natsl_attn_fwd: a key split needs k_rem, v_rem and a batch B_rem that divides B");
     const int own = (flags & NATSL_FLAG_ATTN_OWN_CHUNK) ? 1 : 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (flags & NATSL_FLAG_ATTN_MMA_SYNC) {
-        NATSL_REQUIRE(q_off == 0 && Tq == T, NATSL_ERR_UNSUPPORTED,
-                      "natsl_attn_fwd: the mma.sync comparison kernel has no query offset");
+        NATSL_REQUIRE(q_off == 0 && Tq == T && k_split == 0, NATSL_ERR_UNSUPPORTED,
+                      "natsl_attn_fwd: the mma.sync comparison kernel has no query offset or key split");
         return attn_fwd_mma_sync(q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, DK, DV, nbs, scale,
                                  own, st);
     }
-#define NATSL_ATT_ARGS q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, Tq, q_off, HQ, HKV, HN, nbs, scale, own, st
+#define NATSL_ATT_ARGS \
+    q, k_rem, v_rem, k, v, types_i, indices, attn_n_iters, o, lse, B, B_rem, T, Tq, q_off, k_split, HQ, HKV, HN, nbs, scale, own, st
     if (DK == 64 && DV == 64) return launch_attn_tc<64, 64>(NATSL_ATT_ARGS);
     if (DK == 64 && DV == 128) return launch_attn_tc<64, 128>(NATSL_ATT_ARGS);
     if (DK == 128 && DV == 64) return launch_attn_tc<128, 64>(NATSL_ATT_ARGS);
@@ -442,6 +473,14 @@ extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, co
 #undef NATSL_ATT_ARGS
     set_error("natsl_attn_fwd: unsupported head dims DK=%d DV=%d (each 64 or 128)", DK, DV);
     return NATSL_ERR_UNSUPPORTED;
+}
+
+extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t* types_i,
+                                 const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B,
+                                 int T, int Tq, int q_off, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
+                                 int flags, void* stream) {
+    return natsl_attn_fwd_split(q, nullptr, nullptr, k, v, types_i, indices, attn_n_iters, o, lse, B, B, T, Tq, q_off, 0,
+                                HQ, HKV, HN, DK, DV, nbs, scale, flags, stream);
 }
 
 extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,

@@ -31,7 +31,11 @@ linear_out_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ u,
                   const float* __restrict__ gcs, const float* __restrict__ krstd, const __nv_bfloat16* __restrict__ hin,
                   const float* __restrict__ carry_in, __nv_bfloat16* __restrict__ o, int T, int H, int V, float scale,
-                  int use_l2norm) {
+                  int mode) {
+    // mode bit 0: l2-normalise q (and k through k_rstd); bit 1: no own-chunk term (P = 0), the mode in which only
+    // the softmax branch covers the current chunk (chunk_o.py:210-211)
+    const int use_l2norm = mode & 1;
+    const bool own = !(mode & 2);
     using L = OutSmem<K, VB, GDN>;
     constexpr int NH = VB / 16;          // n-tiles per warp (half of the block's columns)
     extern __shared__ __align__(128) unsigned char smem[];
@@ -122,7 +126,7 @@ linear_out_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                 int i = (e >> 1) ? ib : ia;
                 int j = nt * 8 + qd * 2 + (e & 1);
                 float val = 0.f;
-                if (i >= j && j < valid)
+                if (own && i >= j && j < valid)
                     val = acc[nt][e] * ((e >> 1) ? qb : qa) * s_kr[j] * __expf(((e >> 1) ? gb : ga) - s_g[j]);
                 pv[e] = val;
             }
@@ -207,7 +211,7 @@ linear_out_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
 template <int K, int VB, bool GDN>
 static int launch_out(const void* q, const void* k, const void* w, const void* u, const float* gcs, const float* krstd,
                       const void* hin, const float* carry, void* o, int B, int T, int H, int V, float scale,
-                      int use_l2norm, cudaStream_t st) {
+                      int mode, cudaStream_t st) {
     using L = OutSmem<K, VB, GDN>;
     auto kern = linear_out_kernel<K, VB, GDN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
@@ -221,7 +225,7 @@ static int launch_out(const void* q, const void* k, const void* w, const void* u
         reinterpret_cast<const __nv_bfloat16*>(q), reinterpret_cast<const __nv_bfloat16*>(k),
         reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<const __nv_bfloat16*>(u), gcs, krstd,
         reinterpret_cast<const __nv_bfloat16*>(hin), carry, reinterpret_cast<__nv_bfloat16*>(o), T, H, V, scale,
-        use_l2norm);
+        mode);
     return check_launch("natsl_linear_fwd_o");
 }
 
@@ -229,7 +233,7 @@ static int launch_out(const void* q, const void* k, const void* w, const void* u
 
 extern "C" int natsl_linear_fwd_o(int rule, const void* q, const void* k, const void* w, const void* u,
                                   const float* gcs, const float* k_rstd, const void* h, const float* carry, void* o,
-                                  int B, int T, int H, int K, int V, float scale, int use_l2norm, void* stream) {
+                                  int B, int T, int H, int K, int V, float scale, int mode, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(q && k && u && gcs && h && carry && o, NATSL_ERR_NULL, "natsl_linear_fwd_o: null pointer");
     NATSL_REQUIRE(rule == NATSL_RULE_GDN || rule == NATSL_RULE_MAMBA, NATSL_ERR_UNSUPPORTED,
@@ -239,7 +243,7 @@ extern "C" int natsl_linear_fwd_o(int rule, const void* q, const void* k, const 
     NATSL_REQUIRE(B <= 65535 && (long)H * (V / 64 + 1) <= 65535, NATSL_ERR_TOO_LARGE,
                   "natsl_linear_fwd_o: grid too large (B=%d H=%d)", B, H);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define NATSL_OUT_ARGS q, k, w, u, gcs, k_rstd, h, carry, o, B, T, H, V, scale, use_l2norm, st
+#define NATSL_OUT_ARGS q, k, w, u, gcs, k_rstd, h, carry, o, B, T, H, V, scale, mode, st
     const bool gdn = rule == NATSL_RULE_GDN;
     if (K == 128 && V % 128 == 0) return gdn ? launch_out<128, 128, true>(NATSL_OUT_ARGS) : launch_out<128, 128, false>(NATSL_OUT_ARGS);
     if (K == 128 && V % 64 == 0) return gdn ? launch_out<128, 64, true>(NATSL_OUT_ARGS) : launch_out<128, 64, false>(NATSL_OUT_ARGS);

@@ -171,21 +171,23 @@ linear_scan_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __r
             blk_g = 0.f;
         }
         if (dirty) {
-            __syncthreads();
+            __syncthreads();                   // every warp is done with the k tile of the previous active chunk
+            if (GDN || hout) {                 // bf16 copy of the state: read by the w S product and the h store
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int nt = 0; nt < NTL; ++nt) {
-                    int r = krow0 + mt * 16 + gq;
-                    *reinterpret_cast<uint32_t*>(sb_p + swz<BV * 2>(r, nt) + q * 4) = pack_bf16(S[mt][nt][0], S[mt][nt][1]);
-                    *reinterpret_cast<uint32_t*>(sb_p + swz<BV * 2>(r + 8, nt) + q * 4) =
-                        pack_bf16(S[mt][nt][2], S[mt][nt][3]);
-                }
-            __syncthreads();
+                    for (int nt = 0; nt < NTL; ++nt) {
+                        int r = krow0 + mt * 16 + gq;
+                        *reinterpret_cast<uint32_t*>(sb_p + swz<BV * 2>(r, nt) + q * 4) = pack_bf16(S[mt][nt][0], S[mt][nt][1]);
+                        *reinterpret_cast<uint32_t*>(sb_p + swz<BV * 2>(r + 8, nt) + q * 4) =
+                            pack_bf16(S[mt][nt][2], S[mt][nt][3]);
+                    }
+                __syncthreads();
+            }
             dirty = false;
         }
-        store_tile<K, BV, SCAN_THREADS>(sb_p, hout + ((((long)b * NT + c) * H + h) * K) * V + v0, V, K, tid);
-        if (vsplit == 0 && tid == 0) carry_out[((long)b * NT + c) * H + h] = carry;
+        if (hout) store_tile<K, BV, SCAN_THREADS>(sb_p, hout + ((((long)b * NT + c) * H + h) * K) * V + v0, V, K, tid);
+        if (carry_out && vsplit == 0 && tid == 0) carry_out[((long)b * NT + c) * H + h] = carry;
         const float gl = s_gl[c];
         blk_g += gl;
 
@@ -331,8 +333,9 @@ extern "C" int natsl_linear_fwd_h(int rule, const void* k, const void* w, const 
                                   const int32_t* n_blocks, const float* h0, void* h, float* carry, float* ht, int B,
                                   int T, int H, int HN, int K, int V, int nbs, int flags, void* stream) {
     using namespace natsl;
-    NATSL_REQUIRE(k && u && gcs && types_i && indices && n_blocks && h && carry, NATSL_ERR_NULL,
-                  "natsl_linear_fwd_h: null pointer");
+    NATSL_REQUIRE(k && u && gcs && types_i && indices && n_blocks, NATSL_ERR_NULL, "natsl_linear_fwd_h: null pointer");
+    NATSL_REQUIRE((h && carry) || ((!h && !carry) && ht), NATSL_ERR_NULL,
+                  "natsl_linear_fwd_h: h and carry are given together, or both NULL with ht set");
     NATSL_REQUIRE(rule == NATSL_RULE_GDN || rule == NATSL_RULE_MAMBA, NATSL_ERR_UNSUPPORTED,
                   "natsl_linear_fwd_h: unknown rule %d", rule);
     NATSL_REQUIRE(rule != NATSL_RULE_GDN || w, NATSL_ERR_NULL, "natsl_linear_fwd_h: w is required for the delta rule");

@@ -95,6 +95,6 @@ extern "C" int natsl_gdn_fwd_noalloc(const void* q, const void* k, const void* v
     rc = natsl_linear_fwd_h(NATSL_RULE_GDN, k, w, u, gcs, krstd, types_i, indices, n_blocks, h0, h, carry, ht, B, T, H,
                             HN, K, V, nbs, flags, stream);
     if (rc != NATSL_OK) return rc;
-    return natsl_linear_fwd_o(NATSL_RULE_GDN, q, k, w, u, gcs, krstd, h, carry, o, B, T, H, K, V, scale, use_l2norm,
+    return natsl_linear_fwd_o(NATSL_RULE_GDN, q, k, w, u, gcs, krstd, h, carry, o, B, T, H, K, V, scale, use_l2norm ? 1 : 0,
                               stream);
 }

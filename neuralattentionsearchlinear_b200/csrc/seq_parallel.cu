@@ -52,6 +52,24 @@ __global__ void state_combine_kernel(const float* __restrict__ a, const float* _
     h_in[i] = acc;
 }
 
+// P[0] = h0 (or 0), P[i+1] = a[i] * P[i] + S[i]: exclusive prefixes, the total state and the total decay.
+__global__ void prefix_states_kernel(const float* __restrict__ a, const float* __restrict__ S, const float* __restrict__ h0,
+                                     float* __restrict__ prefix, float* __restrict__ total_S, float* __restrict__ total_a,
+                                     int N, long bh, long kv) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= bh * kv) return;
+    const long g = i / kv;
+    float p = h0 ? h0[i] : 0.f, f = 1.f;
+    for (int n = 0; n < N; ++n) {
+        if (prefix) prefix[(long)n * bh * kv + i] = p;
+        const float an = a[(long)n * bh + g];
+        p = an * p + S[(long)n * bh * kv + i];
+        f *= an;
+    }
+    if (total_S) total_S[i] = p;
+    if (total_a && i % kv == 0) total_a[g] = f;
+}
+
 // packed[b, j*nbs + i, h, :] = x[b, idx[b,j,hn,op]*nbs + i, h, :]   for j < min(n_sel, cap)
 __global__ void __launch_bounds__(256)
 pack_blocks_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ indices, const int* __restrict__ n_blocks,
@@ -95,6 +113,17 @@ extern "C" int natsl_sp_state_combine(const float* a, const float* S, float* h_i
     state_combine_kernel<<<(unsigned)((bh * kv + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         a, S, h_in, rank, bh, kv);
     return check_launch("natsl_sp_state_combine");
+}
+
+extern "C" int natsl_sp_prefix_states(const float* a, const float* S, const float* h0, float* prefix, float* total_S,
+                                      float* total_a, int N, int B, int H, int K, int V, void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(a && S, NATSL_ERR_NULL, "natsl_sp_prefix_states: null pointer");
+    NATSL_REQUIRE(N > 0 && B > 0 && H > 0 && K > 0 && V > 0, NATSL_ERR_BAD_SHAPE, "natsl_sp_prefix_states: bad shape");
+    const long bh = (long)B * H, kv = (long)K * V;
+    prefix_states_kernel<<<(unsigned)((bh * kv + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        a, S, h0, prefix, total_S, total_a, N, bh, kv);
+    return check_launch("natsl_sp_prefix_states");
 }
 
 extern "C" int natsl_pack_selected_blocks(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed,

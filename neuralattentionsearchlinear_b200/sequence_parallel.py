@@ -1,22 +1,32 @@
-"""Sequence-parallel NAtSL-Mamba2 hybrid attention for long sequences (one contiguous segment of the sequence
-per rank, in rank order; every segment but the last a multiple of the block size).
+"""Sequence-parallel NAtSL-Mamba2 hybrid attention for long sequences.
 
-Linear branch: the carried state obeys ``h_out = a * h_in + S_loc`` over a segment (scalar decay), so each rank
-  1. runs the recurrence on its segment from a zero state            -> S_loc, a
-  2. all-gathers (a, S_loc) (a few MB) and folds the earlier ranks   -> h_in
-  3. reruns recurrence + output from h_in.
-Softmax branch: a rank needs only the *selected* key/value blocks of earlier ranks; they are packed per head,
-all-gathered, and placed in front of the rank's own keys, and the attention kernel runs on that virtual sequence
-with the query window set to the rank's own tokens.
+The sequence is cut into segments; a rank holds one segment ('contiguous') or two ('zigzag': segments r and
+2R-1-r of 2R, which balances the softmax branch).  Every segment but the last of the sequence is a multiple of
+the block size.
 
-The reference has no sequence parallelism; results equal the single-device op on the whole sequence with the
-decay carried over all skipped blocks (the layers always select the last block, where the reference's handling
-of trailing skipped blocks makes no difference).
+Linear branch: over a segment the carried state obeys ``h_out = a * h_in + S_loc`` (scalar decay), so
+  1. every segment is cut further into short sub-segments that run side by side as batch entries (the
+     recurrence is serial over chunks, so this is also what keeps one GPU busy at batch 1), each from a zero
+     state                                                                        -> S_loc, a per sub-segment
+  2. the sub-segments of a segment are folded locally, the per-segment (a, S) pairs (a few MB) are all-gathered
+     and folded over the earlier segments                                         -> h_in of every sub-segment
+  3. recurrence + output are rerun from h_in.
+Softmax branch: a segment needs only the *selected* key/value blocks of earlier segments; they are packed per
+head and all-gathered, and the attention kernel reads its keys from two places: the gathered buffer (shared by
+the rank's segments) and the segment's own keys, with the query window set to the segment's own tokens.
+
+The two branches run on two streams; the one host read (the capacity of the key/value gather) happens while
+the linear branch is already enqueued.  The reference has no sequence parallelism; results equal the
+single-device op on the whole sequence with the decay carried over all skipped blocks (the layers always
+select the last block, where the reference's handling of trailing skipped blocks makes no difference).
 
 The collectives are ``torch.distributed`` (NCCL on GPUs); everything else goes through ``backend`` — the CUDA
 ops by default.
 """
 from __future__ import annotations
+
+import contextlib
+import functools
 
 import torch
 import torch.distributed as dist
@@ -24,17 +34,25 @@ import torch.distributed as dist
 from . import _lib, _ops
 from .nats_util import build_selection_tables, current_stream_ptr
 
+_side_streams: dict = {}
+
 
 class CudaSegmentOps:
     """Compute steps of one rank, on the CUDA kernels of this package."""
+
+    def side_stream(self, device):
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in _side_streams:
+            _side_streams[idx] = torch.cuda.Stream(device=idx)
+        return _side_streams[idx]
 
     def tables(self, types, T, nbs):
         return build_selection_tables(types, T, nbs)
 
     def linear(self, q, k, v, g, tables, scale, h0, decay, skip_out):
         o, ht, inter = _ops.linear_fwd(_lib.RULE_MAMBA, q, k, v, g, None, tables, scale, h0, decay, False, True,
-                                       trailing_quirk=False, return_intermediates=True, skip_out=skip_out)
-        return o, ht, inter['gcs']
+                                       trailing_quirk=False, skip_out=skip_out)
+        return o, ht, (inter['gcs'] if inter else None)
 
     def segment_decay(self, gcs, tables, decay):
         B, T, H = gcs.shape
@@ -53,10 +71,21 @@ class CudaSegmentOps:
                   current_stream_ptr(S_all.device))
         return h_in
 
+    def prefix_states(self, a, S, h0, want_prefix):
+        N, B, H, K, V = S.shape
+        dev = S.device
+        prefix = torch.empty_like(S) if want_prefix else None
+        tot_S = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
+        tot_a = torch.empty(B, H, dtype=torch.float32, device=dev)
+        _lib.call("natsl_sp_prefix_states", a.data_ptr(), S.data_ptr(), _lib.ptr(h0), _lib.ptr(prefix), tot_S.data_ptr(),
+                  tot_a.data_ptr(), N, B, H, K, V, current_stream_ptr(dev))
+        return prefix, tot_S, tot_a
+
     def pack(self, x, tables, cap_blocks):
         B, T, H, D = x.shape
         nbs = tables.nats_block_size
-        packed = torch.zeros(B, cap_blocks * nbs, H, D, dtype=x.dtype, device=x.device)
+        # slots past a head's number of selected blocks stay unwritten: they are never selected in the virtual sequence
+        packed = torch.empty(B, cap_blocks * nbs, H, D, dtype=x.dtype, device=x.device)
         _lib.call("natsl_pack_selected_blocks", x.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
                   packed.data_ptr(), B, T, H, tables.types_i.shape[2], D, nbs, 0, cap_blocks,
                   current_stream_ptr(x.device))
@@ -64,6 +93,9 @@ class CudaSegmentOps:
 
     def attn(self, q, k, v, tables, scale, own_chunk, q_off):
         return _ops.attn_fwd(q, k, v, tables, scale, own_chunk, q_off=q_off)[0]
+
+    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk):
+        return _ops.attn_fwd_split(q, k_rem, v_rem, k, v, tables, scale, own_chunk)
 
     def n_attn_blocks(self, tables):
         return tables.n_blocks[..., 0].contiguous()          # [B, HN] int32
@@ -75,20 +107,6 @@ def _all_gather(x: torch.Tensor, world: int, group) -> torch.Tensor:
     out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(out, x, group=group)
     return out.view((world,) + tuple(x.shape))
-
-
-def virtual_attn_types(n_all: torch.Tensor, rank: int, cap: int, types_local: torch.Tensor) -> torch.Tensor:
-    """Block types of the virtual key sequence [world x cap gathered slots | own blocks].
-    n_all [world, B, HN]: softmax-selected block counts of every rank.  Slot j of rank r' is selected iff
-    r' < rank and j < n_all[r'].  The linear column is unused by the softmax branch and left zero."""
-    R, B, HN = n_all.shape
-    dev = types_local.device
-    j = torch.arange(cap, device=dev).view(1, 1, cap, 1)
-    earlier = (torch.arange(R, device=dev) < rank).view(R, 1, 1, 1)
-    sel = (j < n_all.view(R, B, 1, HN)) & earlier                              # [R,B,cap,HN]
-    remote = sel.permute(1, 0, 2, 3).reshape(B, R * cap, HN).to(types_local.dtype)
-    attn_col = torch.cat([remote, types_local[..., 0]], 1)
-    return torch.stack([attn_col, torch.zeros_like(attn_col)], -1).contiguous()
 
 
 def segment_ids(rank: int, world: int, layout: str) -> list:
@@ -103,14 +121,71 @@ def segment_ids(rank: int, world: int, layout: str) -> list:
     raise ValueError(f"unknown layout {layout!r}")
 
 
+@functools.lru_cache(maxsize=None)
+def _layout_constants(world: int, layout: str, device_str: str):
+    """(global id of every gathered segment [world*n_seg] in gathered order, permutation gathered -> sequence order)."""
+    flat_ids = [sid for r in range(world) for sid in segment_ids(r, world, layout)]
+    order = sorted(range(len(flat_ids)), key=lambda i: flat_ids[i])
+    dev = torch.device(device_str)
+    return torch.tensor(flat_ids, device=dev), torch.tensor(order, device=dev)
+
+
+def virtual_attn_types(n_all: torch.Tensor, gathered_ids: torch.Tensor, my_ids, cap: int,
+                       types_local: torch.Tensor) -> torch.Tensor:
+    """Block types of the virtual key sequences [G x cap gathered slots | own blocks] of the rank's segments.
+    n_all [G, B, HN]: softmax-selected block counts of every gathered segment (gathered order); gathered_ids [G]:
+    their global segment index; my_ids: global indices of the n local segments; types_local [n*B, TN, HN, 2]
+    (segment-major batch).  Slot j of gathered segment g is selected for local segment i iff
+    gathered_ids[g] < my_ids[i] and j < n_all[g].  The linear column is unused by the softmax branch (zero)."""
+    G, B, HN = n_all.shape
+    dev = types_local.device
+    n = len(my_ids)
+    mine = torch.tensor(list(my_ids), device=dev).view(n, 1, 1, 1, 1)
+    slot = torch.arange(cap, device=dev).view(1, 1, 1, cap, 1)
+    vis = gathered_ids.to(dev).view(1, 1, G, 1, 1) < mine
+    sel = vis & (slot < n_all.permute(1, 0, 2).reshape(1, B, G, 1, HN))                  # [n,B,G,cap,HN]
+    remote = sel.reshape(n * B, G * cap, HN).to(types_local.dtype)
+    attn_col = torch.cat([remote, types_local[..., 0]], 1)
+    return torch.stack([attn_col, torch.zeros_like(attn_col)], -1).contiguous()
+
+
+def pick_linear_splits(L: int, nbs: int, target_tokens: int = 1024) -> int:
+    """Number of equal sub-segments (multiples of the block size and of 128 tokens) a segment of L tokens is cut
+    into for the linear branch; 1 for a ragged segment."""
+    unit = max(nbs, 128)
+    if L % unit:
+        return 1
+    best = 1
+    for s in range(1, L // unit + 1):
+        if L % (s * unit) == 0 and L // s >= target_tokens:
+            best = s
+    return best
+
+
+def _split(x, B, n):                    # [B, n*m, ...] -> [n*B, m, ...]   (segment-major batch)
+    if n == 1:
+        return x.contiguous()
+    m = x.shape[1] // n
+    return x.reshape(B, n, m, *x.shape[2:]).transpose(0, 1).reshape(n * B, m, *x.shape[2:]).contiguous()
+
+
+def _merge(x, B, n):                    # inverse of _split
+    if n == 1:
+        return x
+    m = x.shape[1]
+    return x.reshape(n, B, m, *x.shape[2:]).transpose(0, 1).reshape(B, n * m, *x.shape[2:]).contiguous()
+
+
 def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g, nats_block_types, *,
                              nats_block_size: int = 256, scale_attn=None, scale_lattn=1.0,
                              ops_for_incomplete_chunks: str = 'all', decay_for_non_mamba_blocks: bool = True,
-                             layout: str = 'contiguous', group=None, backend=None):
-    """One rank's share of ``nats_mixed_attn_mamba`` on a sequence split over the ranks of ``group``.
+                             layout: str = 'contiguous', linear_splits=None, group=None, backend=None):
+    """One rank's share of ``nats_mixed_attn_mamba`` on a sequence split over the ranks of ``group`` (also usable
+    with a single rank, where only the sub-segment split of the linear branch remains).
     All tensors hold this rank's segment(s) along the time axis ([B, T_local, ...]; block types
     [B, TN_local, HN, 2]); with ``layout='zigzag'`` T_local covers the rank's two equally long segments one after
-    the other (see ``segment_ids``).
+    the other (see ``segment_ids``).  ``linear_splits``: sub-segments per segment in the linear branch (default:
+    about 1024 tokens each).
     -> (o_mamba [B,T_local,H,V], o_attn [B,T_local,HQ,V_attn], final_state [B,H,K,V] fp32 on the rank that holds
     the last segment, else None)."""
     if ops_for_incomplete_chunks not in ('all', 'mamba'):
@@ -120,10 +195,11 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     nbs = nats_block_size
     B, T_loc, H, K = q_lattn.shape
-    V = v_lattn.shape[-1]
+    dev = q_lattn.device
     if scale_attn is None:
         scale_attn = k_attn.shape[-1] ** -0.5
     own = ops_for_incomplete_chunks == 'all'
+    decay = decay_for_non_mamba_blocks
     seg = segment_ids(rank, world, layout)
     n_seg = len(seg)
     n_glob = world * n_seg
@@ -131,68 +207,97 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
     if n_seg > 1 or not last_holder:
         if T_loc % (n_seg * max(nbs, 128)):
             raise ValueError("every segment but the last of the sequence must be a multiple of the block size (and of 128)")
-    if world == 1:
-        tb = be.tables(nats_block_types, T_loc, nbs)
-        o_lin, ht, _ = be.linear(q_lattn, k_lattn, v_lattn, g, tb, scale_lattn, None, decay_for_non_mamba_blocks, False)
-        o_attn = be.attn(q_attn, k_attn, v_attn, tb, scale_attn, own, 0)
-        return o_lin, o_attn, ht
     L = T_loc // n_seg
-
-    def split(x):                       # [B, n_seg*n, ...] -> [n_seg*B, n, ...]   (segment-major batch)
-        if n_seg == 1:
-            return x.contiguous()
-        n = x.shape[1] // n_seg
-        return x.reshape(B, n_seg, n, *x.shape[2:]).transpose(0, 1).reshape(n_seg * B, n, *x.shape[2:]).contiguous()
-
-    def merge(x):                       # inverse of split
-        if n_seg == 1:
-            return x
-        n = x.shape[1]
-        return x.reshape(n_seg, B, n, *x.shape[2:]).transpose(0, 1).reshape(B, n_seg * n, *x.shape[2:]).contiguous()
-
-    TNs = nats_block_types.shape[1] // n_seg
-    types_s = split(nats_block_types) if n_seg > 1 else nats_block_types.contiguous()
-    assert types_s.shape[1] == TNs
-    qa, ka, va, ql, kl, vl, gs = (split(x) for x in (q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g))
-    tb = be.tables(types_s, L, nbs)
-    # global order of the gathered segments: entry [r', j] of a gathered [world, n_seg, ...] array is segment
-    # segment_ids(r', world, layout)[j]; `order` lists (r', j) flat indices by increasing global segment index
-    flat_ids = [sid for r in range(world) for sid in segment_ids(r, world, layout)]
-    order = sorted(range(n_glob), key=lambda i: flat_ids[i])
+    s_lin = int(linear_splits) if linear_splits else pick_linear_splits(L, nbs)
+    if s_lin > 1 and L % (s_lin * max(nbs, 128)):
+        raise ValueError(f"linear_splits={s_lin} does not cut a {L}-token segment into multiples of the block size")
+    n_sub = n_seg * s_lin
+    gathered_ids, order = _layout_constants(world, layout, str(dev))
 
     def to_global(x_all):               # [world, n_seg*B, ...] -> [n_glob, B, ...] in sequence order
         y = x_all.reshape(world * n_seg, B, *x_all.shape[2:])
-        return y[torch.tensor(order, device=y.device)].contiguous()
+        return y if layout == 'contiguous' else y[order].contiguous()
 
-    # ---- linear branch
-    _, S_loc, gcs = be.linear(ql, kl, vl, gs, tb, scale_lattn, None, decay_for_non_mamba_blocks, True)
-    a, trail = be.segment_decay(gcs, tb, decay_for_non_mamba_blocks)
-    S_end = (S_loc * trail[..., None, None]).contiguous()
-    a_glob, S_glob = to_global(_all_gather(a, world, group)), to_global(_all_gather(S_end, world, group))
-    h_in = torch.cat([be.state_combine(a_glob, S_glob, sid) for sid in seg], 0)          # [n_seg*B, H, K, V]
-    o_lin, ht, _ = be.linear(ql, kl, vl, gs, tb, scale_lattn, h_in, decay_for_non_mamba_blocks, False)
-    final = ht[(seg.index(n_glob - 1)) * B:(seg.index(n_glob - 1) + 1) * B] if last_holder else None
+    side = be.side_stream(dev) if hasattr(be, 'side_stream') else None
+    cur = torch.cuda.current_stream(dev) if side is not None else None
+    on_side = (lambda: torch.cuda.stream(side)) if side is not None else contextlib.nullcontext
+    made_on_side = []
 
-    # ---- softmax branch
-    n_loc = be.n_attn_blocks(tb)                                                         # [n_seg*B, HN]
-    n_glob_t = to_global(_all_gather(n_loc, world, group))                               # [n_glob, B, HN]
-    cap = int(n_glob_t[:n_glob - 1].max().item())            # one host sync: capacity of the gather
-    step = max(1, 128 // nbs)
-    cap = -(-cap // step) * step                             # keep the query offset a multiple of 128
+    # ---- softmax branch, part 1 (main stream): per-segment tables and the selected-block counts of every segment
+    types_s = _split(nats_block_types, B, n_seg)
+    qa, ka, va = (_split(x, B, n_seg) for x in (q_attn, k_attn, v_attn))
+    tb = be.tables(types_s, L, nbs)
+    if side is not None:
+        side.wait_stream(cur)
+    if world > 1:
+        n_all = _all_gather(be.n_attn_blocks(tb), world, group)                          # [world, n_seg*B, HN]
+
+    # ---- linear branch, part 1 (side stream): every sub-segment from a zero state, folded per segment
+    with on_side():
+        types_l = _split(nats_block_types, B, n_sub)
+        ql, kl, vl, gl = (_split(x, B, n_sub) for x in (q_lattn, k_lattn, v_lattn, g))
+        tbl = tb if n_sub == n_seg else be.tables(types_l, L // s_lin, nbs)
+        if world > 1 or s_lin > 1:
+            _, S_loc, gcs = be.linear(ql, kl, vl, gl, tbl, scale_lattn, None, decay, True)
+            a, trail = be.segment_decay(gcs, tbl, decay)
+            S_end = S_loc * trail[..., None, None]
+            a_sub = a.view(n_seg, s_lin, B, H)
+            S_sub = S_end.view(n_seg, s_lin, B, H, K, -1)
+            if s_lin > 1:
+                tot = [be.prefix_states(a_sub[j], S_sub[j], None, False) for j in range(n_seg)]
+                S_seg = torch.stack([t[1] for t in tot]).reshape(n_seg * B, H, K, -1)
+                a_seg = torch.stack([t[2] for t in tot]).reshape(n_seg * B, H)
+            else:
+                S_seg, a_seg = S_end, a
+
+    # ---- softmax branch, part 2 (main stream): gather the selected blocks, one attention launch for all segments
+    cap = 0
+    if world > 1:
+        cap = int(n_all.max().item())                        # the one host read: capacity of the gather
+        step = max(1, 128 // nbs)
+        cap = -(-cap // step) * step                         # keeps the query offset a multiple of 128
     if cap == 0:
         o_attn = be.attn(qa, ka, va, tb, scale_attn, own, 0)
     else:
-        k_glob = to_global(_all_gather(be.pack(ka, tb, cap), world, group))              # [n_glob, B, cap*nbs, H, D]
-        v_glob = to_global(_all_gather(be.pack(va, tb, cap), world, group))
-        q_off = n_glob * cap * nbs
-        flat = lambda x: x.permute(1, 0, 2, 3, 4).reshape(B, q_off, *x.shape[3:])
-        k_rem, v_rem = flat(k_glob), flat(v_glob)
-        outs = []
-        for j, sid in enumerate(seg):
-            sl = slice(j * B, (j + 1) * B)
-            k_virt, v_virt = torch.cat([k_rem, ka[sl]], 1).contiguous(), torch.cat([v_rem, va[sl]], 1).contiguous()
-            types_virt = virtual_attn_types(n_glob_t.to(torch.int64), sid, cap, types_s[sl])
-            tb_v = be.tables(types_virt, q_off + L, nbs)
-            outs.append(be.attn(qa[sl].contiguous(), k_virt, v_virt, tb_v, scale_attn, own, q_off))
-        o_attn = torch.cat(outs, 0)
-    return merge(o_lin), merge(o_attn), final
+        k_all = _all_gather(be.pack(ka, tb, cap), world, group)                          # [world, n_seg*B, cap*nbs, H, D]
+        v_all = _all_gather(be.pack(va, tb, cap), world, group)
+        S_rem = n_glob * cap * nbs
+
+        def flat(x):                    # -> [B, n_glob*cap*nbs, H, D], gathered order (a view when B = 1)
+            x = x.reshape(n_glob, B, cap * nbs, *x.shape[3:])
+            return x.permute(1, 0, 2, 3, 4).reshape(B, S_rem, *x.shape[3:]).contiguous()
+
+        types_virt = virtual_attn_types(n_all.reshape(n_glob, B, -1).to(torch.int64), gathered_ids, seg, cap, types_s)
+        tb_v = be.tables(types_virt, S_rem + L, nbs)
+        o_attn = be.attn_split(qa, flat(k_all), flat(v_all), ka, va, tb_v, scale_attn, own)
+
+    # ---- linear branch, part 2 (side stream): fold the earlier segments, rerun from the true starting states
+    with on_side():
+        if world > 1 or s_lin > 1:
+            if world > 1:
+                a_glob, S_glob = to_global(_all_gather(a_seg, world, group)), to_global(_all_gather(S_seg, world, group))
+                h_seg = [be.state_combine(a_glob, S_glob, sid) for sid in seg]           # state each segment starts from
+            else:
+                h_seg = [None] * n_seg
+            if s_lin > 1:
+                h_in = torch.cat([be.prefix_states(a_sub[j], S_sub[j], h_seg[j], True)[0] for j in range(n_seg)], 0)
+                h_in = h_in.reshape(n_sub * B, H, K, -1)
+            else:
+                h_in = torch.cat(h_seg, 0)
+        else:
+            h_in = None
+        o_lin, ht, _ = be.linear(ql, kl, vl, gl, tbl, scale_lattn, h_in, decay, False)
+        final = None
+        if last_holder:
+            j = seg.index(n_glob - 1)
+            e = (j * s_lin + s_lin - 1) * B
+            final = ht[e:e + B]
+        o_lin = _merge(o_lin, B, n_sub)
+        made_on_side = [o_lin] + ([final] if final is not None else [])
+    if side is not None:
+        cur.wait_stream(side)
+        for t_ in made_on_side:
+            t_.record_stream(cur)
+        for t_ in (q_lattn, k_lattn, v_lattn, g, nats_block_types):
+            t_.record_stream(side)
+    return o_lin, _merge(o_attn, B, n_seg), final

@@ -40,6 +40,14 @@ self-consistent (its own notes: src/nats/ops/gated_delta_rule/chunk.py:47-50);
 the chunk form here follows the token recurrence instead: the 64-token sub-chunks
 of an unselected block update a temporary state that is rolled back at the end
 of the block.
+
+``own_chunk=False`` is the mode in which only the softmax branch covers the current
+chunk (``ops_for_incomplete_chunks='attn'``, src/nats/ops/mixed_ops/mixed_attn_gdn.py:35-42,86):
+the output keeps just the state term, o = scale * e^{g} q S with S the state after the
+most recent selected 64-token chunk (src/nats/ops/common/chunk_o.py:210-211), and the
+selection acts per 64-token chunk (every chunk of a selected block updates the state,
+chunks of an unselected block only decay it), which is how the reference's chunk
+kernels walk in this mode (chunk_delta_h.py:189-324 iterates selected chunks).
 """
 from __future__ import annotations
 
@@ -59,8 +67,14 @@ def _expand_sel(sel: torch.Tensor, H: int) -> torch.Tensor:
     return sel.to(torch.bool).repeat_interleave(H // HN, dim=2)          # [B,TN,H]
 
 
+def _per_chunk_selection(sel, nbs, T):
+    """[B,TN,HN] per block -> [B,NT,HN] per 64-token chunk."""
+    NT = -(-T // CHUNK)
+    return sel.repeat_interleave(nbs // CHUNK, dim=1)[:, :NT]
+
+
 def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=True,
-                     use_l2norm=True, rule="gdn"):
+                     use_l2norm=True, rule="gdn", own_chunk=True):
     """Token recurrence with re-roll.  Returns (o [B,T,H,V], final_state [B,H,K,V]).
 
     final_state is the state at the end of the last selected block (what the
@@ -73,6 +87,8 @@ def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=T
         scale = K ** -0.5
     if use_l2norm:
         q, k = l2norm(q), l2norm(k)
+    if not own_chunk:
+        sel, nbs = _per_chunk_selection(sel, nbs, T), CHUNK
     selh = _expand_sel(sel, H)
     S = torch.zeros(B, H, K, V, dtype=dt) if h0 is None else h0.to(dt).clone()
     S0 = S.clone()
@@ -89,7 +105,8 @@ def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=T
         else:
             vt = v[:, t]
         S = S + kt[..., :, None] * vt[..., None, :]
-        o[:, t] = torch.einsum("bhkv,bhk->bhv", S, q[:, t] * scale)
+        S_read = S if own_chunk else S0 * gsum.exp()[..., None, None]      # chunk-start state, decayed to t
+        o[:, t] = torch.einsum("bhkv,bhk->bhv", S_read, q[:, t] * scale)
         if (t + 1) % nbs == 0 or t == T - 1:
             m = selh[:, t // nbs][..., None, None]
             rolled = S0 * gsum.exp()[..., None, None] if decay else S0
@@ -102,7 +119,7 @@ def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=T
 
 def linear_chunk(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=True,
                  use_l2norm=True, rule="gdn", reference_trailing_carry=True,
-                 return_intermediates=False):
+                 return_intermediates=False, own_chunk=True):
     """Chunk form (64-token compute chunks).  Same returns as ``linear_recurrent``;
     with ``return_intermediates`` also a dict of per-chunk tensors:
     gcs [B,T,H] (chunk-local cumsum), k_rstd [B,T,H], w [B,T,H,K], u [B,T,H,V]
@@ -114,6 +131,8 @@ def linear_chunk(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=True,
     dt = q.dtype
     C = CHUNK
     assert nbs % C == 0
+    if not own_chunk:
+        sel, nbs = _per_chunk_selection(sel, nbs, T), C
     cpb = nbs // C
     if scale is None:
         scale = K ** -0.5
@@ -177,8 +196,9 @@ def linear_chunk(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=True,
         carry_all[:, c] = carry
         ec = carry.exp()[..., None, None]
         vprime = u[:, :, c] - ec * (w[:, :, c] @ S)                      # chunk_delta_h.py:218-234 / chunk_o.py:167-171,206-208
-        o[:, :, c] = scale * ((gc[:, :, c] + carry[..., None]).exp()[..., None] * (qc[:, :, c] @ S)
-                              + P[:, :, c] @ vprime)                     # chunk_o.py:173,186,209
+        o[:, :, c] = scale * (gc[:, :, c] + carry[..., None]).exp()[..., None] * (qc[:, :, c] @ S)
+        if own_chunk:
+            o[:, :, c] = o[:, :, c] + scale * (P[:, :, c] @ vprime)        # chunk_o.py:173,186,209 (else :210-211)
         gl = gL[:, :, c]
         if rule == "gdn":
             kdec = (gl[..., None] - gc[:, :, c]).exp()                   # chunk_delta_h.py:252

@@ -49,6 +49,22 @@ class OracleSegmentOps:
             f = f * a_all[r]
         return h_in
 
+    def prefix_states(self, a, S, h0, want_prefix):
+        p = torch.zeros_like(S[0]) if h0 is None else h0.clone()
+        f = torch.ones_like(a[0])
+        pre = []
+        for n in range(S.shape[0]):
+            pre.append(p.clone())
+            p = a[n][..., None, None] * p + S[n]
+            f = f * a[n]
+        return (torch.stack(pre) if want_prefix else None), p, f
+
+    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk):
+        rep = q.shape[0] // k_rem.shape[0]                 # the gathered keys are shared by the local segments
+        k_virt = torch.cat([k_rem.repeat(rep, 1, 1, 1), k], 1)
+        v_virt = torch.cat([v_rem.repeat(rep, 1, 1, 1), v], 1)
+        return self.attn(q, k_virt, v_virt, tables, scale, own_chunk, k_rem.shape[1])
+
     def pack(self, x, tables, cap_blocks):
         B, T, H, D = x.shape
         nbs = tables.nats_block_size

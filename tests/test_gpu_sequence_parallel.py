@@ -1,5 +1,6 @@
 """Sequence-parallel Mamba2 hybrid attention on 2 GPUs (NCCL): every rank's share against the single-GPU op on
-the whole sequence (which the other GPU tests check against the oracle).  Skipped with fewer than 2 GPUs."""
+the whole sequence (which the other GPU tests check against the oracle); skipped with fewer than 2 GPUs.
+On one GPU: the sub-segment split of the linear branch and the two-source attention entry point."""
 import os
 import socket
 
@@ -20,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, B, T, H, K, V, nbs, layout, ret):
+def _worker(rank, world, port, B, T, H, K, V, nbs, layout, splits, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
@@ -39,7 +40,8 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, layout, ret):
         c = lambda x: x.to(dev).contiguous()
         o_l, o_a, ht = nats_mixed_attn_mamba_sp(c(q[:, sl]), c(k[:, sl]), c(v[:, sl]), c(q[:, sl]), c(k[:, sl]), c(v[:, sl]),
                                                 c(g[:, sl]), c(types[:, bsel]), nats_block_size=nbs,
-                                                scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout)
+                                                scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
+                                                linear_splits=splits)
         torch.cuda.synchronize()
         # single-GPU op on the whole sequence, on this rank's GPU
         r_l, r_a, r_ht = nat.nats_mixed_attn_mamba(c(q), c(k), c(v), c(q), c(k), c(v), None, c(g), c(types), None,
@@ -57,15 +59,15 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, layout, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("T,nbs,layout", [(4096, 256, "contiguous"), (2048, 64, "contiguous"), (4096, 256, "zigzag"),
-                                          (2048, 128, "zigzag")])
-def test_sp_two_gpus_matches_single_gpu(T, nbs, layout):
+@pytest.mark.parametrize("B,T,nbs,layout,splits", [(1, 4096, 256, "contiguous", None), (1, 2048, 64, "contiguous", 1),
+                                                   (1, 4096, 256, "zigzag", None), (2, 2048, 128, "zigzag", 2)])
+def test_sp_two_gpus_matches_single_gpu(B, T, nbs, layout, splits):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    world, B, H, K, V = 2, 1, 4, 128, 64
+    world, H, K, V = 2, 4, 128, 64
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, layout, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, layout, splits, ret), nprocs=world, join=True)
     for r in range(world):
         err_l, err_a, err_h, mag, status = ret[r]
         assert status == 0
@@ -73,3 +75,52 @@ def test_sp_two_gpus_matches_single_gpu(T, nbs, layout):
         assert err_l <= 2e-2 * max(1.0, mag), (r, err_l)
         assert err_a <= 2e-2 * max(1.0, mag), (r, err_a)
         assert err_h <= 2e-2 * max(1.0, mag), (r, err_h)
+
+
+@pytest.mark.parametrize("B,T,nbs,splits,decay", [(1, 8192, 256, 8, True), (2, 2048, 64, 4, False), (1, 4096, 128, None, True)])
+def test_sub_segment_split_matches_plain_op(B, T, nbs, splits, decay):
+    """One GPU, no process group: the linear branch cut into sub-segments against the plain op."""
+    import neuralattentionsearchlinear_b200 as nat
+    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200.sequence_parallel import nats_mixed_attn_mamba_sp
+    H, K, V = 4, 128, 64
+    dev = torch.device("cuda", 0)
+    q, k, v, g, _ = synth_mamba_inputs(B, T, H, K, V, seed=17)
+    types = otab.synth_types(B, T // nbs, H, 0.2, seed=18)
+    types[:, -1] = 1
+    q, k, v, g, types = (x.to(dev) for x in (q, k, v, g, types))
+    o_l, o_a, ht = nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
+                                            decay_for_non_mamba_blocks=decay, linear_splits=splits)
+    r_l, r_a, r_ht = nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5,
+                                               nats_block_size=nbs, ops_for_incomplete_chunks='all',
+                                               output_final_state_mamba=True, decay_for_non_mamba_blocks=decay)
+    torch.cuda.synchronize()
+    mag = max(1.0, r_l.float().abs().max().item())
+    assert (o_l.float() - r_l.float()).abs().max().item() <= 2e-2 * mag
+    assert torch.equal(o_a, r_a)                           # same kernel, same inputs
+    assert (ht - r_ht).abs().max().item() <= 2e-2 * mag
+    assert _lib.load().natsl_device_status() == 0
+
+
+@pytest.mark.parametrize("DK,DV,nbs", [(128, 64, 256), (64, 128, 64), (128, 128, 128)])
+def test_attn_split_equals_concatenated_keys(DK, DV, nbs):
+    """Keys held in two tensors (gathered part shared by two local segments + own part) against one call per
+    segment on the concatenated keys: bit-identical."""
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    from neuralattentionsearchlinear_b200.nats_util import build_selection_tables
+    dev = torch.device("cuda", 0)
+    B_rem, n_loc, S, L, HQ, HKV = 2, 2, 1024, 768, 4, 2
+    gen = torch.Generator().manual_seed(23)
+    rnd = lambda *s: torch.randn(*s, generator=gen).bfloat16().to(dev)
+    q, k, v = rnd(n_loc * B_rem, L, HQ, DK), rnd(n_loc * B_rem, L, HKV, DK), rnd(n_loc * B_rem, L, HKV, DV)
+    k_rem, v_rem = rnd(B_rem, S, HKV, DK), rnd(B_rem, S, HKV, DV)
+    types = otab.synth_types(n_loc * B_rem, (S + L) // nbs, HKV, 0.4, seed=24).to(dev)
+    tb = build_selection_tables(types, S + L, nbs)
+    o = _ops.attn_fwd_split(q, k_rem, v_rem, k, v, tb, DK ** -0.5, True)
+    for j in range(n_loc):
+        sl = slice(j * B_rem, (j + 1) * B_rem)
+        tbj = build_selection_tables(types[sl].contiguous(), S + L, nbs)
+        kc, vc = torch.cat([k_rem, k[sl]], 1).contiguous(), torch.cat([v_rem, v[sl]], 1).contiguous()
+        oj, _ = _ops.attn_fwd(q[sl].contiguous(), kc, vc, tbj, DK ** -0.5, True, q_off=S)
+        assert torch.equal(o[sl], oj)
+    assert _lib.load().natsl_device_status() == 0

@@ -31,7 +31,7 @@ def _inputs(B, T, H, K, V, nbs, seed):
     return q, k, v, g, types
 
 
-def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret, layout="contiguous"):
+def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret, layout="contiguous", splits=None):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -53,18 +53,21 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, decay, seed, ret, layout="con
         c = lambda x: x[:, tsel].contiguous()
         o_l, o_a, ht = nats_mixed_attn_mamba_sp(c(q), c(k), c(v), c(q), c(k), c(v), c(g), types[:, bsel].contiguous(),
                                                 nats_block_size=nbs, decay_for_non_mamba_blocks=decay, layout=layout,
-                                                backend=OracleSegmentOps())
+                                                linear_splits=splits, backend=OracleSegmentOps())
         ret[rank] = (o_l, o_a, ht, tsel)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,T,nbs,decay", [(2, 1024, 128, True), (3, 1100, 128, True), (2, 768, 256, False)])
-def test_sp_matches_single_process_oracle(world, T, nbs, decay):
+@pytest.mark.parametrize("world,T,nbs,decay,splits", [(2, 1024, 128, True, None), (3, 1100, 128, True, None),
+                                                      (2, 768, 256, False, None), (2, 1024, 128, True, 2),
+                                                      (2, 1024, 256, False, 2)])
+def test_sp_matches_single_process_oracle(world, T, nbs, decay, splits):
     B, H, K, V, seed = 1, 2, 16, 8, 3
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, decay, seed, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, decay, seed, ret, "contiguous", splits), nprocs=world,
+             join=True)
     q, k, v, g, types = _inputs(B, T, H, K, V, nbs, seed)
     o_ref, s_ref = ogdn.linear_recurrent(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=decay,
                                          use_l2norm=False, rule="mamba")
@@ -83,12 +86,13 @@ def _check(ret, world, o_ref, oa_ref, s_ref, holder):
     assert (ret[holder][2] - s_ref).abs().max() < 1e-9
 
 
-@pytest.mark.parametrize("world,T,nbs", [(2, 1024, 128), (3, 1536, 128)])
-def test_sp_zigzag_matches_single_process_oracle(world, T, nbs):
+@pytest.mark.parametrize("world,T,nbs,splits", [(2, 1024, 128, None), (3, 1536, 128, 2), (2, 2048, 128, 4)])
+def test_sp_zigzag_matches_single_process_oracle(world, T, nbs, splits):
     B, H, K, V, seed = 2, 2, 16, 8, 5
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, True, seed, ret, "zigzag"), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), B, T, H, K, V, nbs, True, seed, ret, "zigzag", splits), nprocs=world,
+             join=True)
     q, k, v, g, types = _inputs(B, T, H, K, V, nbs, seed)
     o_ref, s_ref = ogdn.linear_recurrent(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=True,
                                          use_l2norm=False, rule="mamba")
@@ -99,11 +103,46 @@ def test_sp_zigzag_matches_single_process_oracle(world, T, nbs):
 
 def test_virtual_types_layout():
     from neuralattentionsearchlinear_b200.sequence_parallel import virtual_attn_types
-    n_all = torch.tensor([[[2, 0]], [[1, 3]], [[0, 1]]])          # [world=3, B=1, HN=2]
+    n_all = torch.tensor([[[2, 0]], [[1, 3]], [[0, 1]]])          # [G=3, B=1, HN=2]
     local = torch.zeros(1, 2, 2, 2)
     local[0, 1, :, 0] = 1
-    t = virtual_attn_types(n_all, rank=2, cap=3, types_local=local)
+    t = virtual_attn_types(n_all, torch.tensor([0, 1, 2]), [2], cap=3, types_local=local)
     assert t.shape == (1, 3 * 3 + 2, 2, 2)
     assert t[0, :, 0, 0].tolist() == [1, 1, 0, 1, 0, 0, 0, 0, 0, 0, 1]
     assert t[0, :, 1, 0].tolist() == [0, 0, 0, 1, 1, 1, 0, 0, 0, 0, 1]
     assert float(t[..., 1].abs().sum()) == 0.0
+    # two local segments (global ids 1 and 2) over gathered segments in the order (0, 2, 1): segment-major batch
+    local2 = torch.zeros(2, 2, 2, 2)
+    t2 = virtual_attn_types(n_all, torch.tensor([0, 2, 1]), [1, 2], cap=3, types_local=local2)
+    assert t2.shape == (2, 11, 2, 2)
+    assert t2[0, :, 0, 0].tolist() == [1, 1, 0] + [0] * 8                  # segment 1 sees only segment 0
+    assert t2[1, :, 0, 0].tolist() == [1, 1, 0, 0, 0, 0, 0, 0, 0, 0, 0]     # segment 2 sees 0 and 1 (gathered slot 2: n=0)
+    assert t2[1, :, 1, 0].tolist() == [0, 0, 0, 0, 0, 0, 1, 0, 0, 0, 0]
+
+
+def test_pick_linear_splits():
+    from neuralattentionsearchlinear_b200.sequence_parallel import pick_linear_splits
+    assert pick_linear_splits(65536, 256) == 64
+    assert pick_linear_splits(4096, 256) == 4
+    assert pick_linear_splits(1100, 128) == 1            # ragged
+    assert pick_linear_splits(768, 256) == 1
+    assert pick_linear_splits(2048, 64, target_tokens=512) == 4
+
+
+def test_single_rank_sub_segment_split_matches_oracle():
+    """One process, no process group: only the sub-segment split of the linear branch is exercised."""
+    from neuralattentionsearchlinear_b200.sequence_parallel import nats_mixed_attn_mamba_sp
+    from tests.sp_helpers import OracleSegmentOps
+    B, T, H, K, V, nbs, seed = 2, 1024, 2, 16, 8, 128, 11
+    q, k, v, g, types = _inputs(B, T, H, K, V, nbs, seed)
+    types[:, -1] = 1
+    for decay in (True, False):
+        o_l, o_a, ht = nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs,
+                                                decay_for_non_mamba_blocks=decay, linear_splits=4,
+                                                backend=OracleSegmentOps())
+        o_ref, s_ref = ogdn.linear_recurrent(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=decay,
+                                             use_l2norm=False, rule="mamba")
+        oa_ref, _ = oattn.attn_sdpa(q, k, v, oattn.attn_mask(types[..., 0], T, nbs, H))
+        assert (o_l - o_ref).abs().max() < 1e-9
+        assert (o_a - oa_ref).abs().max() < 1e-9
+        assert (ht - s_ref).abs().max() < 1e-9
