@@ -1,17 +1,18 @@
 // Chunk-masked softmax attention forward on the 5th-generation tensor cores.
 //
 // One CTA = 128 queries of one softmax head; two CTAs share an SM (2 x 256 TMEM columns,
-// 2 x ~100 KB shared memory).  Warp roles:
-//   warp 0    TMA producer: Q once, then the K and V tiles of the key-tile walk into two separate
-//             2-stage rings (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the sequence end);
+// 2 x ~113 KB shared memory).  Warp roles (320 threads):
+//   warp 0    TMA producer: Q once, then the K and V tiles of the key-tile walk into a 3-stage and a
+//             2-stage ring (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the sequence end), in the
+//             order in which the tensor core frees the stages;
 //   warp 1    MMA issuer (one thread): S_j = Q K_j^T into one of two TMEM score buffers, issued two
 //             tiles ahead, and O += P_j V_j with P read straight from TMEM; completion is signalled
 //             with tcgen05.commit on mbarriers;
-//   warps 2-5 softmax, one thread per query row: tcgen05.ld of the row's 64 scores, mask, online
-//             softmax in base 2 with a lazily updated maximum (O in TMEM is only rescaled when the
-//             running maximum grows by more than 2^8), P (bf16 pairs) written back with tcgen05.st
-//             over the score buffer it came from; at the end O / l -> bf16 -> shared memory ->
-//             coalesced global stores.
+//   warps 2-9 softmax, 16 query rows per warp, four threads per row (tcgen05.ld.16x256b fragments):
+//             mask, online softmax in base 2 with a lazily updated maximum (O in TMEM is only
+//             rescaled when the running maximum grows by more than 2^8), P (bf16 pairs) written back
+//             with tcgen05.st over the score buffer it came from; at the end O / l -> bf16 -> shared
+//             memory -> coalesced global stores.
 // While the softmax warps work on tile j the tensor core runs Q K_{j+1}^T and P_{j-1} V_{j-1}.
 // The key-tile list (start key, masked, selected) is computed once per CTA into shared memory.
 // Same key-tile walk, mask and output conventions as the mma.sync kernel (attn_walk.cuh):
@@ -28,7 +29,7 @@ int attn_fwd_mma_sync(const void* q, const void* k, const void* v, const int32_t
                       const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int HQ, int HKV, int HN, int DK,
                       int DV, int nbs, float scale, int own, cudaStream_t st);
 
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;          // TMA producer, MMA issuer, 8 softmax warps
 constexpr uint32_t TC_TMEM_COLS = 256;      // S0: [0,64), S1: [64,128), O: [128, 128+DV); P_j aliases S_{j&1}
 constexpr uint32_t TC_O_COL = 128;
 constexpr float LAZY_RESCALE_LOG2 = 8.0f;
@@ -112,9 +113,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
-            mbar_init(bar_p_full + 8 * i, 128);
+            mbar_init(bar_p_full + 8 * i, 8);            // one arrival per softmax warp
         }
         mbar_init(bar_pv, 1);
+        mbar_init(bar_pv + 8, 1);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
@@ -129,6 +131,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
+        const int b_rem = b % B_rem;
         if (lane == 0) {
             prefetch_tensormap(&map_q);
             prefetch_tensormap(&map_k);
@@ -141,66 +144,59 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
         }
-        // K and V rings advance independently: whichever ring has a free stage gets its next tile.
-        int jk = 0, jv = 0, idle = 0;
-        const int b_rem = b % B_rem;
-        while (jk < n_tiles || jv < n_tiles) {
-            bool progressed = false;
-            if (jk < n_tiles) {
-                const int stg = jk % TC_KST;
-                bool ready = jk < TC_KST || mbar_try_wait(bar_k_empty + stg * 8, ((jk / TC_KST) - 1) & 1);
-                ready = __shfl_sync(0xffffffffu, ready, 0);
-                if (ready) {
-                    if (lane == 0) {
-                        const int s0 = tile_desc(jk) & 0x3FFFFFFF;
-                        const bool rem = s0 < k_split;
-                        const CUtensorMap* mk = rem ? &map_kr : &map_k;
-                        const int ts = rem ? s0 : s0 - k_split, bs = rem ? b_rem : b;
-                        const uint32_t full = bar_k_full + stg * 8;
-                        mbar_expect_tx(full, 64 * DK * 2);
+        auto load_k = [&](int j) {                    // lane 0 only
+            const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_KST;
+            const bool rem = s0 < k_split;
+            const CUtensorMap* mk = rem ? &map_kr : &map_k;
+            const int ts = rem ? s0 : s0 - k_split, bs = rem ? b_rem : b;
+            const uint32_t full = bar_k_full + stg * 8;
+            mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
-                        for (int sub = 0; sub < DK / 64; ++sub)
-                            tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hkv, ts, bs, full);
-                    }
-                    ++jk;
-                    progressed = true;
-                }
+            for (int sub = 0; sub < DK / 64; ++sub)
+                tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hkv, ts, bs, full);
+        };
+        auto load_v = [&](int j) {                    // lane 0 only; also warms L2 for the tile TC_VST further on
+            const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_VST;
+            const bool rem = s0 < k_split;
+            const uint32_t full = bar_v_full + stg * 8;
+            mbar_expect_tx(full, 64 * DV * 2);
+#pragma unroll
+            for (int sub = 0; sub < DV / 64; ++sub)
+                tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, hkv,
+                            rem ? s0 : s0 - k_split, rem ? b_rem : b, full);
+            if (j + TC_VST < n_tiles) {
+                const int s1 = tile_desc(j + TC_VST) & 0x3FFFFFFF;
+                const bool rem1 = s1 < k_split;
+                const int t1 = rem1 ? s1 : s1 - k_split, b1 = rem1 ? b_rem : b;
+#pragma unroll
+                for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, hkv, t1, b1);
+#pragma unroll
+                for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, hkv, t1, b1);
             }
+        };
+        // The loads follow the order in which the tensor core frees the ring stages: the K stages of the first two
+        // tiles right after their Q K^T products, then alternately the V stage of tile i (after P_i V_i) and the
+        // K stage of tile i + 2 (Q K_{i+2}^T is issued right behind P_i V_i).  Every wait is for the next event
+        // of that sequence, so the producer sleeps in the barrier instead of polling two rings.
+        int jk = min(TC_KST, n_tiles), jv = min(TC_VST, n_tiles);
+        if (lane == 0) {
+            for (int j = 0; j < jk; ++j) load_k(j);
+            for (int j = 0; j < jv; ++j) load_v(j);
+        }
+        bool ok = true;
+        auto next_k = [&]() {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_k_empty + (jk % TC_KST) * 8, ((jk / TC_KST) - 1) & 1, status));
+            if (ok && lane == 0) load_k(jk);
+            ++jk;
+        };
+        for (int i = 0; ok && i < 2 && jk < n_tiles; ++i) next_k();
+        while (ok && (jk < n_tiles || jv < n_tiles)) {
             if (jv < n_tiles) {
-                const int stg = jv % TC_VST;
-                bool ready = jv < TC_VST || mbar_try_wait(bar_v_empty + stg * 8, ((jv / TC_VST) - 1) & 1);
-                ready = __shfl_sync(0xffffffffu, ready, 0);
-                if (ready) {
-                    if (lane == 0) {
-                        const int s0 = tile_desc(jv) & 0x3FFFFFFF;
-                        const bool rem = s0 < k_split;
-                        const uint32_t full = bar_v_full + stg * 8;
-                        mbar_expect_tx(full, 64 * DV * 2);
-#pragma unroll
-                        for (int sub = 0; sub < DV / 64; ++sub)
-                            tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, hkv,
-                                        rem ? s0 : s0 - k_split, rem ? b_rem : b, full);
-                        // warm L2 for the tile this ring will want next
-                        if (jv + TC_VST < n_tiles) {
-                            const int s1 = tile_desc(jv + TC_VST) & 0x3FFFFFFF;
-                            const bool rem1 = s1 < k_split;
-                            const int t1 = rem1 ? s1 : s1 - k_split, b1 = rem1 ? b_rem : b;
-#pragma unroll
-                            for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, hkv, t1, b1);
-#pragma unroll
-                            for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, hkv, t1, b1);
-                        }
-                    }
-                    ++jv;
-                    progressed = true;
-                }
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_v_empty + (jv % TC_VST) * 8, ((jv / TC_VST) - 1) & 1, status));
+                if (ok && lane == 0) load_v(jv);
+                ++jv;
             }
-            if (progressed) {
-                idle = 0;
-            } else if (++idle > kWaitLimit) {
-                if (lane == 0) atomicExch(status, NATSL_DEV_WAIT_TIMEOUT);
-                break;
-            }
+            if (ok && jk < n_tiles) next_k();
             __syncwarp();
         }
     } else if (warp == 1) {
@@ -242,7 +238,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     umma_ts(tmem + TC_O_COL, tmem + sb * 64 + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bar_v_empty + vstg * 8);
-                umma_commit(bar_pv);
+                umma_commit(bar_pv + sb * 8);
             }
             __syncwarp();
             if (j + 2 < n_tiles) {
@@ -257,132 +253,165 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------------------ softmax + epilogue (128 threads)
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const int t = q0 + row;
-        const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-        const uint32_t t_o = t_lane + TC_O_COL;
-        float m_used = -INFINITY, l = 0.f;
+        // ------------------------------------------------------------ softmax + epilogue (8 warps)
+        // Warp (quad, half) owns the 16 query rows quad*32 + half*16 ... of the tile (a warp reaches only its own
+        // quarter of the TMEM lanes).  In the 16x256b layout a thread holds, of rows ra and ra + 8, the columns
+        // 8k + 2(lane%4), +1 for k = 0..7: 32 scores; the four threads of a row meet through two shuffles.
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        const int row_a = quad * 32 + half * 16 + (lane >> 2), row_b = row_a + 8;
+        const int cq = (lane & 3) * 2;
+        const int t_a = q0 + row_a, t_b = q0 + row_b;
+        const uint32_t t_rows = tmem + ((uint32_t)(quad * 32 + half * 16) << 16);
+        const uint32_t t_o = t_rows + TC_O_COL;
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j & 1;
-            const uint32_t t_s = t_lane + sb * 64;
+            const uint32_t t_s = t_rows + sb * 64;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + sb * 8, (j >> 1) & 1, status));
             if (!ok) break;
             tc_fence_after();
-            uint32_t sr[64];
-            {
-                uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[0]);
-                uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sr[32]);
-                tmem_ld32(t_s, lo);
-                tmem_ld32(t_s + 32, hi);
-                tmem_ld_wait();
-            }
+            uint32_t sr[32];
+            tmem_ld_16x256b_x8(t_s, sr);
+            tmem_ld_wait();
             const int td = tile_desc(j);
-            const bool masked = (td >> 30) & 1;
-            if (masked) {
-                // own-span tile: per row the visible keys are columns [0, c_limit] (attn_walk.cuh: visible())
+            if ((td >> 30) & 1) {
+                // own-span tile: per row the visible keys are columns [0, limit] (attn_walk.cuh: visible())
                 const int s0 = td & 0x3FFFFFFF;
                 const bool selb = (td >> 31) & 1;
                 const int blk_end = (s0 / nbs + 1) * nbs;
-                int c_limit = T - 1 - s0;
+                int lim_a = T - 1 - s0, lim_b = lim_a;
                 if (own_chunk) {
-                    c_limit = min(c_limit, t - s0);
-                    if (!(selb || t < blk_end)) c_limit = -1;
-                } else if (!(selb && t >= blk_end)) {
-                    c_limit = -1;
+                    lim_a = min(lim_a, t_a - s0);
+                    lim_b = min(lim_b, t_b - s0);
+                    if (!(selb || t_a < blk_end)) lim_a = -1;
+                    if (!(selb || t_b < blk_end)) lim_b = -1;
+                } else {
+                    if (!(selb && t_a >= blk_end)) lim_a = -1;
+                    if (!(selb && t_b >= blk_end)) lim_b = -1;
                 }
 #pragma unroll
-                for (int c = 0; c < 64; ++c) sr[c] = (c <= c_limit) ? sr[c] : 0xff800000u;   // -inf
-            }
-            // row maximum of the raw scores (scale > 0, so max(scale * s) = scale * max(s)); four
-            // independent chains keep the dependent-issue latency short
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                for (int k = 0; k < 8; ++k)
 #pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(sr[c + i]));
+                    for (int e = 0; e < 2; ++e) {
+                        const int c = 8 * k + cq + e;
+                        sr[4 * k + e] = (c <= lim_a) ? sr[4 * k + e] : 0xff800000u;          // -inf
+                        sr[4 * k + 2 + e] = (c <= lim_b) ? sr[4 * k + 2 + e] : 0xff800000u;
+                    }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            const bool need = mx > m_used + LAZY_RESCALE_LOG2;
-            bool pv_seen = (j == 0);                  // has this thread observed the completion of P_{j-1} V_{j-1}?
-            if (__any_sync(0xffffffffu, need)) {
-                const float m_new = need ? mx : m_used;
-                const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_used - m_new);
+            // row maxima of the raw scores (scale > 0, so max(scale * s) = scale * max(s))
+            float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+                xa0 = fmax3(xa0, __uint_as_float(sr[4 * k]), __uint_as_float(sr[4 * k + 1]));
+                xb0 = fmax3(xb0, __uint_as_float(sr[4 * k + 2]), __uint_as_float(sr[4 * k + 3]));
+                xa1 = fmax3(xa1, __uint_as_float(sr[4 * k + 4]), __uint_as_float(sr[4 * k + 5]));
+                xb1 = fmax3(xb1, __uint_as_float(sr[4 * k + 6]), __uint_as_float(sr[4 * k + 7]));
+            }
+            float xa = fmaxf(xa0, xa1), xb = fmaxf(xb0, xb1);
+            xa = fmaxf(xa, __shfl_xor_sync(0xffffffffu, xa, 1));
+            xb = fmaxf(xb, __shfl_xor_sync(0xffffffffu, xb, 1));
+            xa = fmaxf(xa, __shfl_xor_sync(0xffffffffu, xa, 2));
+            xb = fmaxf(xb, __shfl_xor_sync(0xffffffffu, xb, 2));
+            const float mx_a = xa * scale_log2, mx_b = xb * scale_log2;
+            const bool need_a = mx_a > m_a + LAZY_RESCALE_LOG2, need_b = mx_b > m_b + LAZY_RESCALE_LOG2;
+            if (__any_sync(0xffffffffu, need_a || need_b)) {
+                const float new_a = need_a ? mx_a : m_a, new_b = need_b ? mx_b : m_b;
+                const float alpha_a = (new_a == -INFINITY) ? 1.f : ex2(m_a - new_a);
+                const float alpha_b = (new_b == -INFINITY) ? 1.f : ex2(m_b - new_b);
                 if (j > 0) {
-                    // O must be at rest: wait until P_{j-1} V_{j-1} has completed
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, status));
+                    // O must be at rest: P_{j-1} V_{j-1} has to be complete.  Even and odd tiles signal on two
+                    // barriers.  S_j was produced behind P_{j-2} V_{j-2}, hence behind P_{j-3} V_{j-3} (the previous
+                    // phase of the barrier waited on), and P_{j+1} V_{j+1} cannot have started: the barrier is in
+                    // the phase waited for or the one after it, so a parity wait without having watched the earlier
+                    // phases is unambiguous.
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, status));
                     if (!ok) break;
-                    pv_seen = true;
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c0 = 0; c0 < DV; c0 += 32) {
+                    for (int c0 = 0; c0 < DV; c0 += 64) {
                         uint32_t orr[32];
-                        tmem_ld32(t_o + c0, orr);
+                        tmem_ld_16x256b_x8(t_o + c0, orr);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-                        tmem_st32(t_o + c0, orr);
+                        for (int k = 0; k < 8; ++k) {
+                            orr[4 * k] = __float_as_uint(__uint_as_float(orr[4 * k]) * alpha_a);
+                            orr[4 * k + 1] = __float_as_uint(__uint_as_float(orr[4 * k + 1]) * alpha_a);
+                            orr[4 * k + 2] = __float_as_uint(__uint_as_float(orr[4 * k + 2]) * alpha_b);
+                            orr[4 * k + 3] = __float_as_uint(__uint_as_float(orr[4 * k + 3]) * alpha_b);
+                        }
+                        tmem_st_16x256b_x8(t_o + c0, orr);
                     }
                 }
-                l *= alpha;
-                m_used = m_new;
+                l_a *= alpha_a;
+                l_b *= alpha_b;
+                m_a = new_a;
+                m_b = new_b;
             }
-            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[32];
+            const float neg_a = (m_a == -INFINITY) ? 0.f : -m_a, neg_b = (m_b == -INFINITY) ? 0.f : -m_b;
+            float la2 = 0.f, lb2 = 0.f;
+            uint32_t pr[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), scale_log2, neg_m));
-                const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), scale_log2, neg_m));
-                rs4[i & 3] += p0 + p1;
-                pk[i] = pack_bf16(p0, p1);
+            for (int k = 0; k < 8; ++k) {
+                const float p0 = ex2(fmaf(__uint_as_float(sr[4 * k]), scale_log2, neg_a));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[4 * k + 1]), scale_log2, neg_a));
+                const float p2 = ex2(fmaf(__uint_as_float(sr[4 * k + 2]), scale_log2, neg_b));
+                const float p3 = ex2(fmaf(__uint_as_float(sr[4 * k + 3]), scale_log2, neg_b));
+                if (k & 1) {
+                    la2 += p0 + p1;
+                    lb2 += p2 + p3;
+                } else {
+                    l_a += p0 + p1;
+                    l_b += p2 + p3;
+                }
+                pr[2 * k] = pack_bf16(p0, p1);                // P column 4k + lane%4 of row a
+                pr[2 * k + 1] = pack_bf16(p2, p3);            // ... of row b
             }
-            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            l += rs;
-            if (!pv_seen) {
-                // every phase of the P V barrier is observed in order (a parity wait can only tell the
-                // current phase from the previous one); by now P_{j-1} V_{j-1} has normally long finished
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (j - 1) & 1, status));
-                if (!ok) break;
-            }
-            tmem_st32(t_s, pk);                       // P_j over the first 32 columns of S_{j&1}
+            l_a += la2;
+            l_b += lb2;
+            tmem_st_16x128b_x8(t_s, pr);                      // P_j over the first 32 columns of S_{j&1}
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar_p_full + sb * 8);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full + sb * 8);
         }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, (n_tiles - 1) & 1, status));
+        if (ok)          // the last product; the one two tiles earlier on the same barrier completed before S of the last tile
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + ((n_tiles - 1) & 1) * 8, ((n_tiles - 1) >> 1) & 1, status));
         unsigned char* stage = smem + L::q;
         if (ok) {
             tc_fence_after();
-            const bool has = l > 0.f;
-            const float inv = has ? 1.f / l : 0.f;
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const bool has_a = l_a > 0.f, has_b = l_b > 0.f;
+            const float inv_a = has_a ? 1.f / l_a : 0.f, inv_b = has_b ? 1.f / l_b : 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < DV; c0 += 32) {
+            for (int c0 = 0; c0 < DV; c0 += 64) {
                 uint32_t orr[32];
-                tmem_ld32(t_o + c0, orr);
+                tmem_ld_16x256b_x8(t_o + c0, orr);
                 tmem_ld_wait();
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    uint32_t w4[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        w4[i] = pack_bf16(__uint_as_float(orr[cc * 8 + 2 * i]) * inv,
-                                          __uint_as_float(orr[cc * 8 + 2 * i + 1]) * inv);
-                    *reinterpret_cast<uint4*>(stage + swz<DV * 2>(row, (c0 >> 3) + cc)) =
-                        make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                for (int k = 0; k < 8; ++k) {
+                    const int chunk = (c0 >> 3) + k;
+                    *reinterpret_cast<uint32_t*>(stage + swz<DV * 2>(row_a, chunk) + (lane & 3) * 4) =
+                        pack_bf16(__uint_as_float(orr[4 * k]) * inv_a, __uint_as_float(orr[4 * k + 1]) * inv_a);
+                    *reinterpret_cast<uint32_t*>(stage + swz<DV * 2>(row_b, chunk) + (lane & 3) * 4) =
+                        pack_bf16(__uint_as_float(orr[4 * k + 2]) * inv_b, __uint_as_float(orr[4 * k + 3]) * inv_b);
                 }
             }
-            if (t - q_off < Tq) lse[((long)b * Tq + (t - q_off)) * HQ + hq] = has ? m_used + log2f(l) : 0.f;
+            if ((lane & 3) == 0) {
+                if (t_a - q_off < Tq) lse[((long)b * Tq + (t_a - q_off)) * HQ + hq] = has_a ? m_a + log2f(l_a) : 0.f;
+                if (t_b - q_off < Tq) lse[((long)b * Tq + (t_b - q_off)) * HQ + hq] = has_b ? m_b + log2f(l_b) : 0.f;
+            }
         }
         // every softmax warp reaches this barrier, also after a failed wait (no warp may be left behind)
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ok) {
             constexpr int CPR = DV / 8;
             __nv_bfloat16* obase = o + (((long)b * Tq + (q0 - q_off)) * HQ + hq) * DV;
             const int st_tid = tid - 64;
-            for (int i = st_tid; i < 128 * CPR; i += 128) {
+            for (int i = st_tid; i < 128 * CPR; i += 256) {
                 const int r = i / CPR, cch = i % CPR;
                 if (q0 - q_off + r < Tq) {
                     const uint4 x = *reinterpret_cast<const uint4*>(stage + swz<DV * 2>(r, cch));

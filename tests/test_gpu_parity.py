@@ -101,6 +101,34 @@ def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own):
     assert_close(lse2, lse_ref, TOL, "lse (mma.sync)")
 
 
+@pytest.mark.parametrize("DK,DV,nbs", [(128, 128, 64), (128, 64, 256), (64, 64, 128)])
+def test_attention_growing_scores(nat, DK, DV, nbs):
+    """Keys whose norm grows along the sequence: the running row maximum keeps rising by more than the lazy
+    threshold, so the accumulator in tensor memory is rescaled many times; plus run-to-run and batch-subset
+    bit-identity (no race between the rescale and the tensor core)."""
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    B, T, HQ, HKV = 3, 2048, 4, 2
+    gen = torch.Generator().manual_seed(DK + nbs)
+    ramp = (1.0 + 9.0 * torch.arange(T) / T).view(1, T, 1, 1)
+    q = torch.randn(B, T, HQ, DK, generator=gen).bfloat16()
+    k = (torch.randn(B, T, HKV, DK, generator=gen) * ramp).bfloat16()
+    v = torch.randn(B, T, HKV, DV, generator=gen).bfloat16()
+    types = otab.synth_types(B, T // nbs, HKV, 0.5, seed=nbs)
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o, lse = _ops.attn_fwd(qc, kc, vc, tb, DK ** -0.5, True)
+    mask = oattn.attn_mask(types[..., 0], T, nbs, HQ)
+    o_ref, lse_ref = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask, DK ** -0.5)
+    assert_close(o, o_ref, TOL, "o_attn")
+    assert_close(lse, lse_ref, TOL, "lse")
+    o_again, _ = _ops.attn_fwd(qc, kc, vc, tb, DK ** -0.5, True)
+    assert torch.equal(o, o_again)
+    tb1 = nat.build_selection_tables(types[1:2].cuda().contiguous(), T, nbs)
+    o_one, _ = _ops.attn_fwd(qc[1:2].contiguous(), kc[1:2].contiguous(), vc[1:2].contiguous(), tb1, DK ** -0.5, True)
+    assert torch.equal(o[1:2], o_one)
+    assert _lib.load().natsl_device_status() == 0
+
+
 GDN_CASES = [  # B, T, H, HN, K, V, nbs, decay, use_h0
     (2, 512, 4, 4, 64, 64, 64, True, False),
     (1, 700, 4, 2, 128, 128, 64, True, True),
