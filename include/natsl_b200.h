@@ -83,14 +83,21 @@ int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, const int32_t
                       const int32_t* attn_n_iters, void* o, float* lse, int B, int T, int Tq, int q_off, int HQ,
                       int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream);
 
-/* Same, with the T keys held in two pairs of tensors: keys [0, k_split) in k_rem, v_rem [B_rem, k_split, HKV, .]
- * (batch index b % B_rem: blocks gathered from other segments, shared by the B / B_rem local segments that sit
- * segment-major in the batch), keys [k_split, T) in k, v [B, T - k_split, HKV, .].  k_split is a multiple of nbs
- * and <= q_off; k_split = 0 ignores k_rem, v_rem.  No reference counterpart (sequence parallelism). */
-int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
-                         const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse,
-                         int B, int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV, int HN, int DK, int DV,
-                         int nbs, float scale, int flags, void* stream);
+/* Same, with the T keys held in two pairs of tensors: keys [0, k_split) in k_rem, v_rem (batch index b % B_rem:
+ * blocks gathered from other segments, shared by the B / B_rem local segments that sit segment-major in the batch),
+ * keys [k_split, T) in k, v [B, T - k_split, HKV, .].  k_split is a multiple of nbs and <= q_off; k_split = 0
+ * ignores the gathered tensors.  Two layouts of the gathered part:
+ *   rem_base = NULL: k_rem, v_rem [B_rem, k_split, HKV, .], token-major like k, v;
+ *   rem_base [B_rem, G, HKV] int32: k_rem, v_rem [B_rem, rem_tokens, .] hold only the selected (block, head) pairs
+ *     of the G gathered segments (natsl_pack_selected_pairs); the virtual key sequence gives every gathered
+ *     segment rem_slots blocks per head (k_split = G * rem_slots * nbs) and virtual block g * rem_slots + j of
+ *     head h is the nbs tokens starting at token (rem_base[b % B_rem, g, h] + j) * nbs.
+ * No reference counterpart (sequence parallelism). */
+int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const int32_t* rem_base, int rem_slots,
+                         int rem_tokens, const void* k, const void* v, const int32_t* types_i, const int32_t* indices,
+                         const int32_t* attn_n_iters, void* o, float* lse, int B, int B_rem, int T, int Tq, int q_off,
+                         int k_split, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags,
+                         void* stream);
 
 /* Debug/parity: dense 0/1 mask [B,HQ,T,T] (uint8) from the same tile walk as natsl_attn_fwd.
  * Counterpart: store_msk=True of the reference kernel, src/nats/ops/attns/attns.py:214-217,
@@ -176,7 +183,10 @@ int natsl_attn_fwd_fp32(int dtype, const void* q, const void* k, const void* v, 
  *   (or NULL = zero) the first one starts from: P[0] = h0, P[i+1] = a[i] P[i] + S[i]; writes prefix [N,B,H,K,V] = P[0..N)
  *   (or NULL), total_S [B,H,K,V] = P[N] (or NULL) and total_a [B,H] = prod a (or NULL).
  * natsl_pack_selected_blocks: packed [B, cap_blocks*nbs, H, D] <- the selected blocks (column `op`) of
- *   x [B,T,H,D] bf16 in index-table order, per head; slots past the number of selected blocks are left untouched. */
+ *   x [B,T,H,D] bf16 in index-table order, per head; slots past the number of selected blocks are left untouched.
+ * natsl_pack_selected_pairs: packed [B, cap_pairs*nbs, D] <- the same blocks with no padding: the selected
+ *   (block, head) pairs of a batch entry back to back, head-major (all blocks of head 0, then head 1, ...); pairs
+ *   beyond cap_pairs are dropped. */
 int natsl_sp_segment_decay(const float* gcs, const int32_t* types_i, float* a, float* trail, int B, int T, int H,
                            int HN, int nbs, int flags, void* stream);
 int natsl_sp_state_combine(const float* a, const float* S, float* h_in, int rank, int world, int B, int H, int K, int V,
@@ -185,6 +195,8 @@ int natsl_sp_prefix_states(const float* a, const float* S, const float* h0, floa
                            float* total_a, int N, int B, int H, int K, int V, void* stream);
 int natsl_pack_selected_blocks(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
                                int T, int H, int HN, int D, int nbs, int op, int cap_blocks, void* stream);
+int natsl_pack_selected_pairs(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
+                              int T, int H, int HN, int D, int nbs, int op, int cap_pairs, void* stream);
 
 /* Output mixing: y = (x1 rstd1 w1 a + x2 rstd2 w2 b) * g * sigmoid(g) over rows of D (64/128/256) bf16
  * elements; xw [rows,2] = (a, b) or NULL; w1, w2 [D] or NULL; activation 0 = swish, 1 = sigmoid.

@@ -34,21 +34,33 @@ def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mm
     return o, lse
 
 
-def attn_fwd_split(q, k_rem, v_rem, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
-    """Softmax branch over a key sequence held in two parts: keys [0, S) in k_rem, v_rem [B_rem, S, HKV, .] (shared by
-    the B / B_rem segments that sit segment-major in the batch of q, k, v) and keys [S, S+L) in k, v [B, L, HKV, .];
-    the queries q [B, L, HQ, DK] are the tokens [S, S+L).  -> o [B, L, HQ, DV] bf16."""
+def attn_fwd_split(q, k_rem, v_rem, k, v, tables: SelectionTables, scale: float, own_chunk: bool, rem_base=None,
+                   rem_slots: int = 0):
+    """Softmax branch over a key sequence held in two parts: keys [0, S) gathered from other segments (shared by the
+    B / B_rem local segments that sit segment-major in the batch of q, k, v) and keys [S, S+L) in k, v [B, L, HKV, .];
+    the queries q [B, L, HQ, DK] are the tokens [S, S+L).  Gathered part: k_rem, v_rem [B_rem, S, HKV, .], or with
+    ``rem_base`` [B_rem, G, HKV] int32 the packed selected (block, head) pairs [B_rem, tokens, .] of G segments with
+    ``rem_slots`` virtual blocks per head each (S = G * rem_slots * block size).  -> o [B, L, HQ, DV] bf16."""
     for t_ in (q, k_rem, v_rem, k, v):
         _need(t_.dtype == BF16 and t_.is_contiguous(), "softmax branch needs contiguous bf16 tensors", TypeError)
     B, L, HQ, DK = q.shape
-    B_rem, S, HKV, DV = v_rem.shape
+    HKV, DV = k.shape[2], v.shape[3]
+    B_rem = k_rem.shape[0]
+    nbs = tables.nats_block_size
+    if rem_base is None:
+        S, rem_tokens = k_rem.shape[1], 0
+    else:
+        _need(rem_base.dtype == torch.int32 and rem_base.is_contiguous() and rem_base.shape[0] == B_rem
+              and rem_base.shape[2] == HKV, "rem_base must be a contiguous int32 [B_rem, G, HKV] tensor")
+        S, rem_tokens = rem_base.shape[1] * int(rem_slots) * nbs, k_rem.shape[1]
     _need(tables.T == S + L, f"tables were built for T={tables.T}, keys have T={S + L}")
     o = torch.empty(B, L, HQ, DV, dtype=BF16, device=q.device)
     lse = torch.empty(B, L, HQ, dtype=torch.float32, device=q.device)
-    _lib.call("natsl_attn_fwd_split", q.data_ptr(), k_rem.data_ptr(), v_rem.data_ptr(), k.data_ptr(), v.data_ptr(),
-              tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(),
-              lse.data_ptr(), B, B_rem, S + L, L, S, S, HQ, HKV, tables.types_i.shape[2], DK, DV, tables.nats_block_size,
-              float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0, current_stream_ptr(q.device))
+    _lib.call("natsl_attn_fwd_split", q.data_ptr(), k_rem.data_ptr(), v_rem.data_ptr(), _lib.ptr(rem_base), int(rem_slots),
+              int(rem_tokens), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
+              tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(), B, B_rem, S + L, L, S, S, HQ, HKV,
+              tables.types_i.shape[2], DK, DV, nbs, float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0,
+              current_stream_ptr(q.device))
     return o
 
 
@@ -66,9 +78,10 @@ def attn_dense_mask(tables: SelectionTables, HQ: int, own_chunk: bool) -> torch.
 
 def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool,
                use_l2norm: bool, output_final_state: bool, trailing_quirk: bool = True,
-               return_intermediates: bool = False, skip_out: bool = False):
+               return_intermediates: bool = False, skip_out: bool = False, own_chunk: bool = True):
     """Linear branch forward (prep -> state recurrence -> output).  Returns (o, ht, inter); with ``skip_out``
-    only the recurrence runs (o is None)."""
+    only the recurrence runs (o is None).  ``own_chunk=False``: the output keeps only the state term (the mode
+    in which the softmax branch alone covers the current chunk); ``tables`` must then be per 64-token chunk."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "linear branch needs bf16 q/k/v", TypeError)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
@@ -81,7 +94,7 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     g = g.float().contiguous()
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     fused = (rule == _lib.RULE_GDN and K == 128 and V == 128 and nbs == 64 and NT <= 1024 and not return_intermediates
-             and not skip_out and USE_FUSED_WALK)
+             and not skip_out and own_chunk and USE_FUSED_WALK)
     if rule == _lib.RULE_GDN:
         beta = beta.contiguous()
         _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
@@ -121,7 +134,7 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
     _lib.call("natsl_linear_fwd_o", rule, q.data_ptr(), k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(),
               _lib.ptr(krstd), h.data_ptr(), carry.data_ptr(), o.data_ptr(), B, T, H, K, V, float(scale),
-              int(use_l2norm and rule == _lib.RULE_GDN), st)
+              int(use_l2norm and rule == _lib.RULE_GDN) | (0 if own_chunk else 2), st)
     return o, ht, inter
 
 

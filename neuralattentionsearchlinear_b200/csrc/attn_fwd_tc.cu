@@ -68,7 +68,8 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kr,
-                   const __grid_constant__ CUtensorMap map_vr, int k_split, int B_rem, const int* __restrict__ types_i,
+                   const __grid_constant__ CUtensorMap map_vr, int k_split, int B_rem, const int* __restrict__ rem_base,
+                   int rem_slots, const int* __restrict__ types_i,
                    const int* __restrict__ indices, const int* __restrict__ attn_n_iters,
                    __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int Tq, int q_off, int HQ, int HKV,
                    int HN, int TN, int nbs, float scale_log2, int own_chunk, int* status) {
@@ -76,6 +77,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // [q_off, q_off + Tq) of that sequence (q_off = 0, Tq = T except under sequence parallelism).
     // Keys [0, k_split) live in a second pair of tensors (map_kr / map_vr, batch index b % B_rem: the
     // gathered blocks of other segments, shared by the local segments), keys [k_split, T) in map_k / map_v.
+    // With rem_base the gathered tensors are [B_rem, tokens, 1, D]: the selected (block, head) pairs of every
+    // gathered segment packed back to back; virtual block g * rem_slots + j of head hkv is pair
+    // rem_base[(b % B_rem, g, hkv)] + j.
     using L = TcSmem<DK, DV>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -92,9 +96,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int* idx = indices + ((long)b * TN * HN + hn) * 2;
     const int* selp = types_i + ((long)b * TN * HN + hn) * 2;
     const long tstride = (long)HN * 2;
-    const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
-    const int n_tiles = walk.n_tiles;
-
     const uint32_t s_q = sbase + L::q, s_k = sbase + L::k, s_v = sbase + L::v;
     int* tile_list = reinterpret_cast<int*>(smem + L::list);
     const uint32_t bar0 = sbase + L::bars;
@@ -118,8 +119,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(bar_pv, 1);
         mbar_init(bar_pv + 8, 1);
         mbar_fence_init();
+        // the query tile depends on nothing else: its load starts before the tables are read
+        prefetch_tensormap(&map_q);
+        mbar_expect_tx(bar_q, 128 * DK * 2);
+#pragma unroll
+        for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
+    const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
+    const int n_tiles = walk.n_tiles;
     for (int j = tid; j < min(n_tiles, TC_LIST_CAP); j += TC_THREADS) tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs);
     tc_fence_before();
     __syncthreads();
@@ -133,27 +141,31 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ------------------------------------------------------------ TMA producer
         const int b_rem = b % B_rem;
         if (lane == 0) {
-            prefetch_tensormap(&map_q);
             prefetch_tensormap(&map_k);
             prefetch_tensormap(&map_v);
             if (k_split > 0) {
                 prefetch_tensormap(&map_kr);
                 prefetch_tensormap(&map_vr);
             }
-            mbar_expect_tx(bar_q, 128 * DK * 2);
-#pragma unroll
-            for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
         }
+        // token coordinate of gathered key s in its tensor (head coordinate rem_head)
+        const int rem_head = rem_base ? 0 : hkv;
+        const int n_seg_rem = rem_base ? k_split / (rem_slots * nbs) : 0;
+        auto rem_token = [&](int s) -> int {
+            if (!rem_base) return s;
+            const int vb = s / nbs, g = vb / rem_slots;
+            return (rem_base[((long)b_rem * n_seg_rem + g) * HKV + hkv] + (vb - g * rem_slots)) * nbs + (s - vb * nbs);
+        };
         auto load_k = [&](int j) {                    // lane 0 only
             const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_KST;
             const bool rem = s0 < k_split;
             const CUtensorMap* mk = rem ? &map_kr : &map_k;
-            const int ts = rem ? s0 : s0 - k_split, bs = rem ? b_rem : b;
+            const int ts = rem ? rem_token(s0) : s0 - k_split, bs = rem ? b_rem : b, hs = rem ? rem_head : hkv;
             const uint32_t full = bar_k_full + stg * 8;
             mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
             for (int sub = 0; sub < DK / 64; ++sub)
-                tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hkv, ts, bs, full);
+                tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hs, ts, bs, full);
         };
         auto load_v = [&](int j) {                    // lane 0 only; also warms L2 for the tile TC_VST further on
             const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_VST;
@@ -162,16 +174,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_expect_tx(full, 64 * DV * 2);
 #pragma unroll
             for (int sub = 0; sub < DV / 64; ++sub)
-                tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, hkv,
-                            rem ? s0 : s0 - k_split, rem ? b_rem : b, full);
+                tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, rem ? rem_head : hkv,
+                            rem ? rem_token(s0) : s0 - k_split, rem ? b_rem : b, full);
             if (j + TC_VST < n_tiles) {
                 const int s1 = tile_desc(j + TC_VST) & 0x3FFFFFFF;
                 const bool rem1 = s1 < k_split;
-                const int t1 = rem1 ? s1 : s1 - k_split, b1 = rem1 ? b_rem : b;
+                const int t1 = rem1 ? rem_token(s1) : s1 - k_split, b1 = rem1 ? b_rem : b, h1 = rem1 ? rem_head : hkv;
 #pragma unroll
-                for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, hkv, t1, b1);
+                for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, h1, t1, b1);
 #pragma unroll
-                for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, hkv, t1, b1);
+                for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, h1, t1, b1);
             }
         };
         // The loads follow the order in which the tensor core frees the ring stages: the K stages of the first two
@@ -428,9 +440,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 template <int DK, int DV>
 static int launch_attn_tc(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
-                          const int* types_i, const int* indices, const int* n_iters, void* o, float* lse, int B,
-                          int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV, int HN, int nbs, float scale,
-                          int own_chunk, cudaStream_t st) {
+                          const int* rem_base, int rem_slots, int rem_tokens, const int* types_i, const int* indices,
+                          const int* n_iters, void* o, float* lse, int B, int B_rem, int T, int Tq, int q_off, int k_split,
+                          int HQ, int HKV, int HN, int nbs, float scale, int own_chunk, cudaStream_t st) {
     using L = TcSmem<DK, DV>;
     auto kern = attn_fwd_tc_kernel<DK, DV>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
@@ -443,8 +455,9 @@ static int launch_attn_tc(const void* q, const void* k_rem, const void* v_rem, c
     if (rc == NATSL_OK) rc = encode_bthd_map(&mk, k, B, T - k_split, HKV, DK, 64, "natsl_attn_fwd(k)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T - k_split, HKV, DV, 64, "natsl_attn_fwd(v)");
     if (k_split > 0) {
-        if (rc == NATSL_OK) rc = encode_bthd_map(&mkr, k_rem, B_rem, k_split, HKV, DK, 64, "natsl_attn_fwd(k_rem)");
-        if (rc == NATSL_OK) rc = encode_bthd_map(&mvr, v_rem, B_rem, k_split, HKV, DV, 64, "natsl_attn_fwd(v_rem)");
+        const int rt = rem_base ? rem_tokens : k_split, rh = rem_base ? 1 : HKV;
+        if (rc == NATSL_OK) rc = encode_bthd_map(&mkr, k_rem, B_rem, rt, rh, DK, 64, "natsl_attn_fwd(k_rem)");
+        if (rc == NATSL_OK) rc = encode_bthd_map(&mvr, v_rem, B_rem, rt, rh, DV, 64, "natsl_attn_fwd(v_rem)");
     } else {
         mkr = mk;
         mvr = mv;
@@ -455,7 +468,8 @@ static int launch_attn_tc(const void* q, const void* k_rem, const void* v_rem, c
     if (rc != NATSL_OK) return rc;
     const int NTq = (Tq + ATT_BM - 1) / ATT_BM, TN = (T + nbs - 1) / nbs;
     dim3 grid(NTq, HQ, B);
-    kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, mkr, mvr, k_split, B_rem, types_i, indices, n_iters,
+    kern<<<grid, TC_THREADS, L::total, st>>>(mq, mk, mv, mkr, mvr, k_split, B_rem, k_split > 0 ? rem_base : nullptr,
+                                             rem_slots, types_i, indices, n_iters,
                                              reinterpret_cast<__nv_bfloat16*>(o),
                                              lse, T, Tq, q_off, HQ, HKV, HN, TN, nbs, scale * 1.44269504f, own_chunk,
                                              status);
@@ -464,10 +478,11 @@ static int launch_attn_tc(const void* q, const void* k_rem, const void* v_rem, c
 
 }  // namespace natsl
 
-extern "C" int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const void* k, const void* v,
-                                    const int32_t* types_i, const int32_t* indices, const int32_t* attn_n_iters, void* o,
-                                    float* lse, int B, int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV,
-                                    int HN, int DK, int DV, int nbs, float scale, int flags, void* stream) {
+extern "C" int natsl_attn_fwd_split(const void* q, const void* k_rem, const void* v_rem, const int32_t* rem_base,
+                                    int rem_slots, int rem_tokens, const void* k, const void* v, const int32_t* types_i,
+                                    const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B,
+                                    int B_rem, int T, int Tq, int q_off, int k_split, int HQ, int HKV, int HN, int DK,
+                                    int DV, int nbs, float scale, int flags, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(q && k && v && types_i && indices && attn_n_iters && o && lse, NATSL_ERR_NULL,
                   "natsl_attn_fwd: null pointer");
@@ -485,6 +500,8 @@ extern "C" int natsl_attn_fwd_split(const void* q, const void* k_rem, const void
                   k_split, q_off);
     NATSL_REQUIRE(k_split == 0 || (k_rem && v_rem && B_rem > 0 && B % B_rem == 0), NATSL_ERR_BAD_SHAPE,
                   "natsl_attn_fwd: a key split needs k_rem, v_rem and a batch B_rem that divides B");
+    NATSL_REQUIRE(k_split == 0 || !rem_base || (rem_slots > 0 && k_split % (rem_slots * nbs) == 0 && rem_tokens > 0),
+                  NATSL_ERR_BAD_SHAPE, "natsl_attn_fwd: packed gathered keys need rem_slots dividing the key split");
     const int own = (flags & NATSL_FLAG_ATTN_OWN_CHUNK) ? 1 : 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (flags & NATSL_FLAG_ATTN_MMA_SYNC) {
@@ -493,8 +510,9 @@ extern "C" int natsl_attn_fwd_split(const void* q, const void* k_rem, const void
         return attn_fwd_mma_sync(q, k, v, types_i, indices, attn_n_iters, o, lse, B, T, HQ, HKV, HN, DK, DV, nbs, scale,
                                  own, st);
     }
-#define NATSL_ATT_ARGS \
-    q, k_rem, v_rem, k, v, types_i, indices, attn_n_iters, o, lse, B, B_rem, T, Tq, q_off, k_split, HQ, HKV, HN, nbs, scale, own, st
+#define NATSL_ATT_ARGS                                                                                                 \
+    q, k_rem, v_rem, k, v, rem_base, rem_slots, rem_tokens, types_i, indices, attn_n_iters, o, lse, B, B_rem, T, Tq, q_off, \
+        k_split, HQ, HKV, HN, nbs, scale, own, st
     if (DK == 64 && DV == 64) return launch_attn_tc<64, 64>(NATSL_ATT_ARGS);
     if (DK == 64 && DV == 128) return launch_attn_tc<64, 128>(NATSL_ATT_ARGS);
     if (DK == 128 && DV == 64) return launch_attn_tc<128, 64>(NATSL_ATT_ARGS);
@@ -508,8 +526,8 @@ extern "C" int natsl_attn_fwd_ex(const void* q, const void* k, const void* v, co
                                  const int32_t* indices, const int32_t* attn_n_iters, void* o, float* lse, int B,
                                  int T, int Tq, int q_off, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
                                  int flags, void* stream) {
-    return natsl_attn_fwd_split(q, nullptr, nullptr, k, v, types_i, indices, attn_n_iters, o, lse, B, B, T, Tq, q_off, 0,
-                                HQ, HKV, HN, DK, DV, nbs, scale, flags, stream);
+    return natsl_attn_fwd_split(q, nullptr, nullptr, nullptr, 0, 0, k, v, types_i, indices, attn_n_iters, o, lse, B, B, T,
+                                Tq, q_off, 0, HQ, HKV, HN, DK, DV, nbs, scale, flags, stream);
 }
 
 extern "C" int natsl_attn_fwd(const void* q, const void* k, const void* v, const int32_t* types_i,

@@ -89,6 +89,31 @@ pack_blocks_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ 
     }
 }
 
+// Same blocks, no padding: pair p = (sum of the counts of the heads before h) + j of batch entry b goes to
+// packed[b, p*nbs + i, :].
+__global__ void __launch_bounds__(256)
+pack_pairs_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ indices, const int* __restrict__ n_blocks,
+                  __nv_bfloat16* __restrict__ packed, int T, int H, int HN, int TN, int D, int nbs, int op, int cap) {
+    const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int G = H / HN, hn = h / G;
+    const int n = n_blocks[((long)b * HN + hn) * 2 + op];
+    if (j >= n) return;
+    int base = 0;
+    for (int g = 0; g < hn; ++g) base += n_blocks[((long)b * HN + g) * 2 + op];
+    base = base * G + (h - hn * G) * n;
+    const int pidx = base + j;
+    if (pidx >= cap) return;
+    const int blk = indices[(((long)b * TN + j) * HN + hn) * 2 + op];
+    const int cpr = D / 8;                          // 16-byte chunks per row
+    for (int e = threadIdx.x; e < nbs * cpr; e += blockDim.x) {
+        const int i = e / cpr, c = e % cpr;
+        const long t = (long)blk * nbs + i;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < T) v = *reinterpret_cast<const uint4*>(x + (((long)b * T + t) * H + h) * D + c * 8);
+        *reinterpret_cast<uint4*>(packed + (((long)b * cap + pidx) * nbs + i) * D + c * 8) = v;
+    }
+}
+
 }  // namespace natsl
 
 extern "C" int natsl_sp_segment_decay(const float* gcs, const int32_t* types_i, float* a, float* trail, int B, int T,
@@ -141,4 +166,21 @@ extern "C" int natsl_pack_selected_blocks(const void* x, const int32_t* indices,
         reinterpret_cast<const __nv_bfloat16*>(x), indices, n_blocks, reinterpret_cast<__nv_bfloat16*>(packed), T, H, HN,
         TN, D, nbs, op, cap_blocks);
     return check_launch("natsl_pack_selected_blocks");
+}
+
+extern "C" int natsl_pack_selected_pairs(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed,
+                                         int B, int T, int H, int HN, int D, int nbs, int op, int cap_pairs,
+                                         void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(x && indices && n_blocks && packed, NATSL_ERR_NULL, "natsl_pack_selected_pairs: null pointer");
+    NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && HN > 0 && H % HN == 0 && D % 8 == 0 && (op == 0 || op == 1),
+                  NATSL_ERR_BAD_SHAPE, "natsl_pack_selected_pairs: bad shape");
+    NATSL_REQUIRE(H <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_pack_selected_pairs: B, H <= 65535");
+    if (cap_pairs <= 0) return NATSL_OK;
+    const int TN = (T + nbs - 1) / nbs;
+    dim3 grid(TN, H, B);
+    pack_pairs_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), indices, n_blocks, reinterpret_cast<__nv_bfloat16*>(packed), T, H, HN,
+        TN, D, nbs, op, cap_pairs);
+    return check_launch("natsl_pack_selected_pairs");
 }

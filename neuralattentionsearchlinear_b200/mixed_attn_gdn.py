@@ -44,6 +44,17 @@ def _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_s
         raise NotImplementedError("use_g_for_attn is not built (the layers always pass False)")
 
 
+def per_chunk_tables(nats_block_types, T, nats_block_size):
+    """Selection tables of the linear branch when the softmax branch alone covers the current chunk
+    (ops_for_incomplete_chunks='attn'): the recurrence then walks 64-token chunks (every chunk of a selected block
+    updates the state, chunks of other blocks only decay it; src/nats/ops/common/chunk_delta_h.py:189-324), which
+    is the plain walk on the block types repeated per chunk."""
+    cpb = nats_block_size // CHUNK_SIZE
+    NT = -(-T // CHUNK_SIZE)
+    per_chunk = torch.round(nats_block_types).repeat_interleave(cpb, dim=1)[:, :NT].contiguous()
+    return build_selection_tables(per_chunk, T, CHUNK_SIZE)
+
+
 class NAtSMixedAttentionGDN(torch.autograd.Function):
     """Forward of mixed_attn_gdn.py:47-191.  Backward (mixed_attn_gdn.py:196-283) is not built yet
     and raises."""
@@ -58,13 +69,15 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
         _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
                       all_incomplete_ops)
         strategy = all_incomplete_ops[ops_for_incomplete_chunks]
-        if not strategy['gated_delta_net']:
-            raise NotImplementedError("ops_for_incomplete_chunks='attn' (no own-block linear term) is not built")
-        if not incomplete_block_start_with_ht:
+        own_linear = strategy['gated_delta_net']
+        if own_linear and not incomplete_block_start_with_ht:
             raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
         T = q_lattn.shape[1]
         tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
         if q_lattn.dtype == torch.float32:
+            if not own_linear:
+                raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
             # fp32 tensors take the reference-precision kernels (token recurrence with re-roll, fp32 softmax)
             o_attn, lse = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
             o_gdn, ht, _ = _ops.linear_recurrent(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
@@ -79,9 +92,10 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
-        o_gdn, ht, _ = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
+        o_gdn, ht, _ = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, lin_tables, scale_lattn,
                                        initial_state_gated_delta, decay_for_non_gdn_blocks,
-                                       lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta)
+                                       lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta,
+                                       own_chunk=own_linear)
         cur.wait_stream(side)
         for t_ in (q_attn, k_attn, v_attn, o_attn, lse):
             t_.record_stream(side)

@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib, _ops
-from .mixed_attn_gdn import _check_common, _chunk_start_state
+from .mixed_attn_gdn import _check_common, _chunk_start_state, per_chunk_tables
 from .nats_util import build_selection_tables
 
 # mixed_attn_mamba.py:33-46
@@ -42,8 +42,9 @@ def nats_mixed_attn_mamba(
     _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
                   all_incomplete_ops)
     strategy = all_incomplete_ops[ops_for_incomplete_chunks]
-    if not strategy['mamba'] or not incomplete_block_start_with_ht:
-        raise NotImplementedError("only own-block linear attention starting from the carried state is built")
+    own_linear = strategy['mamba']
+    if own_linear and not incomplete_block_start_with_ht:
+        raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
     if scale_attn is None:
         scale_attn = k_attn.shape[-1] ** -0.5
     if scale_lattn is None:
@@ -51,15 +52,18 @@ def nats_mixed_attn_mamba(
     T = q_lattn.shape[1]
     with torch.no_grad():
         tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
         if q_lattn.dtype == torch.float32:
+            if not own_linear:
+                raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
             o_attn, _ = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
             o_m, ht, _ = _ops.linear_recurrent(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
                                                initial_state_mamba, decay_for_non_mamba_blocks, False)
             return o_m, o_attn, (ht if output_final_state_mamba else None)
         o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
-        o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
+        o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, lin_tables, scale_lattn,
                                      initial_state_mamba, decay_for_non_mamba_blocks, False,
-                                     output_final_state_mamba)
+                                     output_final_state_mamba, own_chunk=own_linear)
     return o_m, o_attn, ht
 
 

@@ -94,8 +94,17 @@ class CudaSegmentOps:
     def attn(self, q, k, v, tables, scale, own_chunk, q_off):
         return _ops.attn_fwd(q, k, v, tables, scale, own_chunk, q_off=q_off)[0]
 
-    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk):
-        return _ops.attn_fwd_split(q, k_rem, v_rem, k, v, tables, scale, own_chunk)
+    def pack_pairs(self, x, tables, cap_pairs):
+        B, T, H, D = x.shape
+        nbs = tables.nats_block_size
+        packed = torch.empty(B, cap_pairs * nbs, D, dtype=x.dtype, device=x.device)     # the tail past the last pair is never read
+        _lib.call("natsl_pack_selected_pairs", x.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
+                  packed.data_ptr(), B, T, H, tables.types_i.shape[2], D, nbs, 0, cap_pairs,
+                  current_stream_ptr(x.device))
+        return packed
+
+    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk, rem_base, rem_slots):
+        return _ops.attn_fwd_split(q, k_rem, v_rem, k, v, tables, scale, own_chunk, rem_base, rem_slots)
 
     def n_attn_blocks(self, tables):
         return tables.n_blocks[..., 0].contiguous()          # [B, HN] int32
@@ -253,23 +262,29 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
     # ---- softmax branch, part 2 (main stream): gather the selected blocks, one attention launch for all segments
     cap = 0
     if world > 1:
-        cap = int(n_all.max().item())                        # the one host read: capacity of the gather
+        HKV = ka.shape[2]
+        n_g = n_all.reshape(n_glob, B, -1).to(torch.int64)                               # gathered order
+        n_h = n_g.repeat_interleave(HKV // n_g.shape[2], dim=2)                          # per key/value head
+        # the one host read: virtual slots per head and capacity (in pairs) of the gather
+        cap, cap_pairs = (int(x) for x in torch.stack([n_g.max(), n_h.sum(2).max()]).tolist())
         step = max(1, 128 // nbs)
         cap = -(-cap // step) * step                         # keeps the query offset a multiple of 128
     if cap == 0:
         o_attn = be.attn(qa, ka, va, tb, scale_attn, own, 0)
     else:
-        k_all = _all_gather(be.pack(ka, tb, cap), world, group)                          # [world, n_seg*B, cap*nbs, H, D]
-        v_all = _all_gather(be.pack(va, tb, cap), world, group)
-        S_rem = n_glob * cap * nbs
+        # selected (block, head) pairs of every segment, packed back to back: [world, n_seg*B, cap_pairs*nbs, D]
+        k_all = _all_gather(be.pack_pairs(ka, tb, cap_pairs), world, group)
+        v_all = _all_gather(be.pack_pairs(va, tb, cap_pairs), world, group)
 
-        def flat(x):                    # -> [B, n_glob*cap*nbs, H, D], gathered order (a view when B = 1)
-            x = x.reshape(n_glob, B, cap * nbs, *x.shape[3:])
-            return x.permute(1, 0, 2, 3, 4).reshape(B, S_rem, *x.shape[3:]).contiguous()
+        def flat(x):                    # -> [B, n_glob*cap_pairs*nbs, D], gathered order (a view when B = 1)
+            x = x.reshape(n_glob, B, cap_pairs * nbs, x.shape[-1])
+            return x.permute(1, 0, 2, 3).reshape(B, n_glob * cap_pairs * nbs, x.shape[-1]).contiguous()
 
-        types_virt = virtual_attn_types(n_all.reshape(n_glob, B, -1).to(torch.int64), gathered_ids, seg, cap, types_s)
-        tb_v = be.tables(types_virt, S_rem + L, nbs)
-        o_attn = be.attn_split(qa, flat(k_all), flat(v_all), ka, va, tb_v, scale_attn, own)
+        seg_base = torch.arange(n_glob, device=dev).view(n_glob, 1, 1) * cap_pairs
+        rem_base = (n_h.cumsum(2) - n_h + seg_base).permute(1, 0, 2).to(torch.int32).contiguous()   # [B, n_glob, HKV]
+        types_virt = virtual_attn_types(n_g, gathered_ids, seg, cap, types_s)
+        tb_v = be.tables(types_virt, n_glob * cap * nbs + L, nbs)
+        o_attn = be.attn_split(qa, flat(k_all), flat(v_all), ka, va, tb_v, scale_attn, own, rem_base, cap)
 
     # ---- linear branch, part 2 (side stream): fold the earlier segments, rerun from the true starting states
     with on_side():

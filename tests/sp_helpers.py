@@ -59,11 +59,44 @@ class OracleSegmentOps:
             f = f * a[n]
         return (torch.stack(pre) if want_prefix else None), p, f
 
-    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk):
-        rep = q.shape[0] // k_rem.shape[0]                 # the gathered keys are shared by the local segments
-        k_virt = torch.cat([k_rem.repeat(rep, 1, 1, 1), k], 1)
-        v_virt = torch.cat([v_rem.repeat(rep, 1, 1, 1), v], 1)
-        return self.attn(q, k_virt, v_virt, tables, scale, own_chunk, k_rem.shape[1])
+    def pack_pairs(self, x, tables, cap_pairs):
+        B, T, H, D = x.shape
+        nbs = tables.nats_block_size
+        HN = tables.types_i.shape[2]
+        out = torch.zeros(B, cap_pairs * nbs, D, dtype=x.dtype)
+        for b in range(B):
+            p = 0
+            for h in range(H):
+                hn = h // (H // HN)
+                for j in range(int(tables.n_blocks[b, hn, 0])):
+                    blk = int(tables.indices[b, j, hn, 0])
+                    seg = x[b, blk * nbs:(blk + 1) * nbs, h]
+                    if p < cap_pairs:
+                        out[b, p * nbs:p * nbs + seg.shape[0]] = seg
+                    p += 1
+        return out
+
+    def attn_split(self, q, k_rem, v_rem, k, v, tables, scale, own_chunk, rem_base, rem_slots):
+        nbs = tables.nats_block_size
+        B_rem, G, HKV = rem_base.shape
+        S = G * rem_slots * nbs
+
+        def unpack(x):                                     # pairs -> [B_rem, S, HKV, D] virtual layout (zeros elsewhere)
+            out = torch.zeros(B_rem, S, HKV, x.shape[-1], dtype=x.dtype)
+            n_pairs = x.shape[1] // nbs
+            for b in range(B_rem):
+                for g in range(G):
+                    for h in range(HKV):
+                        for j in range(rem_slots):
+                            p = int(rem_base[b, g, h]) + j
+                            if p < n_pairs:
+                                out[b, (g * rem_slots + j) * nbs:(g * rem_slots + j + 1) * nbs, h] = x[b, p * nbs:(p + 1) * nbs]
+            return out
+
+        rep = q.shape[0] // B_rem                          # the gathered keys are shared by the local segments
+        k_virt = torch.cat([unpack(k_rem).repeat(rep, 1, 1, 1), k], 1)
+        v_virt = torch.cat([unpack(v_rem).repeat(rep, 1, 1, 1), v], 1)
+        return self.attn(q, k_virt, v_virt, tables, scale, own_chunk, S)
 
     def pack(self, x, tables, cap_blocks):
         B, T, H, D = x.shape

@@ -194,6 +194,46 @@ def test_op_level_gdn_matches_recurrent_oracle(nat):
     assert_close(ht, s_ref, 2 * TOL, "final_state")
 
 
+@pytest.mark.parametrize("mode", ["all", "attn", "gated_delta_net"])
+@pytest.mark.parametrize("T,nbs,K,V", [(512, 64, 64, 64), (700, 128, 128, 128), (1024, 256, 128, 64)])
+def test_ops_for_incomplete_chunks_modes_gdn(nat, mode, T, nbs, K, V):
+    """The three modes of mixed_attn_gdn.py:35-42: which branch covers the current chunk."""
+    B, H = 2, 4
+    q, k, v, g, beta, _ = synth_gdn_inputs(B, T, H, K, V, seed=T)
+    types = otab.synth_types(B, -(-T // nbs), 2, 0.5, seed=nbs)
+    types[:, -1] = 1
+    cu = lambda x: x.cuda()
+    o_l, o_a, ht = nat.nats_mixed_attn_gdn(cu(q), cu(k), cu(v), cu(q), cu(k), cu(v), None, cu(g), cu(beta), cu(types),
+                                           None, nats_block_size=nbs, ops_for_incomplete_chunks=mode,
+                                           output_final_state_gated_delta=True, decay_for_non_gdn_blocks=True)
+    o_ref, s_ref = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, beta.float(), types[..., 1], nbs=nbs,
+                                     own_chunk=(mode != "attn"))
+    mask = oattn.attn_mask(types[..., 0], T, nbs, H, own_chunk=(mode != "gated_delta_net"))
+    oa_ref, _ = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask)
+    assert_close(o_l, o_ref, TOL, f"o_gdn ({mode})")
+    assert_close(o_a, oa_ref, TOL, f"o_attn ({mode})")
+    assert_close(ht, s_ref, 2 * TOL, f"final_state ({mode})")
+
+
+@pytest.mark.parametrize("mode", ["attn", "mamba"])
+def test_ops_for_incomplete_chunks_modes_mamba(nat, mode):
+    B, T, H, K, V, nbs = 1, 1024, 4, 128, 64, 256
+    q, k, v, g, _ = synth_mamba_inputs(B, T, H, K, V, seed=5)
+    types = otab.synth_types(B, T // nbs, H, 0.4, seed=6)
+    types[:, -1] = 1
+    cu = lambda x: x.cuda()
+    o_l, o_a, ht = nat.nats_mixed_attn_mamba(cu(q), cu(k), cu(v), cu(q), cu(k), cu(v), None, cu(g), cu(types), None,
+                                             scale_attn=K ** -0.5, nats_block_size=nbs, ops_for_incomplete_chunks=mode,
+                                             output_final_state_mamba=True, decay_for_non_mamba_blocks=True)
+    o_ref, s_ref = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, None, types[..., 1], nbs=nbs, scale=1.0,
+                                     use_l2norm=False, rule="mamba", own_chunk=(mode != "attn"))
+    mask = oattn.attn_mask(types[..., 0], T, nbs, H, own_chunk=(mode != "mamba"))
+    oa_ref, _ = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask, K ** -0.5)
+    assert_close(o_l, o_ref, TOL, f"o_mamba ({mode})")
+    assert_close(o_a, oa_ref, TOL, f"o_attn ({mode})")
+    assert_close(ht, s_ref, 2 * TOL, f"final_state ({mode})")
+
+
 def test_error_paths(nat):
     from neuralattentionsearchlinear_b200 import _lib
     types = otab.synth_types(1, 4, 2, 0.5, seed=0).cuda()

@@ -124,3 +124,35 @@ def test_attn_split_equals_concatenated_keys(DK, DV, nbs):
         oj, _ = _ops.attn_fwd(q[sl].contiguous(), kc, vc, tbj, DK ** -0.5, True, q_off=S)
         assert torch.equal(o[sl], oj)
     assert _lib.load().natsl_device_status() == 0
+
+
+@pytest.mark.parametrize("DK,DV,nbs,HKV,HN", [(128, 64, 128, 4, 2), (64, 64, 256, 2, 2)])
+def test_attn_split_packed_pairs_equals_head_major(DK, DV, nbs, HKV, HN):
+    """The gathered keys as packed (block, head) pairs against the padded head-major layout: bit-identical."""
+    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200.sequence_parallel import CudaSegmentOps, virtual_attn_types
+    dev = torch.device("cuda", 0)
+    be = CudaSegmentOps()
+    G, B, n_loc, Lr, L, HQ = 3, 1, 2, 1024, 512, 4
+    gen = torch.Generator().manual_seed(31)
+    rnd = lambda *s: torch.randn(*s, generator=gen).bfloat16().to(dev)
+    k_g, v_g = rnd(G, Lr, HKV, DK), rnd(G, Lr, HKV, DV)                  # the G remote segments as a batch
+    types_g = otab.synth_types(G, Lr // nbs, HN, 0.5, seed=32).to(dev)
+    tb_g = be.tables(types_g, Lr, nbs)
+    n_g = tb_g.n_blocks[..., 0].to(torch.int64).view(G, B, HN)
+    n_h = n_g.repeat_interleave(HKV // HN, dim=2)
+    vcap, cap_pairs = int(n_g.max()), int(n_h.sum(2).max())
+    assert vcap > 0
+    q, k, v = rnd(n_loc * B, L, HQ, DK), rnd(n_loc * B, L, HKV, DK), rnd(n_loc * B, L, HKV, DV)
+    types_l = otab.synth_types(n_loc * B, L // nbs, HN, 0.5, seed=33).to(dev)
+    types_v = virtual_attn_types(n_g, torch.tensor([0, 1, 2]), [3, 4], vcap, types_l)
+    tb_v = be.tables(types_v, G * vcap * nbs + L, nbs)
+    hm = lambda x: be.pack(x, tb_g, vcap).reshape(1, G * vcap * nbs, HKV, x.shape[-1])
+    o_hm = be.attn_split(q, hm(k_g), hm(v_g), k, v, tb_v, DK ** -0.5, True, None, 0)
+    pp = lambda x: be.pack_pairs(x, tb_g, cap_pairs).reshape(1, G * cap_pairs * nbs, x.shape[-1])
+    seg_base = torch.arange(G, device=dev).view(G, 1, 1) * cap_pairs
+    rem_base = (n_h.cumsum(2) - n_h + seg_base).permute(1, 0, 2).to(torch.int32).contiguous()
+    o_pp = be.attn_split(q, pp(k_g), pp(v_g), k, v, tb_v, DK ** -0.5, True, rem_base, vcap)
+    torch.cuda.synchronize()
+    assert torch.equal(o_hm, o_pp)
+    assert _lib.load().natsl_device_status() == 0
