@@ -424,6 +424,10 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
     q, k, v, g, types = (torch.cat(parts[n], 1).to(dev) for n in ("q", "k", "v", "g", "types"))
     stream = torch.cuda.current_stream(dev)
 
+    from neuralattentionsearchlinear_b200 import sequence_parallel as sp
+    lin_group = dist.new_group() if dist is not None else None      # own communicator for the state exchange
+    kv_cap = None
+
     def step():
         if args.sp_plain_op and world == 1:               # the layer's plain op: serial recurrence over the whole sequence
             return nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5, nats_block_size=nbs,
@@ -431,7 +435,8 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
                                              decay_for_non_mamba_blocks=True)
         return nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
                                         decay_for_non_mamba_blocks=True, layout=layout,
-                                        linear_splits=args.sp_linear_splits or None)
+                                        linear_splits=args.sp_linear_splits or None, kv_capacity=kv_cap,
+                                        linear_group=lin_group)
 
     def barrier():
         if dist is not None:
@@ -441,10 +446,18 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
+    run_step, mode = step, "eager, gather capacity read back every step (one host synchronisation)"
+    if args.sp_fixed_capacity:
+        # gather capacity fixed to the exact maxima of this input (read back by the warm-up steps): no host read
+        kv_cap = sp.last_kv_capacity
+        mode = "eager, caller-given gather capacity (no host synchronisation)"
+        for _ in range(3):
+            step()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
-        step()
+        run_step()
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
@@ -460,7 +473,7 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                           "data": "synthetic (seeded, generated per rank)",
                           "config": {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 "
-                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({layout} segments)"},
+                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({layout} segments)", "launch": mode},
                           "device_status": status}))
     if dist is not None:
         dist.destroy_process_group()
@@ -479,6 +492,9 @@ def main():
                     help="segment layout of the sequence-parallel workload (mamba_long)")
     ap.add_argument("--sp-linear-splits", type=int, default=0,
                     help="sub-segments per segment in the linear branch of mamba_long (0: about 1024 tokens each)")
+    ap.add_argument("--sp-fixed-capacity", action="store_true",
+                    help="mamba_long: size the key/value gather from a capacity fixed before the timed region instead of "
+                         "reading the block counts back every step")
     ap.add_argument("--sp-plain-op", action="store_true",
                     help="mamba_long on one GPU through nats_mixed_attn_mamba (no sub-segment split, one stream)")
     ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long"],

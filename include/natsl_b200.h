@@ -52,8 +52,9 @@ const char* natsl_last_error(void);
 int natsl_abi_version(void);
 
 /* Synchronises the current device and returns (and clears) its status word: 0 = every kernel ran to
- * completion; non-zero = a kernel gave up a bounded wait and its outputs are invalid.  The tensor-core
- * kernels never spin forever; they record the failure here instead. */
+ * completion; 1 = a kernel gave up a bounded wait (the tensor-core kernels never spin forever; they record
+ * the failure here instead); 2 = misaligned shared memory; 3 = a capacity given by the caller was too small
+ * (natsl_pack_selected_pairs).  Non-zero means the outputs of the kernels since the last call are invalid. */
 int natsl_device_status(void);
 
 /* Selection tables from the op types [B,TN,HN,2] (column 0 softmax, column 1 linear).
@@ -185,8 +186,9 @@ int natsl_attn_fwd_fp32(int dtype, const void* q, const void* k, const void* v, 
  * natsl_pack_selected_blocks: packed [B, cap_blocks*nbs, H, D] <- the selected blocks (column `op`) of
  *   x [B,T,H,D] bf16 in index-table order, per head; slots past the number of selected blocks are left untouched.
  * natsl_pack_selected_pairs: packed [B, cap_pairs*nbs, D] <- the same blocks with no padding: the selected
- *   (block, head) pairs of a batch entry back to back, head-major (all blocks of head 0, then head 1, ...); pairs
- *   beyond cap_pairs are dropped. */
+ *   (block, head) pairs of a batch entry back to back, head-major (all blocks of head 0, then head 1, ...).  A
+ *   batch entry with more than cap_pairs pairs, or a head with more than max_per_head blocks (0 = no limit),
+ *   sets device status 3 and the surplus is dropped. */
 int natsl_sp_segment_decay(const float* gcs, const int32_t* types_i, float* a, float* trail, int B, int T, int H,
                            int HN, int nbs, int flags, void* stream);
 int natsl_sp_state_combine(const float* a, const float* S, float* h_in, int rank, int world, int B, int H, int K, int V,
@@ -196,7 +198,8 @@ int natsl_sp_prefix_states(const float* a, const float* S, const float* h0, floa
 int natsl_pack_selected_blocks(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
                                int T, int H, int HN, int D, int nbs, int op, int cap_blocks, void* stream);
 int natsl_pack_selected_pairs(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed, int B,
-                              int T, int H, int HN, int D, int nbs, int op, int cap_pairs, void* stream);
+                              int T, int H, int HN, int D, int nbs, int op, int cap_pairs, int max_per_head,
+                              void* stream);
 
 /* Output mixing: y = (x1 rstd1 w1 a + x2 rstd2 w2 b) * g * sigmoid(g) over rows of D (64/128/256) bf16
  * elements; xw [rows,2] = (a, b) or NULL; w1, w2 [D] or NULL; activation 0 = swish, 1 = sigmoid.

@@ -26,7 +26,7 @@ PROTOTYPES = {
     "natsl_attn_fwd_ex": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_attn_fwd_split": [_p, _p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                              _i, _f, _i, _p],
-    "natsl_pack_selected_pairs": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_pack_selected_pairs": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "natsl_sp_prefix_states": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "natsl_sp_segment_decay": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "natsl_sp_state_combine": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p],

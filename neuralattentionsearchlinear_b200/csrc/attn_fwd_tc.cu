@@ -55,14 +55,35 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// packed tile descriptor: bits [0,30) first key, bit 30 masked, bit 31 block selected
-__device__ __forceinline__ int pack_tile(const TileWalk& w, int j, const int* idx, const int* selp, long tstride, int nbs) {
+// Where the gathered part of the key sequence lives (keys below k_split; see the kernel's comment).
+struct RemoteKeys {
+    int k_split;          // keys [0, k_split) are gathered keys
+    const int* base;      // first pair of (segment g, this head): base[g * stride], or nullptr for the head-major layout
+    int stride;
+    int slots;            // virtual blocks per head and gathered segment
+};
+
+// Packed tile descriptor: bits [0,29) token coordinate of the first key in the tensor it is loaded from (own keys:
+// index in k / v; gathered keys: index in k_rem / v_rem), bit 29 gathered, bit 30 masked, bit 31 block selected.
+// Masked tiles always lie in the own keys, where coordinate + k_split is the position in the key sequence.
+__device__ __forceinline__ int pack_tile(const TileWalk& w, int j, const int* idx, const int* selp, long tstride, int nbs,
+                                         const RemoteKeys& rk) {
     bool masked;
-    int s0 = tile_start(w, j, idx, tstride, nbs, masked);
+    const int s0 = tile_start(w, j, idx, tstride, nbs, masked);
     int sel = 1;
     if (masked) sel = selp[(long)(s0 / nbs) * tstride] != 0;
-    return s0 | (masked ? (1 << 30) : 0) | (sel ? (1 << 31) : 0);
+    int coord = s0 - rk.k_split, rem = 0;
+    if (s0 < rk.k_split) {
+        rem = 1;
+        coord = s0;
+        if (rk.base) {
+            const int vb = s0 / nbs, g = vb / rk.slots;
+            coord = (rk.base[(long)g * rk.stride] + (vb - g * rk.slots)) * nbs + (s0 - vb * nbs);
+        }
+    }
+    return coord | (rem << 29) | (masked ? (1 << 30) : 0) | (sel ? (1 << 31) : 0);
 }
+constexpr int TILE_COORD_MASK = 0x1FFFFFFF;
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(TC_THREADS, 2)
@@ -128,18 +149,24 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
     const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
     const int n_tiles = walk.n_tiles;
-    for (int j = tid; j < min(n_tiles, TC_LIST_CAP); j += TC_THREADS) tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs);
+    const int b_rem = b % B_rem;
+    RemoteKeys rk;
+    rk.k_split = k_split;
+    rk.slots = rem_slots;
+    rk.stride = HKV;
+    rk.base = rem_base ? rem_base + ((long)b_rem * (k_split / (rem_slots * nbs))) * HKV + hkv : nullptr;
+    for (int j = tid; j < min(n_tiles, TC_LIST_CAP); j += TC_THREADS)
+        tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs, rk);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     auto tile_desc = [&](int j) -> int {
-        return j < TC_LIST_CAP ? tile_list[j] : pack_tile(walk, j, idx, selp, tstride, nbs);
+        return j < TC_LIST_CAP ? tile_list[j] : pack_tile(walk, j, idx, selp, tstride, nbs, rk);
     };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        const int b_rem = b % B_rem;
         if (lane == 0) {
             prefetch_tensormap(&map_k);
             prefetch_tensormap(&map_v);
@@ -148,42 +175,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 prefetch_tensormap(&map_vr);
             }
         }
-        // token coordinate of gathered key s in its tensor (head coordinate rem_head)
-        const int rem_head = rem_base ? 0 : hkv;
-        const int n_seg_rem = rem_base ? k_split / (rem_slots * nbs) : 0;
-        auto rem_token = [&](int s) -> int {
-            if (!rem_base) return s;
-            const int vb = s / nbs, g = vb / rem_slots;
-            return (rem_base[((long)b_rem * n_seg_rem + g) * HKV + hkv] + (vb - g * rem_slots)) * nbs + (s - vb * nbs);
-        };
+        const int rem_head = rem_base ? 0 : hkv;     // packed pairs have no head axis
         auto load_k = [&](int j) {                    // lane 0 only
-            const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_KST;
-            const bool rem = s0 < k_split;
-            const CUtensorMap* mk = rem ? &map_kr : &map_k;
-            const int ts = rem ? rem_token(s0) : s0 - k_split, bs = rem ? b_rem : b, hs = rem ? rem_head : hkv;
+            const int td = tile_desc(j), stg = j % TC_KST;
+            const bool rem = (td >> 29) & 1;
             const uint32_t full = bar_k_full + stg * 8;
             mbar_expect_tx(full, 64 * DK * 2);
 #pragma unroll
             for (int sub = 0; sub < DK / 64; ++sub)
-                tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, mk, sub * 64, hs, ts, bs, full);
+                tma_load_4d(s_k + stg * (64 * DK * 2) + sub * 8192, rem ? &map_kr : &map_k, sub * 64, rem ? rem_head : hkv,
+                            td & TILE_COORD_MASK, rem ? b_rem : b, full);
         };
         auto load_v = [&](int j) {                    // lane 0 only; also warms L2 for the tile TC_VST further on
-            const int s0 = tile_desc(j) & 0x3FFFFFFF, stg = j % TC_VST;
-            const bool rem = s0 < k_split;
+            const int td = tile_desc(j), stg = j % TC_VST;
+            const bool rem = (td >> 29) & 1;
             const uint32_t full = bar_v_full + stg * 8;
             mbar_expect_tx(full, 64 * DV * 2);
 #pragma unroll
             for (int sub = 0; sub < DV / 64; ++sub)
                 tma_load_4d(s_v + stg * (64 * DV * 2) + sub * 8192, rem ? &map_vr : &map_v, sub * 64, rem ? rem_head : hkv,
-                            rem ? rem_token(s0) : s0 - k_split, rem ? b_rem : b, full);
+                            td & TILE_COORD_MASK, rem ? b_rem : b, full);
             if (j + TC_VST < n_tiles) {
-                const int s1 = tile_desc(j + TC_VST) & 0x3FFFFFFF;
-                const bool rem1 = s1 < k_split;
-                const int t1 = rem1 ? rem_token(s1) : s1 - k_split, b1 = rem1 ? b_rem : b, h1 = rem1 ? rem_head : hkv;
+                const int t1 = tile_desc(j + TC_VST);
+                const bool rem1 = (t1 >> 29) & 1;
+                const int c1 = t1 & TILE_COORD_MASK, b1 = rem1 ? b_rem : b, h1 = rem1 ? rem_head : hkv;
 #pragma unroll
-                for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, h1, t1, b1);
+                for (int sub = 0; sub < DV / 64; ++sub) tma_prefetch_4d(rem1 ? &map_vr : &map_v, sub * 64, h1, c1, b1);
 #pragma unroll
-                for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, h1, t1, b1);
+                for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, h1, c1, b1);
             }
         };
         // The loads follow the order in which the tensor core frees the ring stages: the K stages of the first two
@@ -289,7 +308,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int td = tile_desc(j);
             if ((td >> 30) & 1) {
                 // own-span tile: per row the visible keys are columns [0, limit] (attn_walk.cuh: visible())
-                const int s0 = td & 0x3FFFFFFF;
+                const int s0 = (td & TILE_COORD_MASK) + k_split;     // masked tiles lie in the own keys
                 const bool selb = (td >> 31) & 1;
                 const int blk_end = (s0 / nbs + 1) * nbs;
                 int lim_a = T - 1 - s0, lim_b = lim_a;

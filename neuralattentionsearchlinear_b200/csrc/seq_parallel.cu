@@ -11,7 +11,7 @@
 // Softmax branch: a rank only needs the *selected* key/value blocks of earlier ranks.
 // natsl_pack_selected_blocks compacts them per head (index table order) into a token-major buffer
 // that is all-gathered and placed in front of the rank's own keys.
-#include "common.cuh"
+#include "tc_common.cuh"
 #include "../../include/natsl_b200.h"
 
 namespace natsl {
@@ -93,16 +93,21 @@ pack_blocks_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ 
 // packed[b, p*nbs + i, :].
 __global__ void __launch_bounds__(256)
 pack_pairs_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ indices, const int* __restrict__ n_blocks,
-                  __nv_bfloat16* __restrict__ packed, int T, int H, int HN, int TN, int D, int nbs, int op, int cap) {
+                  __nv_bfloat16* __restrict__ packed, int T, int H, int HN, int TN, int D, int nbs, int op, int cap,
+                  int max_per_head, int* status) {
     const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int G = H / HN, hn = h / G;
     const int n = n_blocks[((long)b * HN + hn) * 2 + op];
     if (j >= n) return;
+    if (max_per_head > 0 && n > max_per_head && threadIdx.x == 0) atomicExch(status, NATSL_DEV_CAPACITY);
     int base = 0;
     for (int g = 0; g < hn; ++g) base += n_blocks[((long)b * HN + g) * 2 + op];
     base = base * G + (h - hn * G) * n;
     const int pidx = base + j;
-    if (pidx >= cap) return;
+    if (pidx >= cap) {
+        if (threadIdx.x == 0) atomicExch(status, NATSL_DEV_CAPACITY);
+        return;
+    }
     const int blk = indices[(((long)b * TN + j) * HN + hn) * 2 + op];
     const int cpr = D / 8;                          // 16-byte chunks per row
     for (int e = threadIdx.x; e < nbs * cpr; e += blockDim.x) {
@@ -170,17 +175,20 @@ extern "C" int natsl_pack_selected_blocks(const void* x, const int32_t* indices,
 
 extern "C" int natsl_pack_selected_pairs(const void* x, const int32_t* indices, const int32_t* n_blocks, void* packed,
                                          int B, int T, int H, int HN, int D, int nbs, int op, int cap_pairs,
-                                         void* stream) {
+                                         int max_per_head, void* stream) {
     using namespace natsl;
     NATSL_REQUIRE(x && indices && n_blocks && packed, NATSL_ERR_NULL, "natsl_pack_selected_pairs: null pointer");
     NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && HN > 0 && H % HN == 0 && D % 8 == 0 && (op == 0 || op == 1),
                   NATSL_ERR_BAD_SHAPE, "natsl_pack_selected_pairs: bad shape");
     NATSL_REQUIRE(H <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_pack_selected_pairs: B, H <= 65535");
     if (cap_pairs <= 0) return NATSL_OK;
+    int* status = nullptr;
+    int rc = status_word_ptr(&status);
+    if (rc != NATSL_OK) return rc;
     const int TN = (T + nbs - 1) / nbs;
     dim3 grid(TN, H, B);
     pack_pairs_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const __nv_bfloat16*>(x), indices, n_blocks, reinterpret_cast<__nv_bfloat16*>(packed), T, H, HN,
-        TN, D, nbs, op, cap_pairs);
+        TN, D, nbs, op, cap_pairs, max_per_head, status);
     return check_launch("natsl_pack_selected_pairs");
 }

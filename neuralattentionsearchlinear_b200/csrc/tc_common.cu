@@ -91,7 +91,9 @@ extern "C" int natsl_device_status(void) {
     }
     if (v != 0) {
         cudaMemset(p, 0, sizeof(int));
-        set_error("a kernel gave up a bounded wait (device status %d); its outputs are invalid", v);
+        set_error(v == NATSL_DEV_CAPACITY
+                      ? "a caller-given capacity was too small (device status %d); the outputs are invalid"
+                      : "a kernel gave up a bounded wait (device status %d); its outputs are invalid", v);
     }
     return v;
 }

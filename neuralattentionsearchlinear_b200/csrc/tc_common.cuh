@@ -18,7 +18,8 @@ namespace natsl {
 
 // ------------------------------------------------------------------ device status word
 // Set by kernels whose bounded waits gave up; read (and cleared) by natsl_device_status().
-enum : int { NATSL_DEV_OK = 0, NATSL_DEV_WAIT_TIMEOUT = 1 };
+// (2 = misaligned shared memory in a tensor-core kernel, 3 = a caller-given capacity was too small.)
+enum : int { NATSL_DEV_OK = 0, NATSL_DEV_WAIT_TIMEOUT = 1, NATSL_DEV_CAPACITY = 3 };
 // Host: device address of the status word on the current device (looked up once per device).
 int status_word_ptr(int** out);
 

@@ -35,6 +35,7 @@ from . import _lib, _ops
 from .nats_util import build_selection_tables, current_stream_ptr
 
 _side_streams: dict = {}
+last_kv_capacity = None          # (blocks per head, pairs) the last call without ``kv_capacity`` read back
 
 
 class CudaSegmentOps:
@@ -94,12 +95,12 @@ class CudaSegmentOps:
     def attn(self, q, k, v, tables, scale, own_chunk, q_off):
         return _ops.attn_fwd(q, k, v, tables, scale, own_chunk, q_off=q_off)[0]
 
-    def pack_pairs(self, x, tables, cap_pairs):
+    def pack_pairs(self, x, tables, cap_pairs, max_per_head=0):
         B, T, H, D = x.shape
         nbs = tables.nats_block_size
         packed = torch.empty(B, cap_pairs * nbs, D, dtype=x.dtype, device=x.device)     # the tail past the last pair is never read
         _lib.call("natsl_pack_selected_pairs", x.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
-                  packed.data_ptr(), B, T, H, tables.types_i.shape[2], D, nbs, 0, cap_pairs,
+                  packed.data_ptr(), B, T, H, tables.types_i.shape[2], D, nbs, 0, cap_pairs, int(max_per_head),
                   current_stream_ptr(x.device))
         return packed
 
@@ -139,6 +140,11 @@ def _layout_constants(world: int, layout: str, device_str: str):
     return torch.tensor(flat_ids, device=dev), torch.tensor(order, device=dev)
 
 
+@functools.lru_cache(maxsize=None)
+def _ids_tensor(ids: tuple, device_str: str) -> torch.Tensor:
+    return torch.tensor(list(ids), device=torch.device(device_str))
+
+
 def virtual_attn_types(n_all: torch.Tensor, gathered_ids: torch.Tensor, my_ids, cap: int,
                        types_local: torch.Tensor) -> torch.Tensor:
     """Block types of the virtual key sequences [G x cap gathered slots | own blocks] of the rank's segments.
@@ -149,7 +155,7 @@ def virtual_attn_types(n_all: torch.Tensor, gathered_ids: torch.Tensor, my_ids, 
     G, B, HN = n_all.shape
     dev = types_local.device
     n = len(my_ids)
-    mine = torch.tensor(list(my_ids), device=dev).view(n, 1, 1, 1, 1)
+    mine = _ids_tensor(tuple(my_ids), str(dev)).view(n, 1, 1, 1, 1)       # cached: no host copy inside a graph capture
     slot = torch.arange(cap, device=dev).view(1, 1, 1, cap, 1)
     vis = gathered_ids.to(dev).view(1, 1, G, 1, 1) < mine
     sel = vis & (slot < n_all.permute(1, 0, 2).reshape(1, B, G, 1, HN))                  # [n,B,G,cap,HN]
@@ -188,13 +194,19 @@ def _merge(x, B, n):                    # inverse of _split
 def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g, nats_block_types, *,
                              nats_block_size: int = 256, scale_attn=None, scale_lattn=1.0,
                              ops_for_incomplete_chunks: str = 'all', decay_for_non_mamba_blocks: bool = True,
-                             layout: str = 'contiguous', linear_splits=None, group=None, backend=None):
+                             layout: str = 'contiguous', linear_splits=None, kv_capacity=None, group=None,
+                             linear_group=None, backend=None):
     """One rank's share of ``nats_mixed_attn_mamba`` on a sequence split over the ranks of ``group`` (also usable
     with a single rank, where only the sub-segment split of the linear branch remains).
     All tensors hold this rank's segment(s) along the time axis ([B, T_local, ...]; block types
     [B, TN_local, HN, 2]); with ``layout='zigzag'`` T_local covers the rank's two equally long segments one after
     the other (see ``segment_ids``).  ``linear_splits``: sub-segments per segment in the linear branch (default:
-    about 1024 tokens each).
+    about 1024 tokens each).  ``kv_capacity`` = (softmax-selected blocks per head, selected (block, head) pairs) a
+    segment may have at most: sizes the key/value gather without reading the counts back to the host (no host
+    synchronisation, so the call can be captured in a CUDA graph); if a segment exceeds it the device status
+    (``natsl_device_status``) reads 3 and the outputs are invalid.  Without it the exact maxima are read back (one
+    host synchronisation) and left in ``last_kv_capacity``.  ``linear_group``: a second process group over the same
+    ranks for the collectives of the linear branch, so that they do not queue behind the key/value gather.
     -> (o_mamba [B,T_local,H,V], o_attn [B,T_local,HQ,V_attn], final_state [B,H,K,V] fp32 on the rank that holds
     the last segment, else None)."""
     if ops_for_incomplete_chunks not in ('all', 'mamba'):
@@ -265,16 +277,23 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
         HKV = ka.shape[2]
         n_g = n_all.reshape(n_glob, B, -1).to(torch.int64)                               # gathered order
         n_h = n_g.repeat_interleave(HKV // n_g.shape[2], dim=2)                          # per key/value head
-        # the one host read: virtual slots per head and capacity (in pairs) of the gather
-        cap, cap_pairs = (int(x) for x in torch.stack([n_g.max(), n_h.sum(2).max()]).tolist())
+        if kv_capacity is not None:
+            cap, cap_pairs = (int(x) for x in kv_capacity)
+            limit = cap
+        else:
+            # the one host read: virtual slots per head and capacity (in pairs) of the gather
+            cap, cap_pairs = (int(x) for x in torch.stack([n_g.max(), n_h.sum(2).max()]).tolist())
+            limit = 0
+            global last_kv_capacity
+            last_kv_capacity = (cap, cap_pairs)
         step = max(1, 128 // nbs)
         cap = -(-cap // step) * step                         # keeps the query offset a multiple of 128
     if cap == 0:
         o_attn = be.attn(qa, ka, va, tb, scale_attn, own, 0)
     else:
         # selected (block, head) pairs of every segment, packed back to back: [world, n_seg*B, cap_pairs*nbs, D]
-        k_all = _all_gather(be.pack_pairs(ka, tb, cap_pairs), world, group)
-        v_all = _all_gather(be.pack_pairs(va, tb, cap_pairs), world, group)
+        k_all = _all_gather(be.pack_pairs(ka, tb, cap_pairs, limit), world, group)
+        v_all = _all_gather(be.pack_pairs(va, tb, cap_pairs, limit), world, group)
 
         def flat(x):                    # -> [B, n_glob*cap_pairs*nbs, D], gathered order (a view when B = 1)
             x = x.reshape(n_glob, B, cap_pairs * nbs, x.shape[-1])
@@ -290,7 +309,8 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
     with on_side():
         if world > 1 or s_lin > 1:
             if world > 1:
-                a_glob, S_glob = to_global(_all_gather(a_seg, world, group)), to_global(_all_gather(S_seg, world, group))
+                lg = linear_group if linear_group is not None else group
+                a_glob, S_glob = to_global(_all_gather(a_seg, world, lg)), to_global(_all_gather(S_seg, world, lg))
                 h_seg = [be.state_combine(a_glob, S_glob, sid) for sid in seg]           # state each segment starts from
             else:
                 h_seg = [None] * n_seg

@@ -59,7 +59,7 @@ class OracleSegmentOps:
             f = f * a[n]
         return (torch.stack(pre) if want_prefix else None), p, f
 
-    def pack_pairs(self, x, tables, cap_pairs):
+    def pack_pairs(self, x, tables, cap_pairs, max_per_head=0):
         B, T, H, D = x.shape
         nbs = tables.nats_block_size
         HN = tables.types_i.shape[2]

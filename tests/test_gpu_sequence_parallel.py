@@ -43,6 +43,15 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, layout, splits, ret):
                                                 scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
                                                 linear_splits=splits)
         torch.cuda.synchronize()
+        # again with the gather capacity given (no host read) and the state exchange on its own communicator
+        from neuralattentionsearchlinear_b200 import sequence_parallel as sp
+        o_l2, o_a2, _ = nats_mixed_attn_mamba_sp(c(q[:, sl]), c(k[:, sl]), c(v[:, sl]), c(q[:, sl]), c(k[:, sl]), c(v[:, sl]),
+                                                 c(g[:, sl]), c(types[:, bsel]), nats_block_size=nbs,
+                                                 scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
+                                                 linear_splits=splits, kv_capacity=sp.last_kv_capacity,
+                                                 linear_group=dist.new_group())
+        torch.cuda.synchronize()
+        assert torch.equal(o_l, o_l2) and torch.equal(o_a, o_a2)
         # single-GPU op on the whole sequence, on this rank's GPU
         r_l, r_a, r_ht = nat.nats_mixed_attn_mamba(c(q), c(k), c(v), c(q), c(k), c(v), None, c(g), c(types), None,
                                                    scale_attn=K ** -0.5, nats_block_size=nbs,
@@ -156,3 +165,21 @@ def test_attn_split_packed_pairs_equals_head_major(DK, DV, nbs, HKV, HN):
     torch.cuda.synchronize()
     assert torch.equal(o_hm, o_pp)
     assert _lib.load().natsl_device_status() == 0
+
+
+def test_pack_pairs_capacity_overflow_sets_status():
+    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200.sequence_parallel import CudaSegmentOps
+    dev = torch.device("cuda", 0)
+    be = CudaSegmentOps()
+    x = torch.zeros(1, 1024, 2, 64, dtype=torch.bfloat16, device=dev)
+    types = torch.ones(1, 8, 2, 2, device=dev)                       # every block selected: 16 pairs, 8 per head
+    tb = be.tables(types, 1024, 128)
+    assert _lib.load().natsl_device_status() == 0
+    be.pack_pairs(x, tb, 16, 8)
+    assert _lib.load().natsl_device_status() == 0
+    be.pack_pairs(x, tb, 12, 0)                                      # too few pairs
+    assert _lib.load().natsl_device_status() == 3
+    be.pack_pairs(x, tb, 16, 4)                                      # more blocks per head than announced
+    assert _lib.load().natsl_device_status() == 3
+    assert _lib.load().natsl_device_status() == 0                    # reading clears it
