@@ -161,39 +161,8 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- l2norm of k rows (in place), rstd out; v rows scaled by beta (in place)
-    {
-        constexpr int CPR = K / 8;                 // lanes per row
-        constexpr int RPP = 32 / CPR > 0 ? 32 / CPR : 1;
-        static_assert(CPR <= 32, "K <= 256");
-        const int sub = lane / CPR, cc = lane % CPR;
-        for (int rr = 0; rr < 16; rr += RPP) {
-            int r = warp * 16 + rr + sub;
-            uint4* p = reinterpret_cast<uint4*>(ks_p + swz<K * 2>(r, cc));
-            uint4 xv = *p;
-            uint32_t* xw = reinterpret_cast<uint32_t*>(&xv);
-            float f[8];
-            float ss = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 t = unpack_bf16(xw[j]);
-                f[2 * j] = t.x; f[2 * j + 1] = t.y;
-                ss += t.x * t.x + t.y * t.y;
-            }
-#pragma unroll
-            for (int o = CPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            float rs = use_l2norm ? rsqrtf(ss + 1e-6f) : 1.0f;
-            if (use_l2norm) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) xw[j] = pack_bf16(f[2 * j] * rs, f[2 * j + 1] * rs);
-                *p = xv;
-            }
-            if (cc == 0) {
-                s_rstd[r] = rs;
-                if (r < valid) krstd_out[(tok0 + r) * H + h] = rs;
-            }
-        }
-    }
+    // ---- q row norms (read only); v rows scaled by beta (in place).  k stays raw in shared memory: its row norms
+    // are the diagonal of K K^T, and 1/norm enters A, P and the right-hand side of w as row / column scales.
     if (q) {
         constexpr int CPR = K / 8;
         constexpr int RPP = 32 / CPR > 0 ? 32 / CPR : 1;
@@ -217,10 +186,9 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
             }
         }
     }
-    scale_rows_inplace<V>(vs_p, s_beta, tid);
-    __syncthreads();
+    scale_rows_inplace<V>(vs_p, s_beta, tid);      // read again only by the substitution, many barriers from here
 
-    // ---- A = strictLower(beta_i (kn_i . kn_j) exp(gcs_i - gcs_j))
+    // ---- A = strictLower(beta_i (kn_i . kn_j) exp(gcs_i - gcs_j)); warp w owns the rows of block w
     {
         const int r0 = warp * 16;
         float acc[8][4];
@@ -240,8 +208,31 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
             }
         }
         const int gq = lane >> 2, qd = lane & 3;
+        // k row norms from the diagonal of the product: the thread with gq == 2 qd + e holds (row gq, gq) in
+        // acc[2 warp][e] and (row gq + 8, gq + 8) in acc[2 warp + 1][2 + e]
+        {
+            const int e = gq - 2 * qd;
+            if (e == 0 || e == 1) {
+                float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+                for (int p = 0; p < 4; ++p)
+                    if (p == warp) {
+                        d0 = e ? acc[2 * p][1] : acc[2 * p][0];
+                        d1 = e ? acc[2 * p + 1][3] : acc[2 * p + 1][2];
+                    }
+                const float rs0 = use_l2norm ? rsqrtf(d0 + 1e-6f) : 1.0f, rs1 = use_l2norm ? rsqrtf(d1 + 1e-6f) : 1.0f;
+                const int ra = r0 + gq, rb = ra + 8;
+                s_rstd[ra] = rs0;
+                s_rstd[rb] = rs1;
+                if (ra < valid) krstd_out[(tok0 + ra) * H + h] = rs0;
+                if (rb < valid) krstd_out[(tok0 + rb) * H + h] = rs1;
+            }
+        }
+        __syncthreads();              // every row's 1/norm is known
         if (q) {
-            // ---- P = tril(qn kn^T e^{gcs_i - gcs_j}), staged through the (still unused) G tile
+            // ---- P = tril(qn kn^T e^{gcs_i - gcs_j}) for the rows of block 3 - w (balances the triangular work),
+            // staged through the (still unused) G tile
+            const int wp = 3 - warp, rp = wp * 16;
             float accp[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -250,8 +241,8 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
 #pragma unroll 2
             for (int kk = 0; kk < K / 16; ++kk) {
                 uint32_t a[4];
-                load_a<K * 2>(qs, r0, kk * 16, lane, a);
-                for (int p = 0; p <= warp; ++p) {
+                load_a<K * 2>(qs, rp, kk * 16, lane, a);
+                for (int p = 0; p <= wp; ++p) {
                     uint32_t bb[4];
                     load_b_nk<K * 2>(ks, p * 16, kk * 16, lane, bb);
                     mma_bf16(accp[2 * p], a, bb[0], bb[1]);
@@ -262,17 +253,18 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
             for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int i = r0 + gq + hh * 8;
+                    const int i = rp + gq + hh * 8;
                     const int j = nt * 8 + qd * 2;
                     float v0 = 0.f, v1 = 0.f;
-                    if (j <= i && j < valid) v0 = accp[nt][hh * 2] * s_qr[i] * __expf(s_gcs[i] - s_gcs[j]);
-                    if (j + 1 <= i && j + 1 < valid) v1 = accp[nt][hh * 2 + 1] * s_qr[i] * __expf(s_gcs[i] - s_gcs[j + 1]);
+                    if (j <= i && j < valid) v0 = accp[nt][hh * 2] * s_qr[i] * s_rstd[j] * __expf(s_gcs[i] - s_gcs[j]);
+                    if (j + 1 <= i && j + 1 < valid)
+                        v1 = accp[nt][hh * 2 + 1] * s_qr[i] * s_rstd[j + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
                     *reinterpret_cast<uint32_t*>(gs_p + swz<128>(i, nt) + qd * 4) = pack_bf16(v0, v1);
                 }
             }
             __syncwarp();
             for (int it = lane; it < 16 * 8; it += 32) {
-                const int r = r0 + (it >> 3), cch = it & 7;
+                const int r = rp + (it >> 3), cch = it & 7;
                 if (r < valid)
                     *reinterpret_cast<uint4*>(p_out + ((tok0 + r) * H + h) * 64 + cch * 8) =
                         *reinterpret_cast<const uint4*>(gs_p + swz<128>(r, cch));
@@ -286,9 +278,10 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = r0 + gq + hh * 8;
                     const int j = nt * 8 + qd * 2;
+                    const float bi = s_beta[i] * s_rstd[i];
                     float v0 = 0.f, v1 = 0.f;
-                    if (i > j) v0 = s_beta[i] * acc[nt][hh * 2] * __expf(s_gcs[i] - s_gcs[j]);
-                    if (i > j + 1) v1 = s_beta[i] * acc[nt][hh * 2 + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
+                    if (i > j) v0 = bi * s_rstd[j] * acc[nt][hh * 2] * __expf(s_gcs[i] - s_gcs[j]);
+                    if (i > j + 1) v1 = bi * s_rstd[j + 1] * acc[nt][hh * 2 + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
                     *reinterpret_cast<float2*>(&As[i * A_LD + j]) = make_float2(v0, v1);
                 }
             }
@@ -296,7 +289,7 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     }
     __syncthreads();
     // k rows -> kn beta e^{gcs} (the KK^T operand is no longer needed)
-    if (tid < 64) s_wsc[tid] = s_beta[tid] * __expf(s_gcs[tid]);
+    if (tid < 64) s_wsc[tid] = s_beta[tid] * s_rstd[tid] * __expf(s_gcs[tid]);
 
     // ---- X_dd = (I + A_dd)^-1 for the four 16x16 diagonal blocks: forward substitution, one warp each
     if (lane < 16) {
@@ -304,10 +297,19 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
         float xcol[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            float sv = (i == cidx) ? 1.f : 0.f;
+            // row i of the block (the same for every lane: broadcast reads), four independent partial sums
+            float arow[16];
 #pragma unroll
-            for (int j = 0; j < i; ++j) sv -= As[(d0 + i) * A_LD + d0 + j] * xcol[j];
-            xcol[i] = sv;
+            for (int j4 = 0; j4 < 16; j4 += 4)
+                if (j4 < i)
+                    *reinterpret_cast<float4*>(&arow[j4]) = *reinterpret_cast<const float4*>(&As[(d0 + i) * A_LD + d0 + j4]);
+            float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+            for (int j = 0; j < i; ++j) {
+                const float t = arow[j] * xcol[j];
+                if ((j & 3) == 0) p0 += t; else if ((j & 3) == 1) p1 += t; else if ((j & 3) == 2) p2 += t; else p3 += t;
+            }
+            xcol[i] = ((i == cidx) ? 1.f : 0.f) - ((p0 + p1) + (p2 + p3));
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) Xs[(warp * 16 + i) * X_LD + cidx] = xcol[i];
