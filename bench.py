@@ -133,11 +133,11 @@ def time_cpu_baseline(inp, budget_s: float, reps: int = 1):
     times = []
     for _ in range(reps):
         t0 = time.perf_counter()
-        cpu_oracle_step(inp, 1, hs)
+        outs = cpu_oracle_step(inp, 1, hs)
         times.append(time.perf_counter() - t0)
     dt = statistics.median(times)
     tokens = CFG["T"] * hs / H                            # token-equivalents of the full-head layer
-    return tokens / dt, f"1 of 8 sequences x {hs} of {H} heads, T=4096 (linear in heads and batch)", dt
+    return tokens / dt, f"1 of 8 sequences x {hs} of {H} heads, T=4096 (linear in heads and batch)", dt, outs, hs
 
 
 def run_reference(args, rank: int):
@@ -333,10 +333,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     n_tok = B * T * H
     frac_lin = float(host["types"][..., 1].float().mean())
     state_bytes = B * NT * H * K * V * 2
-    # ncu dram__bytes_read+write per launch, captured at B=4 (profiles/ncu_full_current_kernels_B4.md), scaled by B/4:
+    # ncu dram__bytes_read+write per launch, captured at B=4 (profiles/ncu_full_hot_kernels_B4.md), scaled by B/4:
     # traffic grows in proportion to the batch (independent (batch, head) units)
-    ncu_traffic_b4 = {"attn_fwd": 248.5e6, "gdn_prep": 223.8e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
-                      "walk_fused": None}
+    ncu_traffic_b4 = {"attn_fwd": 249.1e6, "gdn_prep": 329.7e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
+                      "walk_fused": 359.6e6}
     # the step runs tables, attn_fwd, gdn_prep, walk_fused; scan_fwd_h + out_fwd_o are the two-kernel path the fused
     # walk replaces at this shape (still used for other head dims / block sizes) and are timed for comparison
     in_step = ("attn_fwd", "gdn_prep", "walk_fused")
@@ -361,7 +361,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     dom = max(in_step, key=lambda n: kernel_ms[n])
     roofline = dict(roofs[dom], peak_source=peak_src, dominant_stage=dom)
     # ---- CPU baseline (oracle port) on a bounded sample
-    cpu_val, cpu_sample, _ = time_cpu_baseline({n: t for n, t in host.items()}, budget_s=15.0)
+    cpu_val, cpu_sample, _, (ref_l, ref_a), hs = time_cpu_baseline({n: t for n, t in host.items()}, budget_s=15.0)
+    # output error of the timed device path against the oracle on the sample the oracle just computed
+    err_l = float((out[0][:1, :, :hs].float().cpu() - ref_l).abs().max())
+    err_a = float((out[1][:1, :, :hs].float().cpu() - ref_a).abs().max())
+    mag = float(max(ref_l.abs().max(), ref_a.abs().max()))
     line = {
         "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -374,6 +378,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "kernel_ms": kernel_ms, "roofline": roofline, "roofline_all": roofs,
         "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": cpu_sample},
+        "parity": {"max_abs_err_o_gdn": err_l, "max_abs_err_o_attn": err_a, "max_abs_ref": mag, "tolerance": "rtol=atol=1e-2",
+                   "sample": f"sequence 0, heads 0..{hs - 1}, device outputs of the timed step vs the fp32 CPU oracle"},
     }
     print(json.dumps(line))
     if dist is not None:
@@ -454,11 +460,23 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
         for _ in range(3):
             step()
         barrier()
+    if args.sp_plan and world > 1:
+        # plan / replay: the compute stages replay from CUDA graphs, the five all-gathers stay eager between them
+        plan = sp.GraphedMambaSP(q, k, v, q, k, v, g, types, kv_capacity=sp.last_kv_capacity, nats_block_size=nbs,
+                                 scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
+                                 linear_splits=args.sp_linear_splits or None, linear_group=lin_group)
+        plan.capture()
+        run_step, mode = plan.run, "plan: compute replayed from three CUDA graphs, eager NCCL all-gathers between them"
+        for _ in range(3):
+            run_step()
+        barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_host0 = time.perf_counter()
     e0.record(stream)
     for _ in range(args.steps):
         run_step()
     e1.record(stream)
+    host_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps      # host time to issue one step
     barrier()
     ms = e0.elapsed_time(e1)
     if dist is not None:
@@ -474,6 +492,7 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
                           "data": "synthetic (seeded, generated per rank)",
                           "config": {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 "
                                      "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({layout} segments)", "launch": mode},
+                          "host_issue_ms_per_step": host_ms,
                           "device_status": status}))
     if dist is not None:
         dist.destroy_process_group()
@@ -492,6 +511,8 @@ def main():
                     help="segment layout of the sequence-parallel workload (mamba_long)")
     ap.add_argument("--sp-linear-splits", type=int, default=0,
                     help="sub-segments per segment in the linear branch of mamba_long (0: about 1024 tokens each)")
+    ap.add_argument("--sp-plan", action="store_true",
+                    help="mamba_long on several GPUs through the plan / replay form (CUDA graphs for the compute stages)")
     ap.add_argument("--sp-fixed-capacity", action="store_true",
                     help="mamba_long: size the key/value gather from a capacity fixed before the timed region instead of "
                          "reading the block counts back every step")

@@ -20,7 +20,7 @@
 
 namespace natsl {
 
-constexpr int PREP_THREADS = 128;
+constexpr int PREP_THREADS = 256;          // warps 0-3 and 4-7 work on different things in most phases
 constexpr int A_LD = 68;            // fp32 row pitch of A: 16-byte aligned rows for float4 reads
 constexpr int X_LD = 17;            // pitch of the 16x16 diagonal-block inverses
 
@@ -55,17 +55,17 @@ __device__ __forceinline__ void scale_rows_inplace(unsigned char* tile, const fl
     }
 }
 
-// Block forward substitution on 64 columns [col0, col0+64) of a [64][COLS] tile, in place, by one warp;
-// then the warp stores its 64x64 slice to global memory (row stride gstride elements).
-template <int COLS>
+// Block forward substitution on W columns [col0, col0+W) of a [64][COLS] tile, in place, by one warp;
+// then the warp stores its 64 x W slice to global memory (row stride gstride elements).
+template <int COLS, int W>
 __device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsigned char* zptr, int col0,
                                             __nv_bfloat16* gout, long gstride, int valid, int lane) {
     const int g = lane >> 2, q = lane & 3;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float acc[8][4];
+        float acc[W / 8][4];
 #pragma unroll
-        for (int a = 0; a < 8; ++a)
+        for (int a = 0; a < W / 8; ++a)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[a][e] = 0.f;
 #pragma unroll
@@ -73,7 +73,7 @@ __device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsi
             uint32_t af[4];
             load_a<128>(gtile, 16 * i, 16 * kk, lane, af);
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
+            for (int p = 0; p < W / 16; ++p) {
                 uint32_t bf[4];
                 load_b_kn<COLS * 2>(ztile, 16 * kk, col0 + 16 * p, lane, bf);
                 mma_bf16(acc[2 * p], af, bf[0], bf[1]);
@@ -82,15 +82,16 @@ __device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsi
         }
         __syncwarp();          // all lanes have read the rows of block i before they are overwritten
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < W / 8; ++nt) {
             const int ch = (col0 >> 3) + nt;
             *reinterpret_cast<uint32_t*>(zptr + swz<COLS * 2>(16 * i + g, ch) + q * 4) = pack_bf16(acc[nt][0], acc[nt][1]);
             *reinterpret_cast<uint32_t*>(zptr + swz<COLS * 2>(16 * i + g + 8, ch) + q * 4) = pack_bf16(acc[nt][2], acc[nt][3]);
         }
         __syncwarp();
     }
-    for (int it = lane; it < 64 * 8; it += 32) {
-        const int r = it >> 3, c = it & 7;
+    constexpr int CPW = W / 8;                     // 16-byte chunks per row of the slice
+    for (int it = lane; it < 64 * CPW; it += 32) {
+        const int r = it / CPW, c = it % CPW;
         if (r < valid) {
             const uint4 x = *reinterpret_cast<const uint4*>(zptr + swz<COLS * 2>(r, (col0 >> 3) + c));
             *reinterpret_cast<uint4*>(gout + (long)r * gstride + col0 + c * 8) = x;
@@ -99,7 +100,7 @@ __device__ __forceinline__ void solve_group(uint32_t gtile, uint32_t ztile, unsi
 }
 
 template <int K, int V>
-__global__ void __launch_bounds__(PREP_THREADS)
+__global__ void __launch_bounds__(PREP_THREADS, 3)
 gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                 const __nv_bfloat16* __restrict__ v, const float* __restrict__ g, const void* __restrict__ beta,
                 int beta_dtype, __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ u,
@@ -167,8 +168,8 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
         constexpr int CPR = K / 8;
         constexpr int RPP = 32 / CPR > 0 ? 32 / CPR : 1;
         const int sub = lane / CPR, cc = lane % CPR;
-        for (int rr = 0; rr < 16; rr += RPP) {
-            int r = warp * 16 + rr + sub;
+        for (int rr = 0; rr < 8; rr += RPP) {
+            int r = warp * 8 + rr + sub;
             uint4 xv = *reinterpret_cast<const uint4*>(qs_p + swz<K * 2>(r, cc));
             const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xv);
             float ss = 0.f;
@@ -188,92 +189,81 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     }
     scale_rows_inplace<V>(vs_p, s_beta, tid);      // read again only by the substitution, many barriers from here
 
-    // ---- A = strictLower(beta_i (kn_i . kn_j) exp(gcs_i - gcs_j)); warp w owns the rows of block w
-    {
-        const int r0 = warp * 16;
-        float acc[8][4];
+    // ---- products: warps 0-3 form K K^T (warp w: row block w), warps 4-7 Q K^T (warp 4+i: row block 3-i), side by side
+    const int gq = lane >> 2, qd = lane & 3;
+    const bool kk_warp = warp < 4;
+    const int rblk = kk_warp ? warp : 7 - warp;          // 16-row block of this warp's product
+    const int r0 = rblk * 16;
+    float acc[8][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    if (kk_warp || q) {
+        const uint32_t atile = kk_warp ? ks : qs;
 #pragma unroll 2
         for (int kk = 0; kk < K / 16; ++kk) {
             uint32_t a[4];
-            load_a<K * 2>(ks, r0, kk * 16, lane, a);
-            for (int p = 0; p <= warp; ++p) {
+            load_a<K * 2>(atile, r0, kk * 16, lane, a);
+            for (int p = 0; p <= rblk; ++p) {
                 uint32_t bb[4];
                 load_b_nk<K * 2>(ks, p * 16, kk * 16, lane, bb);
                 mma_bf16(acc[2 * p], a, bb[0], bb[1]);
                 mma_bf16(acc[2 * p + 1], a, bb[2], bb[3]);
             }
         }
-        const int gq = lane >> 2, qd = lane & 3;
+    }
+    if (kk_warp) {
         // k row norms from the diagonal of the product: the thread with gq == 2 qd + e holds (row gq, gq) in
-        // acc[2 warp][e] and (row gq + 8, gq + 8) in acc[2 warp + 1][2 + e]
-        {
-            const int e = gq - 2 * qd;
-            if (e == 0 || e == 1) {
-                float d0 = 0.f, d1 = 0.f;
+        // acc[2 w][e] and (row gq + 8, gq + 8) in acc[2 w + 1][2 + e]
+        const int e = gq - 2 * qd;
+        if (e == 0 || e == 1) {
+            float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-                for (int p = 0; p < 4; ++p)
-                    if (p == warp) {
-                        d0 = e ? acc[2 * p][1] : acc[2 * p][0];
-                        d1 = e ? acc[2 * p + 1][3] : acc[2 * p + 1][2];
-                    }
-                const float rs0 = use_l2norm ? rsqrtf(d0 + 1e-6f) : 1.0f, rs1 = use_l2norm ? rsqrtf(d1 + 1e-6f) : 1.0f;
-                const int ra = r0 + gq, rb = ra + 8;
-                s_rstd[ra] = rs0;
-                s_rstd[rb] = rs1;
-                if (ra < valid) krstd_out[(tok0 + ra) * H + h] = rs0;
-                if (rb < valid) krstd_out[(tok0 + rb) * H + h] = rs1;
-            }
-        }
-        __syncthreads();              // every row's 1/norm is known
-        if (q) {
-            // ---- P = tril(qn kn^T e^{gcs_i - gcs_j}) for the rows of block 3 - w (balances the triangular work),
-            // staged through the (still unused) G tile
-            const int wp = 3 - warp, rp = wp * 16;
-            float accp[8][4];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) accp[i][j] = 0.f;
-#pragma unroll 2
-            for (int kk = 0; kk < K / 16; ++kk) {
-                uint32_t a[4];
-                load_a<K * 2>(qs, rp, kk * 16, lane, a);
-                for (int p = 0; p <= wp; ++p) {
-                    uint32_t bb[4];
-                    load_b_nk<K * 2>(ks, p * 16, kk * 16, lane, bb);
-                    mma_bf16(accp[2 * p], a, bb[0], bb[1]);
-                    mma_bf16(accp[2 * p + 1], a, bb[2], bb[3]);
+            for (int p = 0; p < 4; ++p)
+                if (p == rblk) {
+                    d0 = e ? acc[2 * p][1] : acc[2 * p][0];
+                    d1 = e ? acc[2 * p + 1][3] : acc[2 * p + 1][2];
                 }
-            }
+            const float rs0 = use_l2norm ? rsqrtf(d0 + 1e-6f) : 1.0f, rs1 = use_l2norm ? rsqrtf(d1 + 1e-6f) : 1.0f;
+            const int ra = r0 + gq, rb = ra + 8;
+            s_rstd[ra] = rs0;
+            s_rstd[rb] = rs1;
+            if (ra < valid) krstd_out[(tok0 + ra) * H + h] = rs0;
+            if (rb < valid) krstd_out[(tok0 + rb) * H + h] = rs1;
+        }
+    }
+    __syncthreads();              // every row's 1/norm is known; all products are done, so the q tile may be overwritten
+    if (!kk_warp) {
+        if (q) {
+            // ---- P = tril(qn kn^T e^{gcs_i - gcs_j}), staged through the (still unused) G tile
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int i = rp + gq + hh * 8;
+                    const int i = r0 + gq + hh * 8;
                     const int j = nt * 8 + qd * 2;
                     float v0 = 0.f, v1 = 0.f;
-                    if (j <= i && j < valid) v0 = accp[nt][hh * 2] * s_qr[i] * s_rstd[j] * __expf(s_gcs[i] - s_gcs[j]);
+                    if (j <= i && j < valid) v0 = acc[nt][hh * 2] * s_qr[i] * s_rstd[j] * __expf(s_gcs[i] - s_gcs[j]);
                     if (j + 1 <= i && j + 1 < valid)
-                        v1 = accp[nt][hh * 2 + 1] * s_qr[i] * s_rstd[j + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
+                        v1 = acc[nt][hh * 2 + 1] * s_qr[i] * s_rstd[j + 1] * __expf(s_gcs[i] - s_gcs[j + 1]);
                     *reinterpret_cast<uint32_t*>(gs_p + swz<128>(i, nt) + qd * 4) = pack_bf16(v0, v1);
                 }
             }
             __syncwarp();
             for (int it = lane; it < 16 * 8; it += 32) {
-                const int r = rp + (it >> 3), cch = it & 7;
+                const int r = r0 + (it >> 3), cch = it & 7;
                 if (r < valid)
                     *reinterpret_cast<uint4*>(p_out + ((tok0 + r) * H + h) * 64 + cch * 8) =
                         *reinterpret_cast<const uint4*>(gs_p + swz<128>(r, cch));
             }
-            __syncthreads();          // every warp is done with the q tile before A overwrites it
         }
+        // right-hand side scale of w: kn beta e^{gcs}
+        if (tid - 128 < 64) s_wsc[tid - 128] = s_beta[tid - 128] * s_rstd[tid - 128] * __expf(s_gcs[tid - 128]);
+    } else {
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            if (nt <= 2 * warp + 1) {
+            if (nt <= 2 * rblk + 1) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = r0 + gq + hh * 8;
@@ -287,35 +277,50 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
             }
         }
     }
-    __syncthreads();
-    // k rows -> kn beta e^{gcs} (the KK^T operand is no longer needed)
-    if (tid < 64) s_wsc[tid] = s_beta[tid] * s_rstd[tid] * __expf(s_gcs[tid]);
+    __syncthreads();              // A complete; the P staging is done, so the G tile is free; the w scale is known
 
-    // ---- X_dd = (I + A_dd)^-1 for the four 16x16 diagonal blocks: forward substitution, one warp each
-    if (lane < 16) {
-        const int d0 = warp * 16, cidx = lane;
-        float xcol[16];
+    if (kk_warp) {
+        // ---- X_dd = (I + A_dd)^-1 for the four 16x16 diagonal blocks: forward substitution, one warp each
+        if (lane < 16) {
+            const int d0 = warp * 16, cidx = lane;
+            float xcol[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            // row i of the block (the same for every lane: broadcast reads), four independent partial sums
-            float arow[16];
+            for (int i = 0; i < 16; ++i) {
+                // row i of the block (the same for every lane: broadcast reads), four independent partial sums
+                float arow[16];
 #pragma unroll
-            for (int j4 = 0; j4 < 16; j4 += 4)
-                if (j4 < i)
-                    *reinterpret_cast<float4*>(&arow[j4]) = *reinterpret_cast<const float4*>(&As[(d0 + i) * A_LD + d0 + j4]);
-            float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+                for (int j4 = 0; j4 < 16; j4 += 4)
+                    if (j4 < i)
+                        *reinterpret_cast<float4*>(&arow[j4]) = *reinterpret_cast<const float4*>(&As[(d0 + i) * A_LD + d0 + j4]);
+                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-            for (int j = 0; j < i; ++j) {
-                const float t = arow[j] * xcol[j];
-                if ((j & 3) == 0) p0 += t; else if ((j & 3) == 1) p1 += t; else if ((j & 3) == 2) p2 += t; else p3 += t;
+                for (int j = 0; j < i; ++j) {
+                    const float t = arow[j] * xcol[j];
+                    if ((j & 3) == 0) p0 += t; else if ((j & 3) == 1) p1 += t; else if ((j & 3) == 2) p2 += t; else p3 += t;
+                }
+                xcol[i] = ((i == cidx) ? 1.f : 0.f) - ((p0 + p1) + (p2 + p3));
             }
-            xcol[i] = ((i == cidx) ? 1.f : 0.f) - ((p0 + p1) + (p2 + p3));
-        }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) Xs[(warp * 16 + i) * X_LD + cidx] = xcol[i];
+            for (int i = 0; i < 16; ++i) Xs[(warp * 16 + i) * X_LD + cidx] = xcol[i];
+        }
+    } else {
+        // ---- meanwhile: k rows -> kn beta e^{gcs} (the K K^T operand is no longer needed)
+        constexpr int CPR = K / 8;
+        for (int i = tid - 128; i < 64 * CPR; i += 128) {
+            const int r = i / CPR, cch = i % CPR;
+            uint4* ptr = reinterpret_cast<uint4*>(ks_p + swz<K * 2>(r, cch));
+            uint4 x4 = *ptr;
+            const float sc = s_wsc[r];
+            uint32_t* xw = reinterpret_cast<uint32_t*>(&x4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16(xw[j]);
+                xw[j] = pack_bf16(f.x * sc, f.y * sc);
+            }
+            *ptr = x4;
+        }
     }
     __syncthreads();
-    scale_rows_inplace<K>(ks_p, s_wsc, tid);
 
     // ---- G (bf16, A-operand layout): diagonal blocks X_dd, below-diagonal blocks -X_ii A_ij
     for (int e = tid; e < 4 * 16 * 4; e += PREP_THREADS) {          // diagonal: (block, row, 4 columns)
@@ -343,13 +348,13 @@ gdn_prep_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     }
     __syncthreads();
 
-    // ---- [u | w] = block forward substitution, 64 columns per warp
-    constexpr int NCG = (K + V) / 64;
-    for (int cg = warp; cg < NCG; cg += 4) {
-        if (cg < V / 64)
-            solve_group<V>(gs, vs, vs_p, cg * 64, u + (tok0 * H + h) * V, (long)H * V, valid, lane);
+    // ---- [u | w] = block forward substitution, 32 columns per warp
+    constexpr int NCG = (K + V) / 32;
+    for (int cg = warp; cg < NCG; cg += 8) {
+        if (cg < V / 32)
+            solve_group<V, 32>(gs, vs, vs_p, cg * 32, u + (tok0 * H + h) * V, (long)H * V, valid, lane);
         else
-            solve_group<K>(gs, ks, ks_p, (cg - V / 64) * 64, w + (tok0 * H + h) * K, (long)H * K, valid, lane);
+            solve_group<K, 32>(gs, ks, ks_p, (cg - V / 32) * 32, w + (tok0 * H + h) * K, (long)H * K, valid, lane);
     }
 }
 

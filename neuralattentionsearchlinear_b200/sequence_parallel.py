@@ -336,3 +336,181 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
         for t_ in (q_lattn, k_lattn, v_lattn, g, nats_block_types):
             t_.record_stream(side)
     return o_lin, _merge(o_attn, B, n_seg), final
+
+
+class GraphedMambaSP:
+    """Plan / replay form of ``nats_mixed_attn_mamba_sp`` for a fixed shape (several ranks, CUDA kernels).
+
+    At this scale a rank's share is a few hundred microseconds of GPU work, less than the host needs to issue the
+    ~100 small launches of the eager function.  The plan binds to the caller's tensors (update their contents in
+    place between runs), sizes the key/value gather from ``kv_capacity`` (see ``nats_mixed_attn_mamba_sp``) and
+    captures the compute in three CUDA graphs; the five NCCL all-gathers stay eager, between the graphs:
+
+        graph A  tables, block counts, packed selected (block, head) pairs
+        gather   counts, packed keys, packed values          (asynchronous, default group)
+        graph B  linear branch from zero states, per-segment (a, S)       -- overlaps the gather
+        gather   (a, S)                                       (``linear_group``)
+        graph C  main stream: virtual tables + attention;  side stream: state fold + recurrence and output
+
+    ``run()`` returns the same triple as the eager function; the tensors are reused by the next run.
+    """
+
+    def __init__(self, q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, g, nats_block_types, *, kv_capacity,
+                 nats_block_size: int = 256, scale_attn=None, scale_lattn=1.0, ops_for_incomplete_chunks: str = 'all',
+                 decay_for_non_mamba_blocks: bool = True, layout: str = 'zigzag', linear_splits=None, group=None,
+                 linear_group=None):
+        if ops_for_incomplete_chunks not in ('all', 'mamba'):
+            raise NotImplementedError("only own-block linear attention ('all', 'mamba') is built")
+        if not dist.is_initialized() or dist.get_world_size(group) < 2:
+            raise ValueError("the plan form is for several ranks; use nats_mixed_attn_mamba_sp on one")
+        be = CudaSegmentOps()
+        self.group, self.lin_group = group, (linear_group if linear_group is not None else group)
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.world = world
+        nbs = nats_block_size
+        B, T_loc, H, K = q_lattn.shape
+        dev = q_lattn.device
+        self.dev = dev
+        if scale_attn is None:
+            scale_attn = k_attn.shape[-1] ** -0.5
+        own = ops_for_incomplete_chunks == 'all'
+        decay = decay_for_non_mamba_blocks
+        seg = segment_ids(rank, world, layout)
+        n_seg = len(seg)
+        n_glob = world * n_seg
+        if T_loc % (n_seg * max(nbs, 128)):
+            raise ValueError("every segment must be a multiple of the block size (and of 128)")
+        L = T_loc // n_seg
+        s_lin = int(linear_splits) if linear_splits else pick_linear_splits(L, nbs)
+        n_sub = n_seg * s_lin
+        gathered_ids, order = _layout_constants(world, layout, str(dev))
+        cap, cap_pairs = (int(x) for x in kv_capacity)
+        limit = cap
+        step = max(1, 128 // nbs)
+        cap = max(step, -(-cap // step) * step)
+        cap_pairs = max(1, cap_pairs)
+        HKV = k_attn.shape[2]
+        last_holder = (n_glob - 1) in seg
+        st = {}                          # tensors handed from one stage to the next (static once captured)
+
+        def to_global(x_all):
+            y = x_all.reshape(world * n_seg, B, *x_all.shape[2:])
+            return y if layout == 'contiguous' else y[order].contiguous()
+
+        def stage_a():
+            st['types_s'] = _split(nats_block_types, B, n_seg)
+            st['qa'], st['ka'], st['va'] = (_split(x, B, n_seg) for x in (q_attn, k_attn, v_attn))
+            st['tb'] = be.tables(st['types_s'], L, nbs)
+            st['n_loc'] = be.n_attn_blocks(st['tb'])
+            st['pk'] = be.pack_pairs(st['ka'], st['tb'], cap_pairs, limit)
+            st['pv'] = be.pack_pairs(st['va'], st['tb'], cap_pairs, limit)
+
+        def stage_b():
+            types_l = _split(nats_block_types, B, n_sub)
+            st['lin_in'] = tuple(_split(x, B, n_sub) for x in (q_lattn, k_lattn, v_lattn, g))
+            ql, kl, vl, gl = st['lin_in']
+            st['tbl'] = be.tables(types_l, L // s_lin, nbs)
+            _, S_loc, gcs = be.linear(ql, kl, vl, gl, st['tbl'], scale_lattn, None, decay, True)
+            a, trail = be.segment_decay(gcs, st['tbl'], decay)
+            S_end = S_loc * trail[..., None, None]
+            st['a_sub'] = a.view(n_seg, s_lin, B, H)
+            st['S_sub'] = S_end.view(n_seg, s_lin, B, H, K, -1)
+            if s_lin > 1:
+                tot = [be.prefix_states(st['a_sub'][j], st['S_sub'][j], None, False) for j in range(n_seg)]
+                st['S_seg'] = torch.stack([t[1] for t in tot]).reshape(n_seg * B, H, K, -1).contiguous()
+                st['a_seg'] = torch.stack([t[2] for t in tot]).reshape(n_seg * B, H).contiguous()
+            else:
+                st['S_seg'], st['a_seg'] = S_end.contiguous(), a.contiguous()
+
+        def stage_c():
+            cur = torch.cuda.current_stream(dev)
+            side = be.side_stream(dev)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                a_glob, S_glob = to_global(st['a_all']), to_global(st['S_all'])
+                h_seg = [be.state_combine(a_glob, S_glob, sid) for sid in seg]
+                if s_lin > 1:
+                    h_in = torch.cat([be.prefix_states(st['a_sub'][j], st['S_sub'][j], h_seg[j], True)[0]
+                                      for j in range(n_seg)], 0).reshape(n_sub * B, H, K, -1)
+                else:
+                    h_in = torch.cat(h_seg, 0)
+                ql, kl, vl, gl = st['lin_in']
+                o_lin, ht, _ = be.linear(ql, kl, vl, gl, st['tbl'], scale_lattn, h_in, decay, False)
+                final = None
+                if last_holder:
+                    j = seg.index(n_glob - 1)
+                    e = (j * s_lin + s_lin - 1) * B
+                    final = ht[e:e + B]
+                o_lin = _merge(o_lin, B, n_sub)
+            n_g = st['n_all'].reshape(n_glob, B, -1).to(torch.int64)
+            n_h = n_g.repeat_interleave(HKV // n_g.shape[2], dim=2)
+
+            def flat(x):
+                x = x.reshape(n_glob, B, cap_pairs * nbs, x.shape[-1])
+                return x.permute(1, 0, 2, 3).reshape(B, n_glob * cap_pairs * nbs, x.shape[-1]).contiguous()
+
+            seg_base = torch.arange(n_glob, device=dev).view(n_glob, 1, 1) * cap_pairs
+            rem_base = (n_h.cumsum(2) - n_h + seg_base).permute(1, 0, 2).to(torch.int32).contiguous()
+            types_virt = virtual_attn_types(n_g, gathered_ids, seg, cap, st['types_s'])
+            tb_v = be.tables(types_virt, n_glob * cap * nbs + L, nbs)
+            o_attn = be.attn_split(st['qa'], flat(st['k_all']), flat(st['v_all']), st['ka'], st['va'], tb_v, scale_attn,
+                                   own, rem_base, cap)
+            o_attn = _merge(o_attn, B, n_seg)
+            cur.wait_stream(side)
+            st['out'] = (o_lin, o_attn, final)
+
+        self._stages = (stage_a, stage_b, stage_c)
+        self._st = st
+        self._graphs = None
+        # one eager pass: creates the communicators' buffers, the library's per-device state and the gather outputs
+        stage_a()
+        st['n_all'] = torch.empty((world,) + tuple(st['n_loc'].shape), dtype=st['n_loc'].dtype, device=dev)
+        st['k_all'] = torch.empty((world,) + tuple(st['pk'].shape), dtype=st['pk'].dtype, device=dev)
+        st['v_all'] = torch.empty((world,) + tuple(st['pv'].shape), dtype=st['pv'].dtype, device=dev)
+        self._gather_kv()
+        stage_b()
+        st['a_all'] = torch.empty((world,) + tuple(st['a_seg'].shape), dtype=torch.float32, device=dev)
+        st['S_all'] = torch.empty((world,) + tuple(st['S_seg'].shape), dtype=torch.float32, device=dev)
+        self._gather_state()
+        stage_c()
+        torch.cuda.synchronize(dev)
+
+    def _gather(self, out, inp, group):
+        return dist.all_gather_into_tensor(out.view((-1,) + tuple(out.shape[2:])), inp, group=group, async_op=True)
+
+    def _gather_kv(self):
+        st = self._st
+        hs = [self._gather(st['n_all'], st['n_loc'], self.group), self._gather(st['k_all'], st['pk'], self.group),
+              self._gather(st['v_all'], st['pv'], self.group)]
+        self._pending = hs
+
+    def _gather_state(self):
+        st = self._st
+        hs = [self._gather(st['a_all'], st['a_seg'], self.lin_group), self._gather(st['S_all'], st['S_seg'], self.lin_group)]
+        for h in self._pending + hs:
+            h.wait()
+        self._pending = []
+
+    def capture(self):
+        """Captures the three compute stages into CUDA graphs (call once, after construction, on every rank)."""
+        graphs = []
+        for stage in self._stages:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                stage()
+            graphs.append(gr)
+        torch.cuda.synchronize(self.dev)
+        self._graphs = graphs
+
+    def run(self):
+        if self._graphs is None:
+            a, b, c = self._stages
+            a(); self._gather_kv(); b(); self._gather_state(); c()
+        else:
+            ga, gb, gc = self._graphs
+            ga.replay()
+            self._gather_kv()
+            gb.replay()
+            self._gather_state()
+            gc.replay()
+        return self._st['out']
