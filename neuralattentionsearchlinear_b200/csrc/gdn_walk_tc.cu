@@ -23,7 +23,7 @@ namespace natsl {
 constexpr int WK_THREADS = 320;
 constexpr int WK_EPI = 256;
 constexpr uint32_t WK_TMEM_COLS = 512;
-constexpr uint32_t WK_S = 0, WK_D1 = 128, WK_D2 = 256;     // TMEM column offsets
+constexpr uint32_t WK_S = 0, WK_D1 = 128, WK_D2 = 256, WK_D1B = 384;     // TMEM column offsets (D1 double-buffered)
 constexpr int WK_MAX_NT = 1024;
 
 struct WkSmem {
@@ -64,10 +64,10 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float* m_gl = m_dec + WK_MAX_NT;
     int* m_sel = reinterpret_cast<int*>(m_gl + WK_MAX_NT);
     const uint32_t bar0 = sbase + L::bars;
-    // barriers: full[2] / empty[2] tile stages; pfull / pfree the P tile; d1 (MMA 1 done); pv (v', v'' written);
-    // d2 (MMA 2 done); s3 (MMA 3 done); sready (state copy published, D1/D2 free)
+    // barriers: full[2] / empty[2] tile stages; pfull / pfree the P tile; d1 (MMA 1 done); pv (v', v'' written by the
+    // w lanes); d2 (MMA 2 done); s3 (MMA 3 done); sready (state copy published); odone (output rows read from TMEM)
     const uint32_t bar_full = bar0, bar_empty = bar0 + 16, bar_pfull = bar0 + 32, bar_pfree = bar0 + 40, bar_d1 = bar0 + 48,
-                   bar_pv = bar0 + 56, bar_d2 = bar0 + 64, bar_s3 = bar0 + 72, bar_sready = bar0 + 80;
+                   bar_pv = bar0 + 56, bar_d2 = bar0 + 64, bar_s3 = bar0 + 72, bar_sready = bar0 + 80, bar_odone = bar0 + 88;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 128);
 
     if (tid == 0) {
@@ -78,10 +78,11 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         mbar_init(bar_pfull, 1);
         mbar_init(bar_pfree, 1);
         mbar_init(bar_d1, 1);
-        mbar_init(bar_pv, WK_EPI);
+        mbar_init(bar_pv, WK_EPI / 2);
         mbar_init(bar_d2, 1);
         mbar_init(bar_s3, 1);
         mbar_init(bar_sready, WK_EPI);
+        mbar_init(bar_odone, WK_EPI / 2);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), WK_TMEM_COLS);
@@ -161,19 +162,36 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             ok = __all_sync(0xffffffffu, mbar_wait(bar_full + stg * 8, (c >> 1) & 1, status));
             if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_sready, c & 1, status));
             if (!ok) break;
+            const uint32_t d1 = tmem + ((c & 1) ? WK_D1B : WK_D1);
             if (lane == 0) {
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint64_t ad = umma_desc(base + L::wq + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
                     const uint64_t bs = umma_desc(sbase + L::sbf + kk * 2048, 16384, 1024);
-                    umma_ss(tmem + WK_D1, ad, bs, id_1, kk > 0);
+                    umma_ss(d1, ad, bs, id_1, kk > 0);
                 }
                 umma_commit(bar_d1);
             }
             __syncwarp();
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, c & 1, status));
+            if (!ok) break;
+            if (lane == 0) {
+                // the state update first: the next chunk's products wait for it, the output does not
+                tc_fence_after();
+                if (m_sel[c]) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t ak = umma_desc(base + L::k + kk * 2048, 8192, 1024);
+                        const uint64_t bv = umma_desc(sbase + L::vs + kk * 2048, 8192, 1024);
+                        umma_ss(tmem + WK_S, ak, bv, id_3, 1u);
+                    }
+                }
+                umma_commit(bar_s3);
+            }
+            __syncwarp();
             ok = __all_sync(0xffffffffu, mbar_wait(bar_pfull, c & 1, status));
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_pv, c & 1, status));
+            if (ok && c > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_odone, (c - 1) & 1, status));   // D2 is free
             if (!ok) break;
             if (lane == 0) {
                 tc_fence_after();
@@ -185,15 +203,6 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 umma_commit(bar_d2);
                 umma_commit(bar_pfree);
-                if (m_sel[c]) {
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t ak = umma_desc(base + L::k + kk * 2048, 8192, 1024);
-                        const uint64_t bv = umma_desc(sbase + L::vs + kk * 2048, 8192, 1024);
-                        umma_ss(tmem + WK_S, ak, bv, id_3, 1u);
-                    }
-                }
-                umma_commit(bar_s3);
                 umma_commit(bar_empty + stg * 8);
             }
             __syncwarp();
@@ -285,18 +294,19 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const float carry = m_carry[c];
             const float gl = m_gl[c];
             const bool sel = m_sel[c] != 0;
+            const uint32_t t_d1 = t_lane + ((c & 1) ? WK_D1B : WK_D1);
             // After a failed (bounded) wait the remaining work is skipped; the loop still runs to its end.
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d1, c & 1, status));
-            if (ok) {
-                tc_fence_after();
-                if (!is_q) {
-                    // ---- v' = u - e^{carry} w S ; v'' = v' rstd_k e^{g_last - g}   (the u tile arrived with the stage)
+            if (!is_q) {
+                // ---- w lanes: v' = u - e^{carry} w S ; v'' = v' rstd_k e^{g_last - g}   (the u tile arrived with the stage)
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d1, c & 1, status));
+                if (ok) {
+                    tc_fence_after();
                     const float ec = __expf(carry);
                     const float f2 = r_cur * __expf(fminf(gl - g_cur, 80.f));
 #pragma unroll 1
                     for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                         uint32_t r[32];
-                        tmem_ld32(t_lane + WK_D1 + c0, r);
+                        tmem_ld32(t_d1 + c0, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int cc = 0; cc < 4; ++cc) {
@@ -318,21 +328,36 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         }
                     }
                     fence_async_smem();
+                    tc_fence_before();
+                    mbar_arrive(bar_pv);
                 }
-                tc_fence_before();
-                mbar_arrive(bar_pv);
-                // ---- o = scale (rstd_q e^{g+carry} q S + P v')   (q rows), after MMA 2
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_d2, c & 1, status));
+            }
+            // ---- every lane: publish the updated state for the next chunk (and pre-apply the next update's decay).
+            // This is the serial chain of the walk; the output rows below are read after it.
+            if (ok && sel) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_s3, c & 1, status));
+                if (ok) {
+                    tc_fence_after();
+                    publish_state(next_dec(c + 1), nullptr);
+                    fence_async_smem();
+                }
             }
             if (ok) {
-                tc_fence_after();
-                if (is_q) {
+                tc_fence_before();
+                mbar_arrive(bar_sready);
+            }
+            if (is_q) {
+                // ---- q lanes: o = scale (rstd_q e^{g+carry} q S + P v'), off the chain (D1 is double-buffered, D2 is
+                // released by the arrival below)
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d2, c & 1, status));
+                if (ok) {
+                    tc_fence_after();
                     const float fq = r_cur * __expf(g_cur + carry);
                     __nv_bfloat16* orow = o + ((tok0 + tr) * H + h) * V;
 #pragma unroll 1
                     for (int c0 = cb; c0 < cb + 64; c0 += 32) {
                         uint32_t r1[32], r2[32];
-                        tmem_ld32(t_lane + WK_D1 + c0, r1);
+                        tmem_ld32(t_d1 + c0, r1);
                         tmem_ld32(t_lane + WK_D2 + c0, r2);
                         tmem_ld_wait();
                         if (tr < valid) {
@@ -349,19 +374,8 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             }
                         }
                     }
-                }
-                // ---- publish the updated state for the next chunk (and pre-apply the next update's decay)
-                if (sel) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_s3, c & 1, status));
-                    if (ok) {
-                        tc_fence_after();
-                        publish_state(next_dec(c + 1), nullptr);
-                        fence_async_smem();
-                    }
-                }
-                if (ok) {
                     tc_fence_before();
-                    mbar_arrive(bar_sready);
+                    mbar_arrive(bar_odone);
                 }
             }
             g_cur = g_nxt;

@@ -344,13 +344,14 @@ class GraphedMambaSP:
     At this scale a rank's share is a few hundred microseconds of GPU work, less than the host needs to issue the
     ~100 small launches of the eager function.  The plan binds to the caller's tensors (update their contents in
     place between runs), sizes the key/value gather from ``kv_capacity`` (see ``nats_mixed_attn_mamba_sp``) and
-    captures the compute in three CUDA graphs; the five NCCL all-gathers stay eager, between the graphs:
+    captures the compute in four CUDA graphs; the five NCCL all-gathers stay eager, between the graphs:
 
         graph A  tables, block counts, packed selected (block, head) pairs
-        gather   counts, packed keys, packed values          (asynchronous, default group)
-        graph B  linear branch from zero states, per-segment (a, S)       -- overlaps the gather
-        gather   (a, S)                                       (``linear_group``)
-        graph C  main stream: virtual tables + attention;  side stream: state fold + recurrence and output
+        gather   counts, packed keys, packed values          (asynchronous, default group; runs under B, C)
+        graph B  linear branch from zero states, per-segment (a, S)
+        gather   (a, S)                                       (``linear_group``, its own communicator)
+        graph C  state fold, recurrence and output from the true starting states
+        graph D  virtual tables + attention                   (after the key/value gather has arrived)
 
     ``run()`` returns the same triple as the eager function; the tensors are reused by the next run.
     """
@@ -422,26 +423,24 @@ class GraphedMambaSP:
             else:
                 st['S_seg'], st['a_seg'] = S_end.contiguous(), a.contiguous()
 
-        def stage_c():
-            cur = torch.cuda.current_stream(dev)
-            side = be.side_stream(dev)
-            side.wait_stream(cur)
-            with torch.cuda.stream(side):
-                a_glob, S_glob = to_global(st['a_all']), to_global(st['S_all'])
-                h_seg = [be.state_combine(a_glob, S_glob, sid) for sid in seg]
-                if s_lin > 1:
-                    h_in = torch.cat([be.prefix_states(st['a_sub'][j], st['S_sub'][j], h_seg[j], True)[0]
-                                      for j in range(n_seg)], 0).reshape(n_sub * B, H, K, -1)
-                else:
-                    h_in = torch.cat(h_seg, 0)
-                ql, kl, vl, gl = st['lin_in']
-                o_lin, ht, _ = be.linear(ql, kl, vl, gl, st['tbl'], scale_lattn, h_in, decay, False)
-                final = None
-                if last_holder:
-                    j = seg.index(n_glob - 1)
-                    e = (j * s_lin + s_lin - 1) * B
-                    final = ht[e:e + B]
-                o_lin = _merge(o_lin, B, n_sub)
+        def stage_c():                   # linear branch from the true starting states; needs the (a, S) gather only
+            a_glob, S_glob = to_global(st['a_all']), to_global(st['S_all'])
+            h_seg = [be.state_combine(a_glob, S_glob, sid) for sid in seg]
+            if s_lin > 1:
+                h_in = torch.cat([be.prefix_states(st['a_sub'][j], st['S_sub'][j], h_seg[j], True)[0]
+                                  for j in range(n_seg)], 0).reshape(n_sub * B, H, K, -1)
+            else:
+                h_in = torch.cat(h_seg, 0)
+            ql, kl, vl, gl = st['lin_in']
+            o_lin, ht, _ = be.linear(ql, kl, vl, gl, st['tbl'], scale_lattn, h_in, decay, False)
+            final = None
+            if last_holder:
+                j = seg.index(n_glob - 1)
+                e = (j * s_lin + s_lin - 1) * B
+                final = ht[e:e + B]
+            st['o_lin'], st['final'] = _merge(o_lin, B, n_sub), final
+
+        def stage_d():                   # softmax branch; needs the key/value gather
             n_g = st['n_all'].reshape(n_glob, B, -1).to(torch.int64)
             n_h = n_g.repeat_interleave(HKV // n_g.shape[2], dim=2)
 
@@ -455,44 +454,41 @@ class GraphedMambaSP:
             tb_v = be.tables(types_virt, n_glob * cap * nbs + L, nbs)
             o_attn = be.attn_split(st['qa'], flat(st['k_all']), flat(st['v_all']), st['ka'], st['va'], tb_v, scale_attn,
                                    own, rem_base, cap)
-            o_attn = _merge(o_attn, B, n_seg)
-            cur.wait_stream(side)
-            st['out'] = (o_lin, o_attn, final)
+            st['out'] = (st['o_lin'], _merge(o_attn, B, n_seg), st['final'])
 
-        self._stages = (stage_a, stage_b, stage_c)
+        self._stages = (stage_a, stage_b, stage_c, stage_d)
         self._st = st
         self._graphs = None
         # one eager pass: creates the communicators' buffers, the library's per-device state and the gather outputs
-        stage_a()
-        st['n_all'] = torch.empty((world,) + tuple(st['n_loc'].shape), dtype=st['n_loc'].dtype, device=dev)
-        st['k_all'] = torch.empty((world,) + tuple(st['pk'].shape), dtype=st['pk'].dtype, device=dev)
-        st['v_all'] = torch.empty((world,) + tuple(st['pv'].shape), dtype=st['pv'].dtype, device=dev)
-        self._gather_kv()
-        stage_b()
-        st['a_all'] = torch.empty((world,) + tuple(st['a_seg'].shape), dtype=torch.float32, device=dev)
-        st['S_all'] = torch.empty((world,) + tuple(st['S_seg'].shape), dtype=torch.float32, device=dev)
-        self._gather_state()
-        stage_c()
+        self._issue(stage_a, stage_b, stage_c, stage_d, first=True)
         torch.cuda.synchronize(dev)
 
     def _gather(self, out, inp, group):
         return dist.all_gather_into_tensor(out.view((-1,) + tuple(out.shape[2:])), inp, group=group, async_op=True)
 
-    def _gather_kv(self):
+    def _issue(self, a, b, c, d, first=False):
+        """One step: the key/value gather (default group) runs under the whole linear branch, whose own small
+        gather goes through ``linear_group``; the attention starts when the keys have arrived."""
         st = self._st
-        hs = [self._gather(st['n_all'], st['n_loc'], self.group), self._gather(st['k_all'], st['pk'], self.group),
+        a()
+        if first:
+            for dst, src in (('n_all', 'n_loc'), ('k_all', 'pk'), ('v_all', 'pv')):
+                st[dst] = torch.empty((self.world,) + tuple(st[src].shape), dtype=st[src].dtype, device=self.dev)
+        kv = [self._gather(st['n_all'], st['n_loc'], self.group), self._gather(st['k_all'], st['pk'], self.group),
               self._gather(st['v_all'], st['pv'], self.group)]
-        self._pending = hs
-
-    def _gather_state(self):
-        st = self._st
-        hs = [self._gather(st['a_all'], st['a_seg'], self.lin_group), self._gather(st['S_all'], st['S_seg'], self.lin_group)]
-        for h in self._pending + hs:
+        b()
+        if first:
+            st['a_all'] = torch.empty((self.world,) + tuple(st['a_seg'].shape), dtype=torch.float32, device=self.dev)
+            st['S_all'] = torch.empty((self.world,) + tuple(st['S_seg'].shape), dtype=torch.float32, device=self.dev)
+        for h in [self._gather(st['a_all'], st['a_seg'], self.lin_group), self._gather(st['S_all'], st['S_seg'], self.lin_group)]:
             h.wait()
-        self._pending = []
+        c()
+        for h in kv:
+            h.wait()
+        d()
 
     def capture(self):
-        """Captures the three compute stages into CUDA graphs (call once, after construction, on every rank)."""
+        """Captures the compute stages into CUDA graphs (call once, after construction, on every rank)."""
         graphs = []
         for stage in self._stages:
             gr = torch.cuda.CUDAGraph()
@@ -504,13 +500,7 @@ class GraphedMambaSP:
 
     def run(self):
         if self._graphs is None:
-            a, b, c = self._stages
-            a(); self._gather_kv(); b(); self._gather_state(); c()
+            self._issue(*self._stages)
         else:
-            ga, gb, gc = self._graphs
-            ga.replay()
-            self._gather_kv()
-            gb.replay()
-            self._gather_state()
-            gc.replay()
+            self._issue(*(g.replay for g in self._graphs))
         return self._st['out']
