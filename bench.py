@@ -11,6 +11,9 @@ With N GPUs every rank runs its own batch (independent (batch, head) units, no c
 data path: weak scaling); the timed region is bracketed by a barrier and a device synchronise and
 the time is the maximum over ranks.  Prints ONE JSON line on rank 0.
 
+``--workload mamba_long`` (optional) runs the long-context NAtSL-Mamba2 layer (B=1, T=65536, H=32, block 256),
+sequence-parallel over the ranks (strong scaling); ``--sp-plan`` uses the plan / replay form.
+
 ``--impl reference`` times the reference algorithm's CPU form (the PyTorch restatement under
 ``oracle/``; the reference's own code is Triton-only and cannot run on host cores) on a bounded
 sample of the same workload, on rank 0 only.
@@ -296,23 +299,52 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- end to end: host (pinned) inputs -> device -> op -> host outputs, every step
     h2d = sum(t.numel() * t.element_size() for t in pinned.values())
-    o_host = [torch.empty(B, T, H, V, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    ht_host = torch.empty(B, H, K, V, dtype=torch.float32).pin_memory()
-    d2h = sum(t.numel() * t.element_size() for t in o_host) + ht_host.numel() * 4
-    e2e_steps = max(3, min(args.steps, 10))
+    d2h = 2 * B * T * H * V * 2 + B * H * K * V * 4
+    e2e_steps = max(4, min(args.steps, 10))
 
-    def e2e_step():
-        x = {n: t.to(dev, non_blocking=True) for n, t in pinned.items()}
-        og, oa, hts = step(x)
-        o_host[0].copy_(og, non_blocking=True)
-        o_host[1].copy_(oa, non_blocking=True)
-        ht_host.copy_(hts, non_blocking=True)
+    # Every step copies its inputs from pinned host memory and its outputs back; the copies of neighbouring steps
+    # overlap the compute (PCIe is full duplex): an upload stream, the compute stream and a download stream, two
+    # sets of device input buffers and host output buffers.
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    x_dev = [{n: torch.empty_like(t, device=dev) for n, t in pinned.items()} for _ in range(2)]
+    o_host = [[torch.empty(B, T, H, V, dtype=torch.bfloat16).pin_memory() for _ in range(2)] for _ in range(2)]
+    ht_host = [torch.empty(B, H, K, V, dtype=torch.float32).pin_memory() for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    e2e_step()
+    def e2e_step(i):
+        b2 = i & 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_comp[b2])              # the step that last read this input set has finished
+            for n, t in pinned.items():
+                x_dev[b2][n].copy_(t, non_blocking=True)
+            ev_in[b2].record(s_in)
+        stream.wait_event(ev_in[b2])
+        og, oa, hts = step(x_dev[b2])
+        ev_comp[b2].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[b2])
+            o_host[b2][0].copy_(og, non_blocking=True)
+            o_host[b2][1].copy_(oa, non_blocking=True)
+            ht_host[b2].copy_(hts, non_blocking=True)
+            ev_out[b2].record(s_out)
+        for t_ in (og, oa, hts):
+            t_.record_stream(s_out)
+
+    def e2e_drain():
+        stream.wait_stream(s_out)
+        stream.wait_stream(s_in)
+
+    for i in range(2):
+        e2e_step(i)
+    e2e_drain()
     barrier()
     e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
+    for i in range(e2e_steps):
+        e2e_step(i + 2)
+    e2e_drain()
     e1.record(stream)
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
@@ -374,7 +406,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"},
         "clocks": clk, "gpu_launches": 5 * args.steps,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "pipelining": "uploads, compute and downloads of neighbouring steps overlap (three streams, two buffer sets)"},
         "kernel_ms": kernel_ms, "roofline": roofline, "roofline_all": roofs,
         "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": cpu_sample},
@@ -464,9 +497,13 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
         # plan / replay: the compute stages replay from CUDA graphs, the five all-gathers stay eager between them
         plan = sp.GraphedMambaSP(q, k, v, q, k, v, g, types, kv_capacity=sp.last_kv_capacity, nats_block_size=nbs,
                                  scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
-                                 linear_splits=args.sp_linear_splits or None, linear_group=lin_group)
+                                 linear_splits=args.sp_linear_splits or None, linear_group=lin_group,
+                                 gather_under_linear={"auto": None, "gather-under-linear": True,
+                                                      "branches-side-by-side": False}[args.sp_plan_order])
         plan.capture()
-        run_step, mode = plan.run, "plan: compute replayed from three CUDA graphs, eager NCCL all-gathers between them"
+        run_step = plan.run
+        mode = ("plan: compute replayed from four CUDA graphs, eager NCCL all-gathers between them, "
+                + ("key/value gather under the linear branch" if plan.gather_under_linear else "branches side by side"))
         for _ in range(3):
             run_step()
         barrier()
@@ -513,6 +550,7 @@ def main():
                     help="sub-segments per segment in the linear branch of mamba_long (0: about 1024 tokens each)")
     ap.add_argument("--sp-plan", action="store_true",
                     help="mamba_long on several GPUs through the plan / replay form (CUDA graphs for the compute stages)")
+    ap.add_argument("--sp-plan-order", default="auto", choices=["auto", "gather-under-linear", "branches-side-by-side"])
     ap.add_argument("--sp-fixed-capacity", action="store_true",
                     help="mamba_long: size the key/value gather from a capacity fixed before the timed region instead of "
                          "reading the block counts back every step")

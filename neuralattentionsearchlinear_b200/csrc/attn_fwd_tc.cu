@@ -2,12 +2,12 @@
 //
 // One CTA = 128 queries of one softmax head; two CTAs share an SM (2 x 256 TMEM columns,
 // 2 x ~113 KB shared memory).  Warp roles (320 threads):
-//   warp 0    TMA producer: Q once, then the K and V tiles of the key-tile walk into a 3-stage and a
+//   warp 0    TMA producer: Q once, then the K and V tiles of the key-tile walk into a 3- or 4-stage and a
 //             2-stage ring (cp.async.bulk.tensor, 128-byte swizzle, zero fill past the sequence end), in the
 //             order in which the tensor core frees the stages;
-//   warp 1    MMA issuer (one thread): S_j = Q K_j^T into one of two TMEM score buffers, issued two
-//             tiles ahead, and O += P_j V_j with P read straight from TMEM; completion is signalled
-//             with tcgen05.commit on mbarriers;
+//   warp 1    MMA issuer (one thread): S_j = Q K_j^T into one of two (DV = 128) or three (DV = 64) TMEM score
+//             buffers, issued that many tiles ahead, and O += P_j V_j with P read straight from TMEM;
+//             completion is signalled with tcgen05.commit on mbarriers;
 //   warps 2-9 softmax, 16 query rows per warp, four threads per row (tcgen05.ld.16x256b fragments):
 //             mask, online softmax in base 2 with a lazily updated maximum (O in TMEM is only
 //             rescaled when the running maximum grows by more than 2^8), P (bf16 pairs) written back
@@ -30,22 +30,28 @@ int attn_fwd_mma_sync(const void* q, const void* k, const void* v, const int32_t
                       int DV, int nbs, float scale, int own, cudaStream_t st);
 
 constexpr int TC_THREADS = 320;          // TMA producer, MMA issuer, 8 softmax warps
-constexpr uint32_t TC_TMEM_COLS = 256;      // S0: [0,64), S1: [64,128), O: [128, 128+DV); P_j aliases S_{j&1}
-constexpr uint32_t TC_O_COL = 128;
+constexpr uint32_t TC_TMEM_COLS = 256;      // score buffers of 64 columns, then O (DV columns); P_j aliases the buffer of S_j
+// Score buffers of 64 columns each, then the output accumulator: two buffers when DV = 128 (2*64 + 128 = 256 columns),
+// three when DV = 64 (3*64 + 64): the third one lets Q K^T run one more tile ahead of the softmax.
+template <int DV> struct TcTmem {
+    static constexpr int NSB = DV == 64 ? 3 : 2;
+    static constexpr uint32_t o_col = NSB * 64;
+    static constexpr int KST = NSB + 1;              // K ring stages
+};
 constexpr float LAZY_RESCALE_LOG2 = 8.0f;
 constexpr int TC_LIST_CAP = 128;            // key tiles whose descriptors are kept in shared memory
-constexpr int TC_KST = 3;                   // K ring stages
 constexpr int TC_VST = 2;                   // V ring stages
 
 template <int DK, int DV>
 struct TcSmem {
     static constexpr int q = 0;                                  // DK/64 sub-tiles [128][64]
-    static constexpr int k = q + 128 * DK * 2;                   // TC_KST stages x DK/64 sub-tiles [64][64]
-    static constexpr int v = k + TC_KST * 64 * DK * 2;           // TC_VST stages x DV/64 sub-tiles [64][64]
+    static constexpr int KST = TcTmem<DV>::KST;
+    static constexpr int k = q + 128 * DK * 2;                   // KST stages x DK/64 sub-tiles [64][64]
+    static constexpr int v = k + KST * 64 * DK * 2;              // TC_VST stages x DV/64 sub-tiles [64][64]
     static constexpr int list = v + TC_VST * 64 * DV * 2;        // int[TC_LIST_CAP]
     static constexpr int bars = list + TC_LIST_CAP * 4;
     static constexpr int total = bars + 256;
-    static_assert(128 * DV * 2 <= 128 * DK * 2 + TC_KST * 64 * DK * 2, "output staging must fit over Q + K");
+    static_assert(128 * DV * 2 <= 128 * DK * 2 + KST * 64 * DK * 2, "output staging must fit over Q + K");
     static_assert(total <= 115712, "two CTAs per SM");
 };
 
@@ -122,8 +128,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t bar0 = sbase + L::bars;
     // barrier slots (8 bytes each)
     const uint32_t bar_q = bar0, bar_k_full = bar0 + 8, bar_k_empty = bar0 + 40, bar_v_full = bar0 + 72,
-                   bar_v_empty = bar0 + 104, bar_s_full = bar0 + 136, bar_p_full = bar0 + 152, bar_pv = bar0 + 168;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 192);
+                   bar_v_empty = bar0 + 104, bar_s_full = bar0 + 136, bar_p_full = bar0 + 160, bar_pv = bar0 + 184;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 208);
+    constexpr int NSB = TcTmem<DV>::NSB, TC_KST = TcTmem<DV>::KST;
+    constexpr uint32_t TC_O_COL = TcTmem<DV>::o_col;
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
@@ -133,7 +141,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(bar_v_full + 8 * i, 1);
             mbar_init(bar_v_empty + 8 * i, 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NSB; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
             mbar_init(bar_p_full + 8 * i, 8);            // one arrival per softmax warp
         }
@@ -205,9 +213,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int sub = 0; sub < DK / 64; ++sub) tma_prefetch_4d(rem1 ? &map_kr : &map_k, sub * 64, h1, c1, b1);
             }
         };
-        // The loads follow the order in which the tensor core frees the ring stages: the K stages of the first two
+        // The loads follow the order in which the tensor core frees the ring stages: the K stages of the first NSB
         // tiles right after their Q K^T products, then alternately the V stage of tile i (after P_i V_i) and the
-        // K stage of tile i + 2 (Q K_{i+2}^T is issued right behind P_i V_i).  Every wait is for the next event
+        // K stage of tile i + NSB (Q K_{i+NSB}^T is issued right behind P_i V_i).  Every wait is for the next event
         // of that sequence, so the producer sleeps in the barrier instead of polling two rings.
         int jk = min(TC_KST, n_tiles), jv = min(TC_VST, n_tiles);
         if (lane == 0) {
@@ -220,7 +228,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (ok && lane == 0) load_k(jk);
             ++jk;
         };
-        for (int i = 0; ok && i < 2 && jk < n_tiles; ++i) next_k();
+        for (int i = 0; ok && i < NSB && jk < n_tiles; ++i) next_k();
         while (ok && (jk < n_tiles || jv < n_tiles)) {
             if (jv < n_tiles) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_v_empty + (jv % TC_VST) * 8, ((jv / TC_VST) - 1) & 1, status));
@@ -235,7 +243,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64, false);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, DV, true);
         auto issue_qk = [&](int j) {                  // S_{j&1} = Q K_j^T   (lane 0 only)
-            const int sb = j & 1, stg = j % TC_KST;
+            const int sb = j % NSB, stg = j % TC_KST;
             const uint32_t kt = s_k + stg * (64 * DK * 2);
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
@@ -247,7 +255,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             umma_commit(bar_k_empty + stg * 8);
         };
         bool ok = __all_sync(0xffffffffu, mbar_wait(bar_q, 0, status));
-        for (int j = 0; ok && j < min(2, n_tiles); ++j) {
+        for (int j = 0; ok && j < min(NSB, n_tiles); ++j) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + (j % TC_KST) * 8, (j / TC_KST) & 1, status));
             if (ok && lane == 0) {
                 tc_fence_after();
@@ -256,9 +264,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             __syncwarp();
         }
         for (int j = 0; ok && j < n_tiles; ++j) {
-            const int sb = j & 1, vstg = j % TC_VST;
+            const int sb = j % NSB, vstg = j % TC_VST;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_v_full + vstg * 8, (j / TC_VST) & 1, status));
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_p_full + sb * 8, (j >> 1) & 1, status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_p_full + sb * 8, (j / NSB) & 1, status));
             if (!ok) break;
             if (lane == 0) {
                 tc_fence_after();
@@ -269,11 +277,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     umma_ts(tmem + TC_O_COL, tmem + sb * 64 + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bar_v_empty + vstg * 8);
-                umma_commit(bar_pv + sb * 8);
+                umma_commit(bar_pv + (j & 1) * 8);
             }
             __syncwarp();
-            if (j + 2 < n_tiles) {
-                const int jn = j + 2;
+            if (j + NSB < n_tiles) {
+                const int jn = j + NSB;
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_k_full + (jn % TC_KST) * 8, (jn / TC_KST) & 1, status));
                 if (!ok) break;
                 if (lane == 0) {
@@ -297,9 +305,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            const int sb = j & 1;
+            const int sb = j % NSB;
             const uint32_t t_s = t_rows + sb * 64;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + sb * 8, (j >> 1) & 1, status));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + sb * 8, (j / NSB) & 1, status));
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[32];
@@ -352,10 +360,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const float alpha_b = (new_b == -INFINITY) ? 1.f : ex2(m_b - new_b);
                 if (j > 0) {
                     // O must be at rest: P_{j-1} V_{j-1} has to be complete.  Even and odd tiles signal on two
-                    // barriers.  S_j was produced behind P_{j-2} V_{j-2}, hence behind P_{j-3} V_{j-3} (the previous
-                    // phase of the barrier waited on), and P_{j+1} V_{j+1} cannot have started: the barrier is in
-                    // the phase waited for or the one after it, so a parity wait without having watched the earlier
-                    // phases is unambiguous.
+                    // barriers.  S_j was produced behind P_{j-NSB} V_{j-NSB}, hence behind P_{j-3} V_{j-3} (the
+                    // previous phase of the barrier waited on; NSB <= 3), and P_{j+1} V_{j+1} cannot have started:
+                    // the barrier is in the phase waited for or the one after it, so a parity wait without having
+                    // watched the earlier phases is unambiguous.
                     ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, status));
                     if (!ok) break;
                     tc_fence_after();
@@ -406,7 +414,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p_full + sb * 8);
         }
-        if (ok)          // the last product; the one two tiles earlier on the same barrier completed before S of the last tile
+        // The last two products, in order: S of the last tile was produced behind P V of tile n-1-NSB >= n-4, the
+        // previous phase of the barrier of tile n-2; once that one is complete so is tile n-3, the previous phase
+        // of the barrier of the last tile.
+        if (ok && n_tiles >= 2)
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + ((n_tiles - 2) & 1) * 8, ((n_tiles - 2) >> 1) & 1, status));
+        if (ok)
             ok = __all_sync(0xffffffffu, mbar_wait(bar_pv + ((n_tiles - 1) & 1) * 8, ((n_tiles - 1) >> 1) & 1, status));
         unsigned char* stage = smem + L::q;
         if (ok) {

@@ -296,9 +296,11 @@ gdn_walk_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const bool sel = m_sel[c] != 0;
             const uint32_t t_d1 = t_lane + ((c & 1) ? WK_D1B : WK_D1);
             // After a failed (bounded) wait the remaining work is skipped; the loop still runs to its end.
+            // Every lane first sees MMA 1 of this chunk complete: it was issued behind the previous phase of the
+            // "state published" barrier, so no thread can arrive on that barrier twice within one phase.
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d1, c & 1, status));
             if (!is_q) {
                 // ---- w lanes: v' = u - e^{carry} w S ; v'' = v' rstd_k e^{g_last - g}   (the u tile arrived with the stage)
-                if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_d1, c & 1, status));
                 if (ok) {
                     tc_fence_after();
                     const float ec = __expf(carry);

@@ -303,6 +303,10 @@ def test_gdn_fused_walk(nat, B, T, H, HN, decay, use_h0):
     o2, ht2, _ = _ops.linear_fwd(*args, return_intermediates=True)      # scan + out kernels
     assert_close(o, o2.float(), TOL, "fused vs two-kernel o")
     assert_close(ht, ht2, 2 * TOL, "fused vs two-kernel state")
+    # run-to-run bit-identity: the walk's warps run up to a chunk apart and meet only through mbarriers
+    for _ in range(4):
+        o3, ht3, _ = _ops.linear_fwd(*args)
+        assert torch.equal(o3, o) and torch.equal(ht3, ht)
 
 
 @pytest.mark.parametrize("nbs,decay,T", [(64, True, 512), (128, False, 400), (64, True, 100)])

@@ -54,17 +54,20 @@ def _worker(rank, world, port, B, T, H, K, V, nbs, layout, splits, ret):
         assert torch.equal(o_l, o_l2) and torch.equal(o_a, o_a2)
         # plan / replay form: compute captured in CUDA graphs, collectives eager between them
         xs = [c(q[:, sl]), c(k[:, sl]), c(v[:, sl])]
-        plan = sp.GraphedMambaSP(xs[0], xs[1], xs[2], xs[0], xs[1], xs[2], c(g[:, sl]), c(types[:, bsel]),
-                                 kv_capacity=sp.last_kv_capacity, nats_block_size=nbs, scale_attn=K ** -0.5,
-                                 layout=layout, linear_splits=splits, linear_group=dist.new_group())
-        p_l, p_a, _ = plan.run()
-        torch.cuda.synchronize()
-        assert torch.equal(o_l, p_l) and torch.equal(o_a, p_a)
-        plan.capture()
-        for _ in range(2):
+        lin_group = dist.new_group()
+        for under in (True, False):                        # both orders of a step
+            plan = sp.GraphedMambaSP(xs[0], xs[1], xs[2], xs[0], xs[1], xs[2], c(g[:, sl]), c(types[:, bsel]),
+                                     kv_capacity=sp.last_kv_capacity, nats_block_size=nbs, scale_attn=K ** -0.5,
+                                     layout=layout, linear_splits=splits, linear_group=lin_group,
+                                     gather_under_linear=under)
             p_l, p_a, _ = plan.run()
-        torch.cuda.synchronize()
-        assert torch.equal(o_l, p_l) and torch.equal(o_a, p_a)
+            torch.cuda.synchronize()
+            assert torch.equal(o_l, p_l) and torch.equal(o_a, p_a)
+            plan.capture()
+            for _ in range(2):
+                p_l, p_a, _ = plan.run()
+            torch.cuda.synchronize()
+            assert torch.equal(o_l, p_l) and torch.equal(o_a, p_a)
         # single-GPU op on the whole sequence, on this rank's GPU
         r_l, r_a, r_ht = nat.nats_mixed_attn_mamba(c(q), c(k), c(v), c(q), c(k), c(v), None, c(g), c(types), None,
                                                    scale_attn=K ** -0.5, nats_block_size=nbs,
