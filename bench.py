@@ -367,8 +367,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     state_bytes = B * NT * H * K * V * 2
     # ncu dram__bytes_read+write per launch, captured at B=4 (profiles/ncu_full_hot_kernels_B4.md), scaled by B/4:
     # traffic grows in proportion to the batch (independent (batch, head) units)
-    ncu_traffic_b4 = {"attn_fwd": 249.1e6, "gdn_prep": 329.7e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
-                      "walk_fused": 359.6e6}
+    ncu_traffic_b4 = {"attn_fwd": 249.1e6, "gdn_prep": 330.3e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
+                      "walk_fused": 357.7e6}
     # the step runs tables, attn_fwd, gdn_prep, walk_fused; scan_fwd_h + out_fwd_o are the two-kernel path the fused
     # walk replaces at this shape (still used for other head dims / block sizes) and are timed for comparison
     in_step = ("attn_fwd", "gdn_prep", "walk_fused")
