@@ -68,7 +68,7 @@ def config0_inputs(seed=0, B=2, T=512, H=4, K=64, V=64, dtype=torch.float32):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a checkout of automl/NeuralAttentionSearchLinear")
     ap.add_argument("--fla-naive", default=None, help="path to fla/ops/gated_delta_rule/naive.py")
     args = ap.parse_args()
 
