@@ -129,6 +129,26 @@ def test_attention_growing_scores(nat, DK, DV, nbs):
     assert _lib.load().natsl_device_status() == 0
 
 
+def test_attention_more_key_tiles_than_the_shared_list_holds(nat):
+    """A long, densely selected sequence: the late query tiles walk more key tiles (≈ 150) than the per-CTA tile list
+    in shared memory holds (128), so the descriptors past it are recomputed on the fly."""
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    B, T, HQ, HKV, DK, DV, nbs = 1, 10240, 1, 1, 128, 64, 64
+    gen = torch.Generator().manual_seed(77)
+    q = torch.randn(B, T, HQ, DK, generator=gen).bfloat16()
+    k = torch.randn(B, T, HKV, DK, generator=gen).bfloat16()
+    v = torch.randn(B, T, HKV, DV, generator=gen).bfloat16()
+    types = otab.synth_types(B, T // nbs, 1, 0.9, seed=78)
+    assert int(types[..., 0].sum()) > 135                  # the last query tile sees more than 128 key tiles
+    tb = nat.build_selection_tables(types.cuda(), T, nbs)
+    o, lse = _ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), tb, DK ** -0.5, True)
+    mask = oattn.attn_mask(types[..., 0], T, nbs, HQ)
+    o_ref, lse_ref = oattn.attn_sdpa(q.float(), k.float(), v.float(), mask, DK ** -0.5)
+    assert_close(o, o_ref, TOL, "o_attn")
+    assert_close(lse, lse_ref, TOL, "lse")
+    assert _lib.load().natsl_device_status() == 0
+
+
 GDN_CASES = [  # B, T, H, HN, K, V, nbs, decay, use_h0
     (2, 512, 4, 4, 64, 64, 64, True, False),
     (1, 700, 4, 2, 128, 128, 64, True, True),
