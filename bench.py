@@ -565,6 +565,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"                 # keeps NCCL's version banner off stdout: one JSON line only
     if args.impl == "reference":
         run_reference(args, rank)
     elif args.workload == "mamba_long":
