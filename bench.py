@@ -38,6 +38,24 @@ CFG = dict(B=8, T=4096, H=16, K=128, V=128, nbs=64, p_attn=0.25)
 WORKLOAD = "natsl_gdn_layer_fwd B={B} T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25"
 
 
+def init_process_group_quiet(dev):
+    """NCCL process group; whatever the libraries print while the communicator comes up (NCCL's version banner) goes
+    to stderr, so that stdout carries the one JSON line only."""
+    import torch.distributed as dist
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+    return dist
+
+
 # ------------------------------------------------------------------------------- inputs
 def make_inputs(seed: int, B: int, H: int):
     """Host tensors (fp32 generation on CPU, cast to bf16).  q, k L2-normalised per head."""
@@ -185,8 +203,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(dev)
     dist = None
     if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        dist = init_process_group_quiet(dev)
     B, T, H, K, V, nbs = (CFG[n] for n in ("B", "T", "H", "K", "V", "nbs"))
     host = make_inputs(1000 * rank, B, H)
     pinned = {n: t.pin_memory() for n, t in host.items()}
@@ -434,8 +451,7 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(dev)
     dist = None
     if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        dist = init_process_group_quiet(dev)
     c = MAMBA_LONG
     T, H, K, V, nbs = c["T"], c["H"], c["K"], c["V"], c["nbs"]
     from neuralattentionsearchlinear_b200.sequence_parallel import segment_ids
@@ -565,8 +581,6 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"                 # keeps NCCL's version banner off stdout: one JSON line only
     if args.impl == "reference":
         run_reference(args, rank)
     elif args.workload == "mamba_long":
