@@ -26,5 +26,8 @@ Parity pinning
   vector in the reference project: parity unpinned beyond the internal
   recurrent-vs-chunk cross-check and the mask formula of the reference's own
   debug script (``src/nats/ops/attns/attns.py:2041-2058``).
+* Gradients (``oracle.grad``): true gradients by autograd through the forward oracle, and closed forms of what
+  the reference's backward returns where it is not the true gradient; parity unpinned (no runnable reference),
+  the closed forms are checked against the autograd derivatives they stand for.
 """
-from . import tables, gdn, mamba, attn  # noqa: F401
+from . import tables, gdn, mamba, attn, grad  # noqa: F401
