@@ -78,10 +78,12 @@ def attn_dense_mask(tables: SelectionTables, HQ: int, own_chunk: bool) -> torch.
 
 def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool,
                use_l2norm: bool, output_final_state: bool, trailing_quirk: bool = True,
-               return_intermediates: bool = False, skip_out: bool = False, own_chunk: bool = True):
+               return_intermediates: bool = False, skip_out: bool = False, own_chunk: bool = True, tables_event=None):
     """Linear branch forward (prep -> state recurrence -> output).  Returns (o, ht, inter); with ``skip_out``
     only the recurrence runs (o is None).  ``own_chunk=False``: the output keeps only the state term (the mode
-    in which the softmax branch alone covers the current chunk); ``tables`` must then be per 64-token chunk."""
+    in which the softmax branch alone covers the current chunk); ``tables`` must then be per 64-token chunk.
+    ``tables_event``: CUDA event after which the tables (built on another stream) are valid; the chunk preparation
+    does not read them and is launched before the wait."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "linear branch needs bf16 q/k/v", TypeError)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
@@ -109,6 +111,8 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     else:
         w, u, krstd = None, v, None
         _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
+    if tables_event is not None:
+        torch.cuda.current_stream(dev).wait_event(tables_event)
     ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
     if h0 is not None:
         h0 = h0.float().contiguous()

@@ -73,31 +73,38 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
         if own_linear and not incomplete_block_start_with_ht:
             raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
         T = q_lattn.shape[1]
-        tables = build_selection_tables(nats_block_types, T, nats_block_size)
-        lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
         if q_lattn.dtype == torch.float32:
             if not own_linear:
                 raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
             # fp32 tensors take the reference-precision kernels (token recurrence with re-roll, fp32 softmax)
+            tables = build_selection_tables(nats_block_types, T, nats_block_size)
             o_attn, lse = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
             o_gdn, ht, _ = _ops.linear_recurrent(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
                                                  initial_state_gated_delta, decay_for_non_gdn_blocks,
                                                  lattn_use_qk_l2norm_in_kernel)
             ctx.mark_non_differentiable(o_gdn, o_attn)
             return o_gdn, o_attn, (ht if output_final_state_gated_delta else None)
-        # the two branches are independent: the softmax branch runs on a side stream (as the reference does for
-        # its Mamba2 / DeltaNet ops, src/nats/ops/mixed_ops/mixed_attn_mamba.py:114-124) and joins before returning
+        # The two branches are independent: the softmax branch runs on a side stream (as the reference does for
+        # its Mamba2 / DeltaNet ops, src/nats/ops/mixed_ops/mixed_attn_mamba.py:114-124) and joins before returning.
+        # The selection tables are built on the side stream too: the chunk preparation of the linear branch does not
+        # read them, so it starts at once and only the recurrence waits for the tables.
         cur = torch.cuda.current_stream(q_attn.device)
         side = _get_attn_stream(q_attn.device)
         side.wait_stream(cur)
         with torch.cuda.stream(side):
+            tables = build_selection_tables(nats_block_types, T, nats_block_size)
+            lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
+            tables_ready = torch.cuda.Event()
+            tables_ready.record(side)
             o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
         o_gdn, ht, _ = _ops.linear_fwd(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, lin_tables, scale_lattn,
                                        initial_state_gated_delta, decay_for_non_gdn_blocks,
                                        lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta,
-                                       own_chunk=own_linear)
+                                       own_chunk=own_linear, tables_event=tables_ready)
+        for t_ in (lin_tables.types_i, lin_tables.indices, lin_tables.n_blocks):
+            t_.record_stream(cur)                      # allocated on the side stream, read by the recurrence
         cur.wait_stream(side)
-        for t_ in (q_attn, k_attn, v_attn, o_attn, lse):
+        for t_ in (q_attn, k_attn, v_attn, nats_block_types, o_attn, lse):
             t_.record_stream(side)
         ctx.mark_non_differentiable(o_gdn, o_attn)
         return o_gdn, o_attn, ht
