@@ -15,14 +15,33 @@ def _need(cond: bool, msg: str, exc=ValueError):
         raise exc(msg)
 
 
+def _check_qkv(q, k, v, tables, what: str, same_heads: bool):
+    """Shapes that the kernels take on trust: the same batch, key and value sequences of one length, matching head
+    counts and head dims, tables built for this batch, everything on one CUDA device."""
+    _need(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, f"{what}: q, k, v must be [B, T, H, D]")
+    _need(q.is_cuda and k.device == q.device and v.device == q.device, f"{what}: q, k, v must be on one CUDA device")
+    _need(k.shape[0] == q.shape[0] and v.shape[0] == q.shape[0], f"{what}: q, k, v differ in batch size")
+    _need(k.shape[3] == q.shape[3], f"{what}: q and k differ in head dim ({q.shape[3]} vs {k.shape[3]})")
+    _need(v.shape[1] == k.shape[1] and v.shape[2] == k.shape[2],
+          f"{what}: k {tuple(k.shape)} and v {tuple(v.shape)} differ in length or heads")
+    if same_heads:
+        _need(k.shape[1] == q.shape[1] and k.shape[2] == q.shape[2], f"{what}: q {tuple(q.shape)} and k {tuple(k.shape)} differ")
+    else:
+        _need(q.shape[2] % k.shape[2] == 0, f"{what}: {q.shape[2]} query heads over {k.shape[2]} key/value heads")
+    _need(tables.types_i.shape[0] == q.shape[0] and tables.types_i.device == q.device,
+          f"{what}: the selection tables were built for another batch or device")
+
+
 def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mma_sync: bool = False, q_off: int = 0):
     """q [B,Tq,HQ,DK], k [B,T,HKV,DK], v [B,T,HKV,DV] bf16 -> (o [B,Tq,HQ,DV] bf16, lse [B,Tq,HQ] fp32 base-2).
     The queries are the tokens [q_off, q_off+Tq) of the T-key sequence (q_off = 0 and Tq = T normally)."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "softmax branch needs bf16 q/k/v", TypeError)
+    _check_qkv(q, k, v, tables, "softmax branch", same_heads=False)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, Tq, HQ, DK = q.shape
     T, HKV, DV = k.shape[1], k.shape[2], v.shape[3]
     _need(tables.T == T, f"tables were built for T={tables.T}, keys have T={T}")
+    _need(0 <= q_off and q_off + Tq <= T, f"queries [{q_off}, {q_off + Tq}) do not lie inside the {T} keys")
     HN = tables.types_i.shape[2]
     o = torch.empty(B, Tq, HQ, DV, dtype=BF16, device=q.device)
     lse = torch.empty(B, Tq, HQ, dtype=torch.float32, device=q.device)
@@ -85,11 +104,18 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     ``tables_event``: CUDA event after which the tables (built on another stream) are valid; the chunk preparation
     does not read them and is launched before the wait."""
     _need(q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16, "linear branch needs bf16 q/k/v", TypeError)
+    _check_qkv(q, k, v, tables, "linear branch", same_heads=True)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
     V = v.shape[3]
     dev = q.device
+    _need(tables.T == T, f"tables were built for T={tables.T}, the sequence has T={T}")
+    _need(tuple(g.shape) == (B, T, H) and g.device == dev, f"g must be [B,T,H] = {(B, T, H)} on {dev}, got {tuple(g.shape)}")
+    _need(beta is None or (tuple(beta.shape) == (B, T, H) and beta.device == dev),
+          f"beta must be [B,T,H] = {(B, T, H)} on {dev}")
+    _need(rule != _lib.RULE_GDN or beta is not None, "the gated delta rule needs beta")
     HN = tables.types_i.shape[2]
+    _need(H % HN == 0, f"{H} heads over {HN} selection heads")
     NT = cdiv(T, 64)
     nbs = tables.nats_block_size
     st = current_stream_ptr(dev)
@@ -156,10 +182,14 @@ def linear_recurrent(rule: int, q, k, v, g, beta, tables: SelectionTables, scale
     Returns (o, ht, hstart): output, state after the last selected block, block-start state at the end."""
     _need(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype", TypeError)
     code = _dt_code(q)
+    _check_qkv(q, k, v, tables, "linear branch (recurrent form)", same_heads=True)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, H, K = q.shape
     V = v.shape[3]
     dev = q.device
+    _need(tables.T == T, f"tables were built for T={tables.T}, the sequence has T={T}")
+    _need(tuple(g.shape) == (B, T, H), f"g must be [B,T,H] = {(B, T, H)}, got {tuple(g.shape)}")
+    _need(beta is None or tuple(beta.shape) == (B, T, H), f"beta must be [B,T,H] = {(B, T, H)}")
     g = g.float().contiguous()
     if beta is not None:
         beta = beta.to(q.dtype).contiguous()
@@ -179,6 +209,8 @@ def attn_fwd_fp32(q, k, v, tables: SelectionTables, scale: float, own_chunk: boo
     """Reference-precision softmax branch (fp32 math; fp32 or bf16 tensors).  Returns (o, lse base-2)."""
     _need(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype", TypeError)
     code = _dt_code(q)
+    _check_qkv(q, k, v, tables, "softmax branch (fp32 form)", same_heads=False)
+    _need(k.shape[1] == q.shape[1] and tables.T == q.shape[1], "q, k and the tables must cover the same sequence")
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, T, HQ, DK = q.shape
     HKV, DV = k.shape[2], v.shape[3]

@@ -39,3 +39,27 @@ def test_abi_version_and_error_string():
     assert st == -3 and b"null" in lib.natsl_last_error()
     st = lib.natsl_chunk_local_cumsum(None, None, 1, 1, 1, None)
     assert st == -3
+
+
+def test_op_wrappers_reject_inconsistent_shapes_before_any_launch():
+    """The kernels take shapes on trust; the Python wrappers check them first (no GPU needed to see the errors)."""
+    from types import SimpleNamespace
+    import pytest
+    import torch
+    from neuralattentionsearchlinear_b200 import _ops
+    tb = SimpleNamespace(types_i=torch.zeros(2, 4, 2, 2, dtype=torch.int32), T=256, nats_block_size=64)
+    q = torch.zeros(2, 256, 4, 64)
+    with pytest.raises(ValueError, match="CUDA device"):
+        _ops._check_qkv(q, q, q, tb, "test", same_heads=True)
+    fake = lambda *s: SimpleNamespace(shape=torch.Size(s), dim=lambda: len(s), is_cuda=True, device="cuda:0")
+    tbc = SimpleNamespace(types_i=SimpleNamespace(shape=torch.Size((2, 4, 2, 2)), device="cuda:0"))
+    _ops._check_qkv(fake(2, 256, 4, 64), fake(2, 256, 4, 64), fake(2, 256, 4, 32), tbc, "ok", same_heads=True)
+    _ops._check_qkv(fake(2, 128, 4, 64), fake(2, 256, 2, 64), fake(2, 256, 2, 32), tbc, "ok", same_heads=False)
+    for bad in [(fake(2, 256, 4, 64), fake(3, 256, 4, 64), fake(2, 256, 4, 64)),          # batch
+                (fake(2, 256, 4, 64), fake(2, 256, 4, 32), fake(2, 256, 4, 64)),          # head dim of q vs k
+                (fake(2, 256, 4, 64), fake(2, 256, 4, 64), fake(2, 128, 4, 64)),          # k vs v length
+                (fake(2, 256, 4, 64), fake(2, 200, 4, 64), fake(2, 200, 4, 64))]:         # q vs k length (linear)
+        with pytest.raises(ValueError):
+            _ops._check_qkv(*bad, tbc, "bad", same_heads=True)
+    with pytest.raises(ValueError, match="query heads"):
+        _ops._check_qkv(fake(2, 256, 5, 64), fake(2, 256, 2, 64), fake(2, 256, 2, 64), tbc, "bad", same_heads=False)
