@@ -185,3 +185,172 @@ def attn_grads(q, k, v, sel_attn, do, *, nbs=64, scale=None, own_chunk=True, ref
     per_block = per_block.view(B, HN, HQ // HN, TN).sum(2).permute(0, 2, 1)    # [B,TN,HN]
     dnats = torch.where(sel_attn.to(torch.bool), per_block, torch.zeros_like(per_block))
     return dict(dq=dq.permute(0, 2, 1, 3).contiguous(), dk=fold(dk), dv=fold(dv), dnats=dnats)
+
+
+def linear_chunk_backward(q, k, v, g, beta, sel, do, dht=None, *, scale=None, h0=None, decay=True, use_l2norm=True,
+                          rule="gdn"):
+    """The backward of the chunk form written out (block size 64), in the order a kernel pipeline would take
+    (the reference's order: src/nats/ops/gated_delta_rule/chunk.py:199-332): recompute the forward per chunk,
+    walk the chunks in reverse carrying dS (gradient with respect to the state after the chunk) and the gradient with
+    respect to the carried decay, and push every chunk's gradients through the WY transform, the decays and the l2
+    normalisation.  No autograd; ``tests/test_oracle_grad.py`` checks it against ``linear_true_grads``.
+    -> dict(dq, dk, dv, dg, dbeta, dh0) plus the per-chunk intermediates a kernel test wants:
+       dS [B,NT,H,K,V] (gradient w.r.t. the state after chunk c), dvp [B,T,H,V] (gradient w.r.t. v'),
+       dw [B,T,H,K], du [B,T,H,V]."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    dt = q.dtype
+    assert T % C == 0
+    if scale is None:
+        scale = K ** -0.5
+    NT = T // C
+    gdn = rule == "gdn"
+    if beta is None:
+        beta = torch.ones(B, T, H, dtype=dt)
+    q_rstd = torch.rsqrt((q * q).sum(-1) + 1e-6) if use_l2norm else torch.ones(B, T, H, dtype=dt)
+    k_rstd = torch.rsqrt((k * k).sum(-1) + 1e-6) if use_l2norm else torch.ones(B, T, H, dtype=dt)
+    qn, kn = q * q_rstd[..., None], k * k_rstd[..., None]
+    ch = lambda x, D: x.view(B, NT, C, H, D).permute(0, 3, 1, 2, 4)          # [B,H,NT,C,D]
+    chs = lambda x: x.view(B, NT, C, H).permute(0, 3, 1, 2)                   # [B,H,NT,C]
+    qc, kc, vc, doc = ch(qn, K), ch(kn, K), ch(v, V), ch(do, V)
+    gc = chs(g).cumsum(-1)
+    bc = chs(beta)
+    gam = (gc[..., :, None] - gc[..., None, :]).exp()
+    tril_s = torch.tril(torch.ones(C, C, dtype=torch.bool), -1)
+    tril_i = torch.tril(torch.ones(C, C, dtype=torch.bool), 0)
+    zero = torch.zeros((), dtype=dt)
+    kk = kc @ kc.transpose(-1, -2)
+    if gdn:
+        A = torch.where(tril_s, bc[..., :, None] * kk * gam, zero)
+        eye = torch.eye(C, dtype=dt)
+        Ai = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)
+        zu = vc * bc[..., None]                                               # right-hand sides of the WY solve
+        zw = kc * (bc * gc.exp())[..., None]
+        u, w = Ai @ zu, Ai @ zw
+    else:
+        u, w = vc, torch.zeros_like(kc)
+    qk = qc @ kc.transpose(-1, -2)
+    P = torch.where(tril_i, qk * gam, zero)
+    gL = gc[..., -1]
+    selh = ogdn._expand_sel(sel, H).permute(0, 2, 1)                           # [B,H,NT]
+    # ---- forward recurrence: the state and the carry every chunk reads
+    S = torch.zeros(B, H, K, V, dtype=dt) if h0 is None else h0.clone()
+    carry = torch.zeros(B, H, dtype=dt)
+    S_read, carry_read, vps = [], [], []
+    last_sel = -1
+    for c in range(NT):
+        act = selh[..., c]
+        S_read.append(S)
+        carry_read.append(carry)
+        vp = u[:, :, c] - carry.exp()[..., None, None] * (w[:, :, c] @ S)
+        vps.append(vp)
+        gl = gL[:, :, c]
+        kd = (gl[..., None] - gc[:, :, c]).exp() if gdn else torch.clamp(gl[..., None] - gc[:, :, c], max=0.0).exp()
+        S_new = (gl + carry).exp()[..., None, None] * S + kc[:, :, c].transpose(-1, -2) @ (vp * kd[..., None])
+        S = torch.where(act[..., None, None], S_new, S)
+        carry = torch.where(act, torch.zeros_like(carry), carry + gl if decay else carry)
+    # ---- reverse walk
+    # the final state the forward returns is the state after the last selected chunk of each (b, h)
+    idx = torch.arange(NT).view(1, 1, NT)
+    last = torch.where(selh, idx, torch.full_like(idx, -1)).amax(-1)          # [B,H], -1 if none
+    dS = torch.zeros(B, H, K, V, dtype=dt)
+    dcar = torch.zeros(B, H, dtype=dt)                                         # gradient w.r.t. the carry after the chunk
+    dh0_extra = torch.zeros(B, H, K, V, dtype=dt)
+    if dht is not None:
+        dh0_extra = torch.where((last < 0)[..., None, None], dht, dh0_extra)   # no selected chunk: final state = h0
+    dqn = torch.zeros_like(qc)
+    dkn = torch.zeros_like(kc)
+    dvc = torch.zeros_like(vc)
+    dgc = torch.zeros_like(gc)                                                 # w.r.t. the chunk-local cumsum
+    dbc = torch.zeros_like(bc)
+    dS_all = torch.zeros(B, NT, H, K, V, dtype=dt)
+    dvp_all, dw_all, du_all = torch.zeros_like(vc), torch.zeros_like(kc), torch.zeros_like(vc)
+    for c in range(NT - 1, -1, -1):
+        act = selh[..., c]
+        a3 = act[..., None, None]
+        if dht is not None:
+            dS = dS + torch.where((last == c)[..., None, None], dht, torch.zeros_like(dht))
+        dS_all[:, c] = dS
+        S_c, car = S_read[c], carry_read[c]
+        vp, gl, g_c = vps[c], gL[:, :, c], gc[:, :, c]
+        ec = car.exp()
+        kraw = gl[..., None] - g_c
+        kd = kraw.exp() if gdn else torch.clamp(kraw, max=0.0).exp()
+        k_c, q_c, do_c = kc[:, :, c], qc[:, :, c], doc[:, :, c]
+        # state update (selected chunks): S+ = e^{gl+car} S + k^T (vp * kd)
+        kdS = k_c @ dS                                                         # [C,V]
+        dvp = torch.where(a3, kdS * kd[..., None], torch.zeros_like(vp))
+        dk_c = torch.where(a3, (vp * kd[..., None]) @ dS.transpose(-1, -2), torch.zeros_like(k_c))
+        dkd = torch.where(act[..., None], (kdS * vp).sum(-1) * kd, torch.zeros_like(kd))   # w.r.t. log kd
+        if not gdn:
+            dkd = torch.where(kraw < 0, dkd, torch.zeros_like(dkd))            # clamp(min(.,0)) passes no gradient above 0
+        dec = (gl + car).exp()
+        ddec = (dS * S_c).sum((-1, -2)) * dec                                  # w.r.t. (gl + car), selected only
+        dgl = torch.where(act, ddec + dkd.sum(-1), torch.zeros_like(gl))
+        dg_tok = -dkd                                                          # w.r.t. the local cumsum of each token
+        dcar_in = torch.where(act, ddec, dcar)                                 # a selected chunk resets the carry
+        if decay:
+            dgl = dgl + torch.where(act, torch.zeros_like(dcar), dcar)
+        dS_prev = torch.where(a3, dec[..., None, None] * dS, dS)
+        # output: o = s [ (e^{g+car} q) S + P vp ]
+        E = (g_c + car[..., None]).exp()
+        dvp = dvp + scale * (P[:, :, c].transpose(-1, -2) @ do_c)
+        dP = torch.where(tril_i, scale * (do_c @ vp.transpose(-1, -2)), zero)
+        dEq = scale * (do_c @ S_c.transpose(-1, -2))                           # w.r.t. (E q)
+        dS_prev = dS_prev + scale * ((q_c * E[..., None]).transpose(-1, -2) @ do_c)
+        dq_c = dEq * E[..., None]
+        dE = (dEq * q_c).sum(-1) * E                                           # w.r.t. (g + car) per token
+        dg_tok = dg_tok + dE
+        dcar_in = dcar_in + dE.sum(-1)
+        # v' = u - e^{car} w S
+        du = dvp
+        dw = -ec[..., None, None] * (dvp @ S_c.transpose(-1, -2))
+        dS_prev = dS_prev - ec[..., None, None] * (w[:, :, c].transpose(-1, -2) @ dvp)
+        dcar_in = dcar_in - ec * ((w[:, :, c] @ S_c) * dvp).sum((-1, -2))
+        dvp_all[:, :, c], dw_all[:, :, c], du_all[:, :, c] = dvp, dw, du
+        # P = tril(q k^T Gamma)
+        dqk = dP * gam[:, :, c]
+        dq_c = dq_c + dqk @ k_c
+        dk_c = dk_c + dqk.transpose(-1, -2) @ q_c
+        dGam = dP * qk[:, :, c] * gam[:, :, c]                                 # w.r.t. (g_i - g_j)
+        if gdn:
+            # u = Ai zu, w = Ai zw, Ai = (I + A)^-1
+            Ai_c = Ai[:, :, c]
+            dzu, dzw = Ai_c.transpose(-1, -2) @ du, Ai_c.transpose(-1, -2) @ dw
+            dAi = du @ zu[:, :, c].transpose(-1, -2) + dw @ zw[:, :, c].transpose(-1, -2)
+            dA = torch.where(tril_s, -(Ai_c.transpose(-1, -2) @ dAi @ Ai_c.transpose(-1, -2)), zero)
+            b_c = bc[:, :, c]
+            # A = beta_i (k k^T)_ij Gamma_ij
+            dkk = dA * b_c[..., :, None] * gam[:, :, c]
+            dk_c = dk_c + dkk @ k_c + dkk.transpose(-1, -2) @ k_c
+            db = (dA * kk[:, :, c] * gam[:, :, c]).sum(-1)
+            dGam = dGam + dA * A[:, :, c]
+            # zu = v beta ; zw = k beta e^{g}
+            dvc[:, :, c] = dzu * b_c[..., None]
+            db = db + (dzu * vc[:, :, c]).sum(-1)
+            eg = g_c.exp()
+            dk_c = dk_c + dzw * (b_c * eg)[..., None]
+            zk = (dzw * k_c).sum(-1)
+            db = db + zk * eg
+            dg_tok = dg_tok + zk * b_c * eg
+            dbc[:, :, c] = db
+        else:
+            dvc[:, :, c] = du
+        dg_tok = dg_tok + dGam.sum(-1) - dGam.sum(-2)
+        dg_tok[..., -1] = dg_tok[..., -1] + dgl                                # g_last is the cumsum at the last token
+        dgc[:, :, c] = dg_tok
+        dqn[:, :, c], dkn[:, :, c] = dq_c, dk_c
+        dS, dcar = dS_prev, dcar_in
+    dh0 = dS + dh0_extra
+    # ---- back through the chunk-local cumsum and the l2 normalisation
+    dg = torch.flip(torch.flip(dgc, [-1]).cumsum(-1), [-1])                    # reverse cumsum inside each chunk
+    un = lambda x, D: x.permute(0, 2, 3, 1, 4).reshape(B, T, H, D)
+    uns = lambda x: x.permute(0, 2, 3, 1).reshape(B, T, H)
+    dqn_t, dkn_t = un(dqn, K), un(dkn, K)
+    if use_l2norm:
+        dq = q_rstd[..., None] * (dqn_t - qn * (dqn_t * qn).sum(-1, keepdim=True))
+        dk = k_rstd[..., None] * (dkn_t - kn * (dkn_t * kn).sum(-1, keepdim=True))
+    else:
+        dq, dk = dqn_t, dkn_t
+    return dict(dq=dq, dk=dk, dv=un(dvc, V), dg=uns(dg), dbeta=uns(dbc) if gdn else None,
+                dh0=dh0 if h0 is not None else None, dS=dS_all, dvp=un(dvp_all, V), dw=un(dw_all, K), du=un(du_all, V))

@@ -119,3 +119,39 @@ def test_dnats_attn_is_the_bias_derivative_on_selected_blocks():
     want = bias.grad.view(B, 2, 2, TN).sum(2).permute(0, 2, 1)
     want = torch.where(sel.to(torch.bool), want, torch.zeros_like(want))
     assert (got - want).abs().max() < 1e-10
+
+
+@pytest.mark.parametrize("rule", ["gdn", "mamba"])
+@pytest.mark.parametrize("decay,use_h0", [(True, True), (False, False)])
+def test_written_out_chunk_backward_equals_autograd(rule, decay, use_h0):
+    B, T, H, K, V = 2, 320, 2, 8, 6
+    q, k, v, g, beta, do, dht, h0 = _inputs(B, T, H, K, V, 9)
+    types = otab.synth_types(B, T // 64, 2, 0.5, seed=10, dtype=DT)
+    types[0, -1] = 1                                        # batch 0 ends selected, batch 1 as drawn
+    sel = types[..., 1]
+    kw = dict(scale=0.6, decay=decay, use_l2norm=(rule == "gdn"), rule=rule, h0=h0 if use_h0 else None)
+    b = beta if rule == "gdn" else None
+    got = ograd.linear_chunk_backward(q, k, v, g, b, sel, do, dht, **kw)
+    true = ograd.linear_true_grads(q, k, v, g, beta, sel, do, dht, **kw)
+    for n in ("dq", "dk", "dv", "dg", "dbeta", "dh0"):
+        if true[n] is None:
+            assert got[n] is None
+            continue
+        assert (got[n] - true[n]).abs().max() < 1e-8, (n, float((got[n] - true[n]).abs().max()))
+
+
+def test_state_gradients_of_the_written_out_backward_equal_the_probe_gradients():
+    B, T, H, K, V = 1, 320, 2, 8, 6
+    q, k, v, g, beta, do, dht, h0 = _inputs(B, T, H, K, V, 11)
+    types = otab.synth_types(B, T // 64, 2, 0.5, seed=12, dtype=DT)
+    types[:, -1] = 1
+    sel = types[..., 1]
+    kw = dict(scale=0.6, decay=True, use_l2norm=True, rule="gdn", h0=h0)
+    got = ograd.linear_chunk_backward(q, k, v, g, beta, sel, do, dht, **kw)
+    o, sfin, probes, _ = ograd.chunk_forward_with_probes(q, k, v, g, beta, sel, **kw)
+    grads = torch.autograd.grad((o * do).sum() + (sfin * dht).sum(), probes, allow_unused=True)
+    for c, gr in enumerate(grads):
+        want = torch.zeros_like(got["dS"][:, c]) if gr is None else gr
+        # the probe sits after the chunk and after the point where the final state is taken, so on the last
+        # selected chunk it also receives the gradient of the final state, like dS
+        assert (got["dS"][:, c] - want).abs().max() < 1e-9, c
