@@ -66,6 +66,18 @@ def config0_inputs(seed=0, B=2, T=512, H=4, K=64, V=64, dtype=torch.float32):
     return q, k, v, g, beta
 
 
+def grad_pin_inputs():
+    """Small float64 inputs of the backward pin (B=1, T=256, H=2, K=8, V=6, block 64)."""
+    gen = torch.Generator().manual_seed(21)
+    dt = torch.float64
+    B, T, H, K, V = 1, 256, 2, 8, 6
+    r = lambda *s: torch.randn(*s, generator=gen, dtype=dt)
+    types = otab.synth_types(B, T // 64, 2, 0.5, seed=22, dtype=dt)
+    types[:, -1] = 1
+    return dict(q=r(B, T, H, K), k=r(B, T, H, K), v=r(B, T, H, V), g=-torch.nn.functional.softplus(r(B, T, H)) * 0.3,
+                beta=r(B, T, H).sigmoid(), do=r(B, T, H, V), dht=r(B, H, K, V), types=types)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of a checkout of automl/NeuralAttentionSearchLinear")
@@ -118,6 +130,19 @@ def main():
     np.savez_compressed(os.path.join(HERE, "oracle_config0.npz"), types=types.numpy(),
                         o_lin=o_l[:, ::7].numpy(), s_lin=s_l.numpy(), o_attn=o_a[:, ::7].numpy(), lse=lse[:, ::7].numpy(),
                         mask_rowsum=mask.sum(-1).numpy().astype(np.int32))
+    # ---- 4. regression pin of the no-own-chunk mode and of the backward oracle (float64, small) -------------
+    from oracle import grad as ograd
+    x = grad_pin_inputs()
+    sel = x["types"][..., 1]
+    o_na, s_na = ogdn.linear_chunk(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, nbs=64, own_chunk=False)
+    gr = ograd.linear_chunk_backward(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, x["do"], x["dht"], decay=True)
+    dn = ograd.dnats_linear(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, x["do"], x["dht"], decay=True)
+    ga = ograd.attn_grads(x["q"], x["k"], x["v"], x["types"][..., 0], x["do"], nbs=64, reference_compat=True)
+    np.savez_compressed(os.path.join(HERE, "oracle_grad_pin.npz"), o_no_own=o_na[:, ::5].numpy(), s_no_own=s_na.numpy(),
+                        dq=gr["dq"][:, ::5].numpy(), dk=gr["dk"][:, ::5].numpy(), dv=gr["dv"][:, ::5].numpy(),
+                        dg=gr["dg"].numpy(), dbeta=gr["dbeta"].numpy(), dnats_lin=dn.numpy(),
+                        dq_attn_compat=ga["dq"][:, ::5].numpy(), dk_attn_compat=ga["dk"][:, ::5].numpy(),
+                        dnats_attn=ga["dnats"].numpy())
     print("golden vectors written to", HERE)
 
 

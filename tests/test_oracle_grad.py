@@ -155,3 +155,29 @@ def test_state_gradients_of_the_written_out_backward_equal_the_probe_gradients()
         # the probe sits after the chunk and after the point where the final state is taken, so on the last
         # selected chunk it also receives the gradient of the final state, like dS
         assert (got["dS"][:, c] - want).abs().max() < 1e-9, c
+
+
+def test_regression_pin_of_the_no_own_chunk_mode_and_the_backward_oracle():
+    """tests/golden/oracle_grad_pin.npz (written by tests/golden/make_golden.py) pins the oracle's own values."""
+    import importlib.util
+    import os
+    import numpy as np
+    golden_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(golden_dir, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    z = np.load(os.path.join(golden_dir, "oracle_grad_pin.npz"))
+    x = mg.grad_pin_inputs()
+    sel = x["types"][..., 1]
+    o_na, s_na = ogdn.linear_chunk(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, nbs=64, own_chunk=False)
+    assert np.allclose(o_na[:, ::5].numpy(), z["o_no_own"], atol=1e-12) and np.allclose(s_na.numpy(), z["s_no_own"], atol=1e-12)
+    gr = ograd.linear_chunk_backward(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, x["do"], x["dht"], decay=True)
+    for n in ("dq", "dk", "dv"):
+        assert np.allclose(gr[n][:, ::5].numpy(), z[n], atol=1e-10), n
+    assert np.allclose(gr["dg"].numpy(), z["dg"], atol=1e-10) and np.allclose(gr["dbeta"].numpy(), z["dbeta"], atol=1e-10)
+    dn = ograd.dnats_linear(x["q"], x["k"], x["v"], x["g"], x["beta"], sel, x["do"], x["dht"], decay=True)
+    assert np.allclose(dn.numpy(), z["dnats_lin"], atol=1e-10)
+    ga = ograd.attn_grads(x["q"], x["k"], x["v"], x["types"][..., 0], x["do"], nbs=64, reference_compat=True)
+    assert np.allclose(ga["dq"][:, ::5].numpy(), z["dq_attn_compat"], atol=1e-10)
+    assert np.allclose(ga["dk"][:, ::5].numpy(), z["dk_attn_compat"], atol=1e-10)
+    assert np.allclose(ga["dnats"].numpy(), z["dnats_attn"], atol=1e-10)
