@@ -37,6 +37,7 @@ extern "C" {
 #define NATSL_FLAG_ATTN_OWN_CHUNK 2     /* softmax branch also covers the query's own block ('all', 'attn') */
 #define NATSL_FLAG_NO_TRAILING_QUIRK 4  /* carry the decay also over skipped blocks after the last selected one */
 #define NATSL_FLAG_ATTN_MMA_SYNC 8      /* natsl_attn_fwd: use the mma.sync comparison kernel instead of tcgen05 */
+#define NATSL_FLAG_BWD_REFERENCE_COMPAT 16 /* natsl_attn_bwd: drop the own-block terms, as the reference's default backward does */
 
 #define NATSL_ATTN_BT 128 /* query rows per attention tile; the attn_n_iters table is built for it */
 
@@ -207,6 +208,70 @@ int natsl_pack_selected_pairs(const void* x, const int32_t* indices, const int32
 int natsl_norm_gate_mix(const void* x1, const void* x2, const void* g, const void* xw, int xw_dtype, const void* w1,
                         const void* w2, int w_dtype, void* y, long rows, int D, float eps, int activation,
                         void* stream);
+
+/* ---- backward pass ------------------------------------------------------------------------------------------- */
+
+/* Backward of the softmax branch.  Inputs as natsl_attn_fwd plus o, lse (its outputs) and d_o [B,T,HQ,DV] bf16.
+ * Outputs: dq [B,T,HQ,DK], dk [B,T,HKV,DK], dv [B,T,HKV,DV] bf16; delta [B,T,HQ] fp32 = rowsum(o * do) (scratch
+ * the second kernel reads); dnats_part [B,cdiv(T,64),HQ] fp32 = per 64-key tile and query head the sum of the score
+ * gradients over the queries of later blocks (the caller sums tiles of a block and heads of a selection group and
+ * keeps selected blocks only: the reference's dnats column 0).  flags: NATSL_FLAG_ATTN_OWN_CHUNK as in the forward;
+ * NATSL_FLAG_BWD_REFERENCE_COMPAT reproduces the reference's default backward, which leaves out every own-block term
+ * (src/nats/ops/mixed_ops/mixed_attn_gdn.py:237 passes the flag only for sliding windows).
+ * Replaces: parallel_attn_nats_bwd src/nats/ops/attns/attns.py:1562-1759 (preprocess :357-372, dq :383-708,
+ * dk/dv :719-982). */
+int natsl_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                   const int32_t* types_i, void* dq, void* dk, void* dv, float* delta, float* dnats_part, int B, int T,
+                   int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale, int flags, void* stream);
+
+/* Backward of the linear branch, block size 64, in five stages that run after the forward's own preparation
+ * (natsl_gdn_chunk_prep / natsl_chunk_local_cumsum -> w, u, gcs) and recurrence (natsl_linear_fwd_h -> h, carry).
+ * For NATSL_RULE_MAMBA pass w = NULL, u = vp = v, and NULL for v, dw, beta, dv, dbeta.
+ *  1 natsl_linear_bwd_pre    qn, kn [B,T,H,K] bf16 = l2-normalised q, k with q_rstd, k_rstd [B,T,H] (use_l2norm = 0:
+ *                            nothing is written, pass q, k themselves on); dvl [B,T,H,V] bf16 = scale * P^T do.
+ *  2 natsl_linear_bwd_dh     reverse walk over the chunks: dS_all [B,NT,H,K,V] bf16 = gradient w.r.t. the state after
+ *                            every chunk that updates it (other slots are not written), dvp [B,T,H,V] bf16 = gradient
+ *                            w.r.t. v', dh0 [B,H,K,V] fp32 (may be NULL); dht [B,H,K,V] fp32 or NULL.
+ *  3 natsl_linear_bwd_state  vp [B,T,H,V] = v'; dw, dq1, dk1 [B,T,H,K] bf16 (dk1 is written for updating chunks only);
+ *                            dkd [B,T,H] fp32; scal [B,NT,H,4] fp32 (slots 0-2); dnats_lin [B,NT,H] fp32 = the
+ *                            reference's dnats column 1 before the sum over the heads of a selection group
+ *                            (invalid_dnats: also for chunks that do not update the state, from the raw values and the
+ *                            state gradient of the next updating chunk).
+ *  4 natsl_linear_bwd_intra  dq, dk [B,T,H,K], dv [B,T,H,V] bf16, dbeta, dg_tok [B,T,H] fp32, scal slot 3.
+ *  5 natsl_linear_bwd_dg     dg [B,T,H] fp32 from dg_tok and scal; flags as natsl_linear_fwd_h.
+ * Replaces: chunk_gated_delta_rule_nats_bwd src/nats/ops/gated_delta_rule/chunk.py:170-332 (kernels
+ * src/nats/ops/common/chunk_o.py:234-571, 927-1173, src/nats/ops/common/chunk_delta_h.py:346-635,
+ * src/nats/ops/gated_delta_rule/wy_fast.py:169-334), chunk_mamba2_bwd src/nats/ops/mamba/chunk.py:112-240, the reversed
+ * cumsums chunk.py:318-331 and l2norm_bwd src/nats/ops/mixed_ops/mixed_attn_gdn.py:273-275. */
+int natsl_linear_bwd_pre(const void* q, const void* k, const void* d_o, const float* gcs, void* qn, void* kn, float* q_rstd,
+                         float* k_rstd, void* dvl, int B, int T, int H, int K, int V, float scale, int use_l2norm,
+                         void* stream);
+int natsl_linear_bwd_dh(int rule, const void* qn, const void* kn, const void* w, const void* d_o, const void* dvl,
+                        const float* gcs, const float* carry, const int32_t* types_i, const int32_t* indices,
+                        const int32_t* n_blocks, const float* dht, void* dS_all, void* dvp, float* dh0, int B, int T, int H,
+                        int HN, int K, int V, float scale, void* stream);
+int natsl_linear_bwd_state(int rule, const void* kn, const void* v, const void* w, const void* u, const void* d_o,
+                           const void* dvp, const float* gcs, const void* h, const float* carry, const void* dS_all,
+                           const int32_t* types_i, const int32_t* indices, const int32_t* n_blocks,
+                           const int32_t* starting_h_idx, void* vp, void* dw, void* dq1, void* dk1, float* dkd, float* scal,
+                           float* dnats_lin, int B, int T, int H, int HN, int K, int V, float scale, int invalid_dnats,
+                           void* stream);
+int natsl_linear_bwd_intra(int rule, const void* qn, const void* kn, const void* v, const void* w, const void* u,
+                           const void* vp, const void* dvp, const void* dw, const void* d_o, const void* dq1,
+                           const void* dk1, const float* gcs, const void* beta, int beta_dtype, const float* q_rstd,
+                           const float* k_rstd, const float* dkd, const int32_t* types_i, void* dq, void* dk, void* dv,
+                           float* dbeta, float* dg_tok, float* scal, int B, int T, int H, int HN, int K, int V, float scale,
+                           int use_l2norm, void* stream);
+int natsl_linear_bwd_dg(const float* dg_tok, const float* scal, const int32_t* types_i, const int32_t* indices,
+                        const int32_t* n_blocks, float* dg, int B, int T, int H, int HN, int flags, void* stream);
+
+/* Backward of natsl_norm_gate_mix: dx1, dx2, dg [rows, D] bf16; dxw [rows, 2] fp32 (NULL iff xw is NULL); dw_part
+ * [n_part, 2, D] fp32 = per-CTA partial sums of the gradients of w1 and w2 (n_part CTAs are launched, each strides over
+ * the rows; the caller adds the partials up).
+ * Replaces: the backward of FusedMultiInputRMSNormGated, src/nats/modules/fused_norm_gate.py:353, :657. */
+int natsl_norm_gate_mix_bwd(const void* x1, const void* x2, const void* g, const void* xw, int xw_dtype, const void* w1,
+                            const void* w2, int w_dtype, const void* dy, void* dx1, void* dx2, void* dg, float* dxw,
+                            float* dw_part, int n_part, long rows, int D, float eps, int activation, void* stream);
 
 /* Gated-delta-rule branch forward (prep -> recurrence -> output) that allocates nothing and asks
  * the caller for no intermediate buffers: they live in a fixed NATSL_NOALLOC_SCRATCH_BYTES array

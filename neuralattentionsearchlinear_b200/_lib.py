@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libnatsl_b200.so")
 DT_BF16, DT_F32, DT_F16, DT_I32 = 0, 1, 2, 3
 RULE_GDN, RULE_MAMBA = 0, 1
 FLAG_DECAY_SKIPPED, FLAG_ATTN_OWN_CHUNK, FLAG_NO_TRAILING_QUIRK, FLAG_ATTN_MMA_SYNC = 1, 2, 4, 8
+FLAG_BWD_REFERENCE_COMPAT = 16
 ATTN_BT = 128
 
 _p, _i, _f = C.c_void_p, C.c_int, C.c_float
@@ -41,6 +42,15 @@ PROTOTYPES = {
     "natsl_linear_recurrent_fwd": [_i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "natsl_attn_fwd_fp32": [_i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_norm_gate_mix": [_p, _p, _p, _p, _i, _p, _p, _i, _p, C.c_long, _i, _f, _i, _p],
+    "natsl_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_linear_bwd_pre": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_linear_bwd_dh": [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p],
+    "natsl_linear_bwd_state": [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p,
+                               _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_linear_bwd_intra": [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p,
+                               _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "natsl_linear_bwd_dg": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
+    "natsl_norm_gate_mix_bwd": [_p, _p, _p, _p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, C.c_long, _i, _f, _i, _p],
     "natsl_gdn_fwd_noalloc": [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20

@@ -220,3 +220,133 @@ def attn_fwd_fp32(q, k, v, tables: SelectionTables, scale: float, own_chunk: boo
               o.data_ptr(), lse.data_ptr(), B, T, HQ, HKV, tables.types_i.shape[2], DK, DV, tables.nats_block_size,
               float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0, current_stream_ptr(q.device))
     return o, lse
+
+
+# ------------------------------------------------------------------------------------------------ backward
+def attn_bwd(q, k, v, o, lse, do, tables: SelectionTables, scale: float, own_chunk: bool, reference_compat: bool = False):
+    """Backward of the softmax branch.  -> (dq, dk, dv bf16, dnats_attn [B,TN,HN] fp32): ``dnats_attn`` is the sum of the
+    score gradients of the keys of a softmax-selected block over the queries of later blocks, summed over the heads
+    of a selection group and zero for the other blocks (src/nats/ops/attns/attns.py:922, 975-978, 1625-1629, 1749-1755).
+    ``reference_compat``: leave out every own-block term like the reference's default backward."""
+    for t_ in (q, k, v, o, do):
+        _need(t_.dtype == BF16, "softmax-branch backward needs bf16 tensors", TypeError)
+    _check_qkv(q, k, v, tables, "softmax branch (backward)", same_heads=False)
+    q, k, v, o, do, lse = (t_.contiguous() for t_ in (q, k, v, o, do, lse))
+    B, T, HQ, DK = q.shape
+    HKV, DV = k.shape[2], v.shape[3]
+    _need(k.shape[1] == T and tables.T == T, "q, k and the tables must cover the same sequence")
+    _need(tuple(do.shape) == (B, T, HQ, DV) and tuple(o.shape) == (B, T, HQ, DV), "o and do must be [B,T,HQ,DV]")
+    TN, HN = tables.types_i.shape[1], tables.types_i.shape[2]
+    nbs = tables.nats_block_size
+    NT = cdiv(T, 64)
+    dev = q.device
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty(B, T, HQ, dtype=torch.float32, device=dev)
+    part = torch.empty(B, NT, HQ, dtype=torch.float32, device=dev)
+    flags = (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_BWD_REFERENCE_COMPAT if reference_compat else 0)
+    _lib.call("natsl_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+              tables.types_i.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), part.data_ptr(),
+              B, T, HQ, HKV, HN, DK, DV, nbs, float(scale), flags, current_stream_ptr(dev))
+    cpb = nbs // 64
+    if NT != TN * cpb:                                        # ragged last block: pad the tile axis
+        part = torch.nn.functional.pad(part, (0, 0, 0, TN * cpb - NT))
+    per_block = part.view(B, TN, cpb, HN, HQ // HN).sum((2, 4))
+    dnats = per_block * (tables.types_i[..., 0] != 0)
+    return dq, dk, dv, dnats
+
+
+def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool, use_l2norm: bool,
+               do, dht=None, invalid_dnats: bool = True, trailing_quirk: bool = True, return_intermediates: bool = False):
+    """Backward of the linear branch (block size 64).  Recomputes the forward's preparation and recurrence, then runs the
+    five backward stages.  -> dict(dq, dk, dv bf16; dg fp32; dbeta fp32 or None; dh0 fp32 or None; dnats [B,NT,HN] fp32
+    = the reference's dnats column for the linear branch, src/nats/ops/common/chunk_o.py:440-443, 459-492, 1568-1575)."""
+    gdn = rule == _lib.RULE_GDN
+    for t_ in (q, k, v, do):
+        _need(t_.dtype == BF16, "linear-branch backward needs bf16 tensors", TypeError)
+    _check_qkv(q, k, v, tables, "linear branch (backward)", same_heads=True)
+    _need(tables.nats_block_size == 64, "the backward pass is built for nats_block_size = 64", NotImplementedError)
+    q, k, v, do = q.contiguous(), k.contiguous(), v.contiguous(), do.contiguous()
+    B, T, H, K = q.shape
+    V = v.shape[3]
+    _need(K in (64, 128) and V in (64, 128), f"backward head dims K={K} V={V}: 64 or 128 each", NotImplementedError)
+    _need(tables.T == T, f"tables were built for T={tables.T}, the sequence has T={T}")
+    dev = q.device
+    HN = tables.types_i.shape[2]
+    NT = cdiv(T, 64)
+    st = current_stream_ptr(dev)
+    g = g.float().contiguous()
+    bf = dict(dtype=BF16, device=dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    gcs = torch.empty(B, T, H, **f32)
+    # ---- forward recompute: w, u, gcs; the state and the carried decay every chunk reads
+    if gdn:
+        beta = beta.contiguous()
+        _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
+        w, u = torch.empty(B, T, H, K, **bf), torch.empty(B, T, H, V, **bf)
+        krs0 = torch.empty(B, T, H, **f32)
+        _lib.call("natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                  _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
+                  krs0.data_ptr(), B, T, H, K, V, int(use_l2norm), st)
+    else:
+        w, u, krs0 = None, v, None
+        _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
+    if h0 is not None:
+        h0 = h0.float().contiguous()
+    flags = (_lib.FLAG_DECAY_SKIPPED if decay else 0) | (0 if trailing_quirk else _lib.FLAG_NO_TRAILING_QUIRK)
+    h = torch.empty(B, NT, H, K, V, **bf)
+    carry = torch.empty(B, NT, H, **f32)
+    _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krs0),
+              tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
+              h.data_ptr(), carry.data_ptr(), None, B, T, H, HN, K, V, 64, flags, st)
+    # ---- 1: normalised q, k and the chunk-local part of dv'
+    l2 = bool(use_l2norm and gdn)
+    if l2:
+        qn, kn = torch.empty_like(q), torch.empty_like(k)
+        qrs, krs = torch.empty(B, T, H, **f32), torch.empty(B, T, H, **f32)
+    else:
+        qn, kn, qrs, krs = q, k, None, None
+    dvl = torch.empty(B, T, H, V, **bf)
+    _lib.call("natsl_linear_bwd_pre", q.data_ptr(), k.data_ptr(), do.data_ptr(), gcs.data_ptr(), _lib.ptr(qn if l2 else None),
+              _lib.ptr(kn if l2 else None), _lib.ptr(qrs), _lib.ptr(krs), dvl.data_ptr(), B, T, H, K, V, float(scale), int(l2), st)
+    # ---- 2: reverse walk
+    dS_all = torch.empty(B, NT, H, K, V, **bf)
+    dvp = torch.empty(B, T, H, V, **bf)
+    dh0 = torch.empty(B, H, K, V, **f32) if h0 is not None else None
+    if dht is not None:
+        dht = dht.float().contiguous()
+    _lib.call("natsl_linear_bwd_dh", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(w), do.data_ptr(), dvl.data_ptr(),
+              gcs.data_ptr(), carry.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
+              tables.n_blocks.data_ptr(), _lib.ptr(dht), dS_all.data_ptr(), dvp.data_ptr(), _lib.ptr(dh0), B, T, H, HN, K, V,
+              float(scale), st)
+    # ---- 3: everything that contracts with the state or its gradient
+    vp = torch.empty(B, T, H, V, **bf) if gdn else v
+    dw = torch.empty(B, T, H, K, **bf) if gdn else None
+    dq1, dk1 = torch.empty(B, T, H, K, **bf), torch.empty(B, T, H, K, **bf)
+    dkd = torch.empty(B, T, H, **f32)
+    scal = torch.empty(B, NT, H, 4, **f32)
+    dn_lin = torch.empty(B, NT, H, **f32)
+    _lib.call("natsl_linear_bwd_state", rule, kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w), u.data_ptr(),
+              do.data_ptr(), dvp.data_ptr(), gcs.data_ptr(), h.data_ptr(), carry.data_ptr(), dS_all.data_ptr(),
+              tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
+              tables.starting_h_idx.data_ptr(), _lib.ptr(vp if gdn else None), _lib.ptr(dw), dq1.data_ptr(), dk1.data_ptr(),
+              dkd.data_ptr(), scal.data_ptr(), dn_lin.data_ptr(), B, T, H, HN, K, V, float(scale), int(invalid_dnats), st)
+    # ---- 4: the 64 x 64 part, the WY transform and the l2 norm
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    dv = torch.empty_like(v) if gdn else dvp
+    dbeta = torch.empty(B, T, H, **f32) if gdn else None
+    dg_tok = torch.empty(B, T, H, **f32)
+    _lib.call("natsl_linear_bwd_intra", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w),
+              _lib.ptr(u if gdn else None), vp.data_ptr(), _lib.ptr(dvp if gdn else None), _lib.ptr(dw), do.data_ptr(),
+              dq1.data_ptr(), dk1.data_ptr(), gcs.data_ptr(), _lib.ptr(beta if gdn else None),
+              _lib.DT_BF16 if (gdn and beta.dtype == BF16) else _lib.DT_F32, _lib.ptr(qrs), _lib.ptr(krs), dkd.data_ptr(),
+              tables.types_i.data_ptr(), dq.data_ptr(), dk.data_ptr(), _lib.ptr(dv if gdn else None), _lib.ptr(dbeta),
+              dg_tok.data_ptr(), scal.data_ptr(), B, T, H, HN, K, V, float(scale), int(l2), st)
+    # ---- 5: decay gradients
+    dg = torch.empty(B, T, H, **f32)
+    _lib.call("natsl_linear_bwd_dg", dg_tok.data_ptr(), scal.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
+              tables.n_blocks.data_ptr(), dg.data_ptr(), B, T, H, HN, flags, st)
+    dnats = dn_lin.view(B, NT, HN, H // HN).sum(-1)
+    out = dict(dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, dnats=dnats)
+    if return_intermediates:
+        out.update(dS=dS_all, dvp=dvp, dw=dw, vp=vp, h=h, carry=carry, gcs=gcs, w=w, u=u)
+    return out

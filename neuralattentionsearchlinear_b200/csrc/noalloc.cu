@@ -71,6 +71,19 @@ extern "C" int natsl_gdn_fwd_noalloc(const void* q, const void* k, const void* v
     NATSL_REQUIRE(q && k && v && g && beta && types_i && indices && n_blocks && o, NATSL_ERR_NULL,
                   "natsl_gdn_fwd_noalloc: null pointer");
     NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && K > 0 && V > 0, NATSL_ERR_BAD_SHAPE, "natsl_gdn_fwd_noalloc: empty shape");
+    // Everything the three stages would reject is rejected here, before the first launch: a refused call
+    // must leave the shared array (and the outputs) untouched.
+    NATSL_REQUIRE(HN > 0 && H % HN == 0, NATSL_ERR_BAD_SHAPE, "natsl_gdn_fwd_noalloc: %d heads over %d selection heads", H,
+                  HN);
+    NATSL_REQUIRE(nbs >= 64 && nbs % 64 == 0, NATSL_ERR_UNSUPPORTED,
+                  "natsl_gdn_fwd_noalloc: nats_block_size must be a multiple of 64 (got %d)", nbs);
+    NATSL_REQUIRE((K == 64 && (V == 64 || V == 128)) || (K == 128 && (V == 64 || V == 128 || V == 256)),
+                  NATSL_ERR_UNSUPPORTED,
+                  "natsl_gdn_fwd_noalloc: unsupported head dims K=%d V=%d (K in {64,128}, V in {64,128,256})", K, V);
+    NATSL_REQUIRE(beta_dtype == NATSL_DT_BF16 || beta_dtype == NATSL_DT_F32, NATSL_ERR_UNSUPPORTED,
+                  "natsl_gdn_fwd_noalloc: beta must be bf16 or f32");
+    NATSL_REQUIRE(B <= 65535 && (long)H * (V / 64 + 1) <= 65535, NATSL_ERR_TOO_LARGE,
+                  "natsl_gdn_fwd_noalloc: grid too large (B=%d H=%d)", B, H);
     const size_t NT = (size_t)(T + 63) / 64;
     const size_t n_tok = (size_t)B * T * H;
     const size_t sz_w = align256(n_tok * K * 2), sz_u = align256(n_tok * V * 2), sz_f = align256(n_tok * 4);

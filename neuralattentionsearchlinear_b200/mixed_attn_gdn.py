@@ -6,6 +6,9 @@ Same function names, argument order, defaults and return values as the reference
 """
 from __future__ import annotations
 
+import contextlib
+import os
+
 import torch
 
 from . import _lib, _ops
@@ -55,9 +58,52 @@ def per_chunk_tables(nats_block_types, T, nats_block_size):
     return build_selection_tables(per_chunk, T, CHUNK_SIZE)
 
 
+# The reference's softmax-branch backward leaves out every own-block term of dq, dk, dv with the default settings
+# (the flag it passes in backward is tied to sliding windows: mixed_attn_gdn.py:237 against :115 in the forward), so
+# it is not the gradient of its own forward.  The default here is the true gradient; set this switch (or the
+# environment variable NATSL_REFERENCE_COMPAT_BWD=1) to reproduce the reference's numbers instead.
+REFERENCE_COMPAT_BWD = os.environ.get("NATSL_REFERENCE_COMPAT_BWD", "0") == "1"
+
+
+@contextlib.contextmanager
+def reference_compat_bwd(enabled: bool = True):
+    """Within this context the ops record ``enabled`` as their softmax-branch backward mode."""
+    global REFERENCE_COMPAT_BWD
+    old, REFERENCE_COMPAT_BWD = REFERENCE_COMPAT_BWD, bool(enabled)
+    try:
+        yield
+    finally:
+        REFERENCE_COMPAT_BWD = old
+
+
+def _zeros_like_or_none(t):
+    return None if t is None else torch.zeros_like(t)
+
+
+def hybrid_backward(ctx, rule, do_lin, do_attn, dht):
+    """Shared backward of the two hybrid ops: softmax-branch dq/dk/dv, linear-branch dq/dk/dv/dg/dbeta/dh0 and the
+    ``dnats`` pair (mixed_attn_gdn.py:196-283; mixed_attn_mamba.py:194-292)."""
+    if not ctx.bwd_ok:
+        raise NotImplementedError(ctx.bwd_why)
+    q_attn, k_attn, v_attn, o_attn, lse, q, k, v, g, beta, h0 = ctx.saved_tensors
+    tables = ctx.tables
+    if do_attn is None:
+        do_attn = torch.zeros_like(o_attn)
+    if do_lin is None:
+        do_lin = torch.zeros(q.shape[:3] + (v.shape[3],), dtype=q.dtype, device=q.device)
+    dqa, dka, dva, dn_attn = _ops.attn_bwd(q_attn, k_attn, v_attn, o_attn, lse, do_attn.to(o_attn.dtype), tables,
+                                           ctx.scale_attn, ctx.own_attn, reference_compat=ctx.compat)
+    r = _ops.linear_bwd(rule, q, k, v, g, beta, tables, ctx.scale_lattn, h0, ctx.decay, ctx.use_l2norm,
+                        do_lin.to(q.dtype), dht=dht, invalid_dnats=ctx.invalid_dnats_linear)
+    dnats = torch.stack([dn_attn, r['dnats']], -1).to(ctx.types_dtype)
+    dg = r['dg'].to(g.dtype)
+    dbeta = None if r['dbeta'] is None else r['dbeta'].to(beta.dtype)
+    dh0 = None if (h0 is None or r['dh0'] is None) else r['dh0'].to(h0.dtype)
+    return dqa, dka, dva, r['dq'], r['dk'], r['dv'], dh0, dg, dbeta, dnats
+
+
 class NAtSMixedAttentionGDN(torch.autograd.Function):
-    """Forward of mixed_attn_gdn.py:47-191.  Backward (mixed_attn_gdn.py:196-283) is not built yet
-    and raises."""
+    """Forward and backward of mixed_attn_gdn.py:47-283."""
 
     @staticmethod
     def forward(ctx, q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_gated_delta, g, beta,
@@ -73,6 +119,7 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
         if own_linear and not incomplete_block_start_with_ht:
             raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
         T = q_lattn.shape[1]
+        ctx.bwd_ok, ctx.bwd_why = True, ""
         if q_lattn.dtype == torch.float32:
             if not own_linear:
                 raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
@@ -82,7 +129,7 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
             o_gdn, ht, _ = _ops.linear_recurrent(_lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, tables, scale_lattn,
                                                  initial_state_gated_delta, decay_for_non_gdn_blocks,
                                                  lattn_use_qk_l2norm_in_kernel)
-            ctx.mark_non_differentiable(o_gdn, o_attn)
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for bf16 tensors (fp32 tensors run forward only)"
             return o_gdn, o_attn, (ht if output_final_state_gated_delta else None)
         # The two branches are independent: the softmax branch runs on a side stream (as the reference does for
         # its Mamba2 / DeltaNet ops, src/nats/ops/mixed_ops/mixed_attn_mamba.py:114-124) and joins before returning.
@@ -101,17 +148,31 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
                                        initial_state_gated_delta, decay_for_non_gdn_blocks,
                                        lattn_use_qk_l2norm_in_kernel, output_final_state_gated_delta,
                                        own_chunk=own_linear, tables_event=tables_ready)
-        for t_ in (lin_tables.types_i, lin_tables.indices, lin_tables.n_blocks):
-            t_.record_stream(cur)                      # allocated on the side stream, read by the recurrence
         cur.wait_stream(side)
-        for t_ in (q_attn, k_attn, v_attn, nats_block_types, o_attn, lse):
-            t_.record_stream(side)
-        ctx.mark_non_differentiable(o_gdn, o_attn)
+        for t_ in (tables.types_i, tables.indices, tables.n_blocks, tables.starting_h_idx, lin_tables.types_i,
+                   lin_tables.indices, lin_tables.n_blocks, o_attn, lse):
+            t_.record_stream(cur)                      # allocated on the side stream, read on the current one
+        for t_ in (q_attn, k_attn, v_attn, nats_block_types):
+            t_.record_stream(side)                     # allocated elsewhere, read on the side stream
+        if not own_linear:
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is not built for ops_for_incomplete_chunks='attn'"
+        elif nats_block_size != CHUNK_SIZE:
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for nats_block_size = 64"
+        ctx.save_for_backward(q_attn, k_attn, v_attn, o_attn, lse, q_lattn, k_lattn, v_lattn, g, beta,
+                              initial_state_gated_delta)
+        ctx.tables = tables
+        ctx.scale_attn, ctx.scale_lattn, ctx.own_attn = float(scale_attn), float(scale_lattn), strategy['attn']
+        ctx.decay, ctx.use_l2norm = bool(decay_for_non_gdn_blocks), bool(lattn_use_qk_l2norm_in_kernel)
+        ctx.invalid_dnats_linear = bool(compute_dnats_for_invalid_blocks_linear_att)
+        ctx.compat = REFERENCE_COMPAT_BWD
+        ctx.types_dtype = nats_block_types.dtype
         return o_gdn, o_attn, ht
 
     @staticmethod
-    def backward(ctx, *grads):
-        raise NotImplementedError("backward of nats_mixed_attn_gdn is not built yet")
+    def backward(ctx, do_gdn, do_attn, dht):
+        grads = hybrid_backward(ctx, _lib.RULE_GDN, do_gdn, do_attn, dht)
+        dqa, dka, dva, dq, dk, dv, dh0, dg, dbeta, dnats = grads
+        return (dqa, dka, dva, dq, dk, dv, dh0, dg, dbeta, dnats) + (None,) * 15
 
 
 def nats_mixed_attn_gdn(
@@ -137,20 +198,22 @@ def nats_mixed_attn_gdn(
 ):
     """-> (o_gated_delta [B,T,H,V], o_attn [B,T,HQ,V_attn], final_state [B,H,K,V] fp32 or None).
 
+    Differentiable (bf16 tensors, block size 64, modes 'all' and 'gated_delta_net'): gradients flow to q/k/v of both
+    branches, g, beta, the initial state and, as the reference's ``dnats``, to ``nats_block_types``.  Configurations
+    without a backward raise ``NotImplementedError`` when ``backward`` is reached.
     ``n_nats_blocks`` is accepted for signature parity; the counts are recomputed on the device
     from ``nats_block_types``."""
     if scale_attn is None:
         scale_attn = k_attn.shape[-1] ** -0.5
     if scale_lattn is None:
         scale_lattn = k_lattn.shape[-1] ** -0.5
-    with torch.no_grad():
-        return NAtSMixedAttentionGDN.apply(
-            q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_gated_delta, g, beta,
-            nats_block_types, n_nats_blocks, scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats,
-            nats_block_size, attn_sw_size, ops_for_incomplete_chunks, output_final_state_gated_delta,
-            compute_dnats_for_invalid_blocks_attn, compute_dnats_for_invalid_blocks_linear_att,
-            decay_for_non_gdn_blocks, incomplete_block_start_with_ht, use_g_for_attn,
-            lattn_use_qk_l2norm_in_kernel)
+    return NAtSMixedAttentionGDN.apply(
+        q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_gated_delta, g, beta,
+        nats_block_types, n_nats_blocks, scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats,
+        nats_block_size, attn_sw_size, ops_for_incomplete_chunks, output_final_state_gated_delta,
+        compute_dnats_for_invalid_blocks_attn, compute_dnats_for_invalid_blocks_linear_att,
+        decay_for_non_gdn_blocks, incomplete_block_start_with_ht, use_g_for_attn,
+        lattn_use_qk_l2norm_in_kernel)
 
 
 def _chunk_start_state(inter, ht, gcs, tables, op_type_last_chunk, T, nbs, decay):
@@ -188,9 +251,9 @@ def nats_mixed_attn_gdn_chunk_inference(
         cu_seqlens=None, cu_seqlens_nats=None,
         nats_block_size: int = 64,
         attn_sw_size: int | None = None,
-        ops_for_incomplete_chunks: str = 'all',
-        output_final_state_gated_delta: bool = True,
-        decay_for_non_gdn_blocks: bool = True,
+        ops_for_incomplete_chunks: str = 'gated_delta_net',
+        output_final_state_gated_delta: bool = False,
+        decay_for_non_gdn_blocks: bool = False,
         incomplete_block_start_with_ht: bool = True,
         use_g_for_attn: bool = False,
         lattn_use_qk_l2norm_in_kernel: bool = True,

@@ -8,6 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib, _ops
+from . import mixed_attn_gdn as gdn_ops
 from .mixed_attn_gdn import _check_common, _chunk_start_state, per_chunk_tables
 from .nats_util import build_selection_tables
 
@@ -17,6 +18,56 @@ all_incomplete_ops = {
     'attn': dict(attn=True, mamba=False),
     'mamba': dict(attn=False, mamba=True),
 }
+
+
+class NAtSMixedAttentionMamba(torch.autograd.Function):
+    """Forward and backward of mixed_attn_mamba.py:51-292."""
+
+    @staticmethod
+    def forward(ctx, q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_mamba, g, nats_block_types,
+                n_nats_blocks, scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats, nats_block_size, attn_sw_size,
+                ops_for_incomplete_chunks, output_final_state_mamba, compute_dnats_for_invalid_blocks_attn,
+                compute_dnats_for_invalid_blocks_linear_att, decay_for_non_mamba_blocks, incomplete_block_start_with_ht,
+                use_g_for_attn):
+        _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
+                      all_incomplete_ops)
+        strategy = all_incomplete_ops[ops_for_incomplete_chunks]
+        own_linear = strategy['mamba']
+        if own_linear and not incomplete_block_start_with_ht:
+            raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
+        T = q_lattn.shape[1]
+        tables = build_selection_tables(nats_block_types, T, nats_block_size)
+        lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
+        ctx.bwd_ok, ctx.bwd_why = True, ""
+        if q_lattn.dtype == torch.float32:
+            if not own_linear:
+                raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
+            o_attn, _ = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+            o_m, ht, _ = _ops.linear_recurrent(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
+                                               initial_state_mamba, decay_for_non_mamba_blocks, False)
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for bf16 tensors (fp32 tensors run forward only)"
+            return o_m, o_attn, (ht if output_final_state_mamba else None)
+        o_attn, lse = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
+        o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, lin_tables, scale_lattn,
+                                     initial_state_mamba, decay_for_non_mamba_blocks, False,
+                                     output_final_state_mamba, own_chunk=own_linear)
+        if not own_linear:
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is not built for ops_for_incomplete_chunks='attn'"
+        elif nats_block_size != 64:
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for nats_block_size = 64"
+        ctx.save_for_backward(q_attn, k_attn, v_attn, o_attn, lse, q_lattn, k_lattn, v_lattn, g, None, initial_state_mamba)
+        ctx.tables = tables
+        ctx.scale_attn, ctx.scale_lattn, ctx.own_attn = float(scale_attn), float(scale_lattn), strategy['attn']
+        ctx.decay, ctx.use_l2norm = bool(decay_for_non_mamba_blocks), False
+        ctx.invalid_dnats_linear = bool(compute_dnats_for_invalid_blocks_linear_att)
+        ctx.compat = gdn_ops.REFERENCE_COMPAT_BWD
+        ctx.types_dtype = nats_block_types.dtype
+        return o_m, o_attn, ht
+
+    @staticmethod
+    def backward(ctx, do_m, do_attn, dht):
+        dqa, dka, dva, dq, dk, dv, dh0, dg, _, dnats = gdn_ops.hybrid_backward(ctx, _lib.RULE_MAMBA, do_m, do_attn, dht)
+        return (dqa, dka, dva, dq, dk, dv, dh0, dg, dnats) + (None,) * 14
 
 
 def nats_mixed_attn_mamba(
@@ -38,33 +89,17 @@ def nats_mixed_attn_mamba(
         incomplete_block_start_with_ht: bool = True,
         use_g_for_attn: bool = False,
 ):
-    """-> (o_mamba [B,T,H,V], o_attn [B,T,HQ,V_attn], final_state [B,H,K,V] fp32 or None).  Forward only."""
-    _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn,
-                  all_incomplete_ops)
-    strategy = all_incomplete_ops[ops_for_incomplete_chunks]
-    own_linear = strategy['mamba']
-    if own_linear and not incomplete_block_start_with_ht:
-        raise NotImplementedError("incomplete_block_start_with_ht=False is not built")
+    """-> (o_mamba [B,T,H,V], o_attn [B,T,HQ,V_attn], final_state [B,H,K,V] fp32 or None).  Differentiable for bf16
+    tensors with block size 64 in the modes 'all' and 'mamba' (other configurations raise in ``backward``)."""
     if scale_attn is None:
         scale_attn = k_attn.shape[-1] ** -0.5
     if scale_lattn is None:
         scale_lattn = 1                                                     # mixed_attn_mamba.py:318-319
-    T = q_lattn.shape[1]
-    with torch.no_grad():
-        tables = build_selection_tables(nats_block_types, T, nats_block_size)
-        lin_tables = tables if own_linear else per_chunk_tables(nats_block_types, T, nats_block_size)
-        if q_lattn.dtype == torch.float32:
-            if not own_linear:
-                raise NotImplementedError("ops_for_incomplete_chunks='attn' is built for bf16 tensors only")
-            o_attn, _ = _ops.attn_fwd_fp32(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
-            o_m, ht, _ = _ops.linear_recurrent(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, tables, scale_lattn,
-                                               initial_state_mamba, decay_for_non_mamba_blocks, False)
-            return o_m, o_attn, (ht if output_final_state_mamba else None)
-        o_attn, _ = _ops.attn_fwd(q_attn, k_attn, v_attn, tables, scale_attn, own_chunk=strategy['attn'])
-        o_m, ht, _ = _ops.linear_fwd(_lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, lin_tables, scale_lattn,
-                                     initial_state_mamba, decay_for_non_mamba_blocks, False,
-                                     output_final_state_mamba, own_chunk=own_linear)
-    return o_m, o_attn, ht
+    return NAtSMixedAttentionMamba.apply(
+        q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, initial_state_mamba, g, nats_block_types, n_nats_blocks,
+        scale_attn, scale_lattn, cu_seqlens, cu_seqlens_nats, nats_block_size, attn_sw_size, ops_for_incomplete_chunks,
+        output_final_state_mamba, compute_dnats_for_invalid_blocks_attn, compute_dnats_for_invalid_blocks_linear_att,
+        decay_for_non_mamba_blocks, incomplete_block_start_with_ht, use_g_for_attn)
 
 
 def nats_mixed_attn_mamba_chunk_inference(

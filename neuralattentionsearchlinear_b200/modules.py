@@ -93,9 +93,47 @@ def hard_softmax(logits: torch.Tensor, dim: int = -1) -> torch.Tensor:
     return y_hard - y_soft.detach() + y_soft
 
 
+def _dt(t):
+    return _lib.DT_BF16 if (t is not None and t.dtype == torch.bfloat16) else _lib.DT_F32
+
+
+class _NormGateMix(torch.autograd.Function):
+    """y = (rms(x1) w1 a + rms(x2) w2 b) * act(g) on [rows, D] bf16 tensors: ``natsl_norm_gate_mix`` forward,
+    ``natsl_norm_gate_mix_bwd`` backward (src/nats/modules/fused_norm_gate.py:38-182, 353, 657)."""
+
+    @staticmethod
+    def forward(ctx, x1, x2, g, xw, w1, w2, eps, activation):
+        rows, D = x1.shape
+        y = torch.empty_like(x1)
+        _lib.call("natsl_norm_gate_mix", x1.data_ptr(), x2.data_ptr(), g.data_ptr(), _lib.ptr(xw), _dt(xw),
+                  _lib.ptr(w1), _lib.ptr(w2), _dt(w1), y.data_ptr(), rows, D, float(eps), int(activation),
+                  current_stream_ptr(x1.device))
+        ctx.save_for_backward(x1, x2, g, xw, w1, w2)
+        ctx.eps, ctx.activation = float(eps), int(activation)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x1, x2, g, xw, w1, w2 = ctx.saved_tensors
+        rows, D = x1.shape
+        dy = dy.contiguous()
+        dx1, dx2, dg = torch.empty_like(x1), torch.empty_like(x2), torch.empty_like(g)
+        dxw = torch.empty(rows, 2, dtype=torch.float32, device=x1.device) if xw is not None else None
+        n_part = int(min(-(-rows // 8), 1184))
+        dw_part = torch.empty(n_part, 2, D, dtype=torch.float32, device=x1.device)
+        _lib.call("natsl_norm_gate_mix_bwd", x1.data_ptr(), x2.data_ptr(), g.data_ptr(), _lib.ptr(xw), _dt(xw),
+                  _lib.ptr(w1), _lib.ptr(w2), _dt(w1), dy.data_ptr(), dx1.data_ptr(), dx2.data_ptr(), dg.data_ptr(),
+                  _lib.ptr(dxw), dw_part.data_ptr(), n_part, rows, D, ctx.eps, ctx.activation, current_stream_ptr(x1.device))
+        dw1 = dw2 = None
+        if w1 is not None:
+            dw = dw_part.sum(0)
+            dw1, dw2 = dw[0].to(w1.dtype), dw[1].to(w2.dtype)
+        return dx1, dx2, dg, (None if xw is None else dxw.to(xw.dtype)), dw1, dw2, None, None
+
+
 class FusedMultiInputRMSNormGated(nn.Module):
     """y = (rms(x1) w1 a + rms(x2) w2 b) * g * sigmoid(g)  (src/nats/modules/fused_norm_gate.py:1354-1429).
-    Forward only: runs ``natsl_norm_gate_mix`` on CUDA bf16 inputs."""
+    Runs ``natsl_norm_gate_mix`` (and its backward kernel) on CUDA bf16 inputs."""
 
     def __init__(self, hidden_size: int, elementwise_affine: bool = True, eps: float = 1e-5, activation: str = 'swish',
                  device=None, dtype=None):
@@ -119,7 +157,6 @@ class FusedMultiInputRMSNormGated(nn.Module):
         shape = x1.shape
         x1c, x2c, gc = (t.contiguous().view(-1, D) for t in (x1, x2, g.to(x1.dtype)))
         rows = x1c.shape[0]
-        y = torch.empty_like(x1c)
         xw = None
         if x_weights_after_norm is not None:
             xw = x_weights_after_norm.contiguous().view(-1, 2)
@@ -129,8 +166,5 @@ class FusedMultiInputRMSNormGated(nn.Module):
         w1, w2 = self.weight1, self.weight2
         if w1 is not None and w1.dtype not in (torch.bfloat16, torch.float32):
             w1, w2 = w1.float(), w2.float()
-        code = lambda t: _lib.DT_BF16 if (t is not None and t.dtype == torch.bfloat16) else _lib.DT_F32
-        _lib.call("natsl_norm_gate_mix", x1c.data_ptr(), x2c.data_ptr(), gc.data_ptr(), _lib.ptr(xw), code(xw),
-                  _lib.ptr(w1), _lib.ptr(w2), code(w1), y.data_ptr(), rows, D, float(self.eps),
-                  1 if self.activation == 'sigmoid' else 0, current_stream_ptr(x1.device))
+        y = _NormGateMix.apply(x1c, x2c, gc, xw, w1, w2, float(self.eps), 1 if self.activation == 'sigmoid' else 0)
         return y.view(shape)

@@ -288,6 +288,11 @@ def nats_mixed_attn_mamba_sp(q_attn, k_attn, v_attn, q_lattn, k_lattn, v_lattn, 
             last_kv_capacity = (cap, cap_pairs)
         step = max(1, 128 // nbs)
         cap = -(-cap // step) * step                         # keeps the query offset a multiple of 128
+        if kv_capacity is not None:
+            # a caller-given capacity always takes the packed path (also when it is zero), so that segments holding
+            # more selected blocks than promised set device status 3 instead of being left out silently
+            cap, cap_pairs = max(step, cap), max(1, cap_pairs)
+            limit = cap
     if cap == 0:
         o_attn = be.attn(qa, ka, va, tb, scale_attn, own, 0)
     else:

@@ -37,6 +37,22 @@ def attn_mask(sel_attn: torch.Tensor, T: int, nbs: int, HQ: int, own_chunk: bool
     return m
 
 
+def attn_mask_rows(sel_attn: torch.Tensor, T: int, nbs: int, HQ: int, t0: int, t1: int, own_chunk: bool = True) -> torch.Tensor:
+    """Rows [t0, t1) of ``attn_mask`` -> bool [B,HQ,t1-t0,T], for sequences whose full mask does not fit in memory."""
+    B, TN, HN = sel_attn.shape
+    s = torch.arange(T)
+    t = torch.arange(t0, t1)
+    blk_s, blk_t = s // nbs, t // nbs
+    sel = sel_attn.to(torch.bool).repeat_interleave(HQ // HN, dim=2).permute(0, 2, 1)   # [B,HQ,TN]
+    col_sel = sel[:, :, blk_s]                                                          # [B,HQ,T]
+    past = t[:, None] >= (blk_s[None, :] + 1) * nbs
+    m = col_sel[:, :, None, :] & past[None, None]
+    if own_chunk:
+        own = (blk_t[:, None] == blk_s[None, :]) & (t[:, None] >= s[None, :])
+        m = m | own[None, None]
+    return m
+
+
 def attn_sdpa(q, k, v, mask, scale=None):
     """q [B,T,HQ,K]; k [B,T,HKV,K]; v [B,T,HKV,V]; mask [B,HQ,T,T] bool.
     Returns (o [B,T,HQ,V], lse [B,T,HQ] base-2)."""

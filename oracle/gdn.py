@@ -74,11 +74,16 @@ def _per_chunk_selection(sel, nbs, T):
 
 
 def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=True,
-                     use_l2norm=True, rule="gdn", own_chunk=True):
+                     use_l2norm=True, rule="gdn", own_chunk=True, return_block_start=False):
     """Token recurrence with re-roll.  Returns (o [B,T,H,V], final_state [B,H,K,V]).
 
     final_state is the state at the end of the last selected block (what the
     reference's chunk recurrence holds when it stops, chunk_delta_h.py:311-324).
+    With ``return_block_start`` a third value is returned: the state a decoder
+    continues from (src/nats/ops/gated_delta_rule/chunk_fwd.py:178-206) -- when T ends
+    a block, the state after that block's end-of-block step (kept if the block
+    is selected in ``sel``, else rolled back); otherwise the state at the start
+    of the unfinished last block.
     """
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -108,12 +113,18 @@ def linear_recurrent(q, k, v, g, beta, sel, nbs=64, scale=None, h0=None, decay=T
         S_read = S if own_chunk else S0 * gsum.exp()[..., None, None]      # chunk-start state, decayed to t
         o[:, t] = torch.einsum("bhkv,bhk->bhv", S_read, q[:, t] * scale)
         if (t + 1) % nbs == 0 or t == T - 1:
+            if t == T - 1 and (t + 1) % nbs != 0:
+                start = S0.clone()                       # start of the unfinished block
             m = selh[:, t // nbs][..., None, None]
             rolled = S0 * gsum.exp()[..., None, None] if decay else S0
             S = torch.where(m, S, rolled)
             Sfin = torch.where(m, S, Sfin)
             S0 = S.clone()
             gsum = torch.zeros_like(gsum)
+            if t == T - 1 and (t + 1) % nbs == 0:
+                start = S0.clone()
+    if return_block_start:
+        return o, Sfin, start
     return o, Sfin
 
 

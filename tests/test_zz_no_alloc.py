@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-2
 
 
-def _run_both(nat, B, T, H, HN, K, V, nbs, seed, use_h0):
+def _run_both(nat, B, T, H, HN, K, V, nbs, seed, use_h0, warmed=False):
     from neuralattentionsearchlinear_b200 import _lib, _ops
     dev = torch.device("cuda", 0)
     q, k, v, g, beta, h0 = synth_gdn_inputs(B, T, H, K, V, seed=seed, normalize_qk=False)
@@ -31,12 +31,17 @@ def _run_both(nat, B, T, H, HN, K, V, nbs, seed, use_h0):
     ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(dev)
+    free_before = torch.cuda.mem_get_info(dev)[0]      # sees a raw cudaMalloc inside the library too
     _lib.call("natsl_gdn_fwd_noalloc", q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
               _lib.DT_BF16, tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), _lib.ptr(h0),
               o.data_ptr(), ht.data_ptr(), B, T, H, HN, K, V, nbs, scale, _lib.FLAG_DECAY_SKIPPED, 1,
               torch.cuda.current_stream(dev).cuda_stream)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated(dev) == before
+    if warmed:
+        # the first call on a device may make the driver load the library's kernels; from the second call on the
+        # device's free memory must not move (the intermediates of this shape would take about 6 MiB)
+        assert abs(torch.cuda.mem_get_info(dev)[0] - free_before) < (1 << 20)
     assert_close(o, o_ref, TOL, "o (no-alloc vs regular)")
     assert_close(ht, ht_ref, TOL, "final state (no-alloc vs regular)")
 
@@ -46,6 +51,20 @@ def test_no_alloc_entry_matches_regular_path_twice():
     assert torch.cuda.is_available()
     _run_both(nat, 2, 700, 4, 2, 128, 128, 64, seed=3, use_h0=True)       # ragged last chunk, ~6 MB of scratch
     _run_both(nat, 1, 1024, 2, 2, 64, 128, 128, seed=4, use_h0=False)     # second call: other shape, stale scratch
+    _run_both(nat, 2, 700, 4, 2, 128, 128, 64, seed=5, use_h0=True, warmed=True)   # kernels loaded: free memory fixed
+
+
+def test_no_alloc_entry_rejects_before_launching():
+    """A call the stages would refuse (here: value dim 96) is refused before anything is launched, so the output
+    buffer keeps its contents."""
+    from neuralattentionsearchlinear_b200 import _lib
+    x = torch.zeros(4096, device="cuda")
+    o = torch.full((4096,), 7.0, device="cuda")
+    with pytest.raises(_lib.NatslError, match="unsupported head dims"):
+        _lib.call("natsl_gdn_fwd_noalloc", *([x.data_ptr()] * 5), _lib.DT_BF16, *([x.data_ptr()] * 3), None,
+                  o.data_ptr(), None, 1, 64, 1, 1, 64, 96, 64, 1.0, 0, 1, None)
+    torch.cuda.synchronize()
+    assert bool((o == 7.0).all())
 
 
 def test_no_alloc_entry_rejects_oversize():
