@@ -4,8 +4,8 @@
 //     p = exp2(scale*log2(e) * q.k - lse),   delta = rowsum(o * do),   ds = p * (do.v - delta)
 // the gradients are dq = scale * ds k, dk = scale * ds^T q, dv = p^T do.
 //
-// Two kernels, both on mma.sync with bf16 operands and fp32 accumulation, both deterministic (no atomics on
-// global memory):
+// Two kernels, both on mma.sync with bf16 operands and fp32 accumulation, both deterministic (no atomics; every
+// reduction has a fixed order):
 //   attn_bwd_dq_kernel    one CTA per (64 queries, query head): walks the visible 64-key tiles, keeps dq in
 //                         registers; also writes delta (the preprocess kernel of the reference folded in).
 //   attn_bwd_dkdv_kernel  one CTA per (64 keys, key/value head): walks the query tiles that see these keys
@@ -210,14 +210,15 @@ attn_bwd_dkdv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const uint32_t ks = smem_u32(ks_p), vs = smem_u32(vs_p);
     const uint32_t qring = smem_u32(smem + L::ring_a), doring = smem_u32(smem + L::ring_b);
     float* s_vec = reinterpret_cast<float*>(smem + L::vec);  // [stage][lse 64 | delta 64]
-    __shared__ float s_dn[16];
+    __shared__ float s_dn[16][4];                            // per query head of the group and warp: fixed summation order
     __shared__ int s_npast[16];
 
     load_tile_async<64, DK, AB_THREADS>(ks, k + (tokk * HKV + hkv) * DK, (long)HKV * DK, valid_k, tid);
     load_tile_async<64, DV, AB_THREADS>(vs, v + (tokk * HKV + hkv) * DV, (long)HKV * DV, valid_k, tid);
     cp_async_commit();
     if (tid < 16) {
-        s_dn[tid] = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 4; ++wv) s_dn[tid][wv] = 0.f;
         int np = 0;
         if (tid < G) {
             const int hq = hkv * G + tid;
@@ -285,7 +286,7 @@ attn_bwd_dkdv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         decode(i, gi, qt, own);
         if (gi != dn_gi) {                                    // uniform over the CTA
             dn_acc = warp_sum(dn_acc);
-            if (lane == 0) atomicAdd(&s_dn[dn_gi], dn_acc);
+            if (lane == 0) s_dn[dn_gi][warp] += dn_acc;
             dn_acc = 0.f;
             dn_gi = gi;
         }
@@ -322,7 +323,7 @@ attn_bwd_dkdv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     }
     cp_async_wait<0>();
     dn_acc = warp_sum(dn_acc);
-    if (lane == 0 && total > 0) atomicAdd(&s_dn[dn_gi], dn_acc);
+    if (lane == 0 && total > 0) s_dn[dn_gi][warp] += dn_acc;
 
     // ---- stores: dk = scale * acc, dv; staged through the (idle) ring buffers
     unsigned char* st_k = smem + L::ring_a;
@@ -336,7 +337,7 @@ attn_bwd_dkdv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     __syncthreads();
     store_tile<64, DK, AB_THREADS>(st_k, dk + (tokk * HKV + hkv) * DK, (long)HKV * DK, valid_k, tid);
     store_tile<64, DV, AB_THREADS>(st_v, dv + (tokk * HKV + hkv) * DV, (long)HKV * DV, valid_k, tid);
-    if (tid < G) dnats_part[((long)b * NT + kt) * HQ + hkv * G + tid] = s_dn[tid];
+    if (tid < G) dnats_part[((long)b * NT + kt) * HQ + hkv * G + tid] = (s_dn[tid][0] + s_dn[tid][1]) + (s_dn[tid][2] + s_dn[tid][3]);
 }
 
 template <int DK, int DV>

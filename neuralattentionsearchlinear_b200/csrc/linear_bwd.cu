@@ -22,7 +22,8 @@
 //                            then the l2-norm backward (mixed_attn_gdn.py:273-275).
 //   linear_bwd_dg_kernel     per (batch, head): the scalar chain of the carried decay over skipped chunks and the
 //                            reverse chunk-local cumsum (chunk.py:318-331, src/nats/ops/utils/cumsum.py REVERSED).
-// All products run on mma.sync with bf16 operands and fp32 accumulation.  No atomics on global memory.
+// All products run on mma.sync with bf16 operands and fp32 accumulation.  No atomics on global memory; shared-memory
+// sums either have one writer per slot or exactly two terms, so results are reproducible bit for bit.
 #include "warp_gemm.cuh"
 #include "../../include/natsl_b200.h"
 
@@ -341,8 +342,8 @@ struct StSmem {
     static constexpr int dvs = us + 64 * V * 2;               // dv'
     static constexpr int dos = dvs + 64 * V * 2;
     static constexpr int vs = dos + 64 * V * 2;               // raw v (chunks that do not update the state, GDN)
-    static constexpr int vec = vs + (GDN ? 64 * V * 2 : 0);   // g[64], r[64], red[16]
-    static constexpr int total = vec + (64 + 64 + 16) * 4;
+    static constexpr int vec = vs + (GDN ? 64 * V * 2 : 0);   // g[64], r[64], red[8 warps][2] + red2[2]
+    static constexpr int total = vec + (64 + 64 + 32) * 4;
     static_assert(K * V * 2 >= 64 * K * 2, "the dS tile doubles as an output staging buffer");
 };
 
@@ -407,7 +408,7 @@ linear_bwd_state_kernel(const __nv_bfloat16* __restrict__ kn, const __nv_bfloat1
         s_g[tid] = gcs[(tok0 + min(tid, valid - 1)) * H + h];
         s_r[tid] = 0.f;
     }
-    if (tid < 16) s_red[tid] = 0.f;
+    if (tid < 32) s_red[tid] = 0.f;
     const float car = carry_in[((long)b * NT + c) * H + h];
     const float ec = __expf(car);
     cp_async_wait<0>();
@@ -503,9 +504,9 @@ linear_bwd_state_kernel(const __nv_bfloat16* __restrict__ kn, const __nv_bfloat1
     }
     dd = warp_sum(dd);
     t1 = warp_sum(t1);
-    if (lane == 0) {
-        atomicAdd(&s_red[0], dd);
-        atomicAdd(&s_red[1], t1);
+    if (lane == 0) {                                         // one slot per warp: the sums below have a fixed order
+        s_red[2 * warp] = dd;
+        s_red[2 * warp + 1] = t1;
     }
     __syncthreads();                                         // all products done: k, w, dS tiles become staging buffers
     // ---- per-token decay gradient of the state write, dnats
@@ -516,7 +517,7 @@ linear_bwd_state_kernel(const __nv_bfloat16* __restrict__ kn, const __nv_bfloat1
         if (tid < valid) dkd_out[(tok0 + tid) * H + h] = act ? val : 0.f;
         float dn = (tid < valid) ? s_r[tid] * kd : 0.f;
         dn = warp_sum(dn);
-        if (lane == 0) atomicAdd(&s_red[2], dn);
+        if (lane == 0) s_red[16 + warp] = dn;
     }
     store_acc_bf16<K * 2, NK>(ks_p, acc_k, r0, nk0, lane);
     store_acc_bf16<K * 2, NK>(ws_p, acc_q, r0, nk0, lane);
@@ -530,10 +531,15 @@ linear_bwd_state_kernel(const __nv_bfloat16* __restrict__ kn, const __nv_bfloat1
     }
     if (tid == 0) {
         float* sc = scal + (((long)b * NT + c) * H + h) * 4;
-        const float dn = s_red[2];
-        sc[0] = act ? s_red[0] * __expf(gl + car) : 0.f;     // ddec
+        const float dn = s_red[16] + s_red[17];
+        float dd_tot = 0.f, t1_tot = 0.f;
+        for (int wv = 0; wv < 8; ++wv) {
+            dd_tot += s_red[2 * wv];
+            t1_tot += s_red[2 * wv + 1];
+        }
+        sc[0] = act ? dd_tot * __expf(gl + car) : 0.f;       // ddec
         sc[1] = act ? dn : 0.f;                              // sum of the per-token decay gradients of the write
-        sc[2] = ec * s_red[1];                               // e^{car} <w S, dv'>
+        sc[2] = ec * t1_tot;                                 // e^{car} <w S, dv'>
         dnats_lin[((long)b * NT + c) * H + h] = (slot >= 0) ? dn : 0.f;
     }
 }
@@ -556,8 +562,9 @@ struct InSmem {
     static constexpr int As = hs + (GDN ? 64 * 64 * 2 : 0);   // A fp32 [64][68]
     static constexpr int Xs = As + (GDN ? 64 * LB_A_LD * 4 : 0);
     static constexpr int vec = Xs + (GDN ? 4 * 16 * LB_X_LD * 4 : 0);
-    // g, beta, dg, db, zk, dE, dotq, dotk: 8 x 64 floats, + 16
-    static constexpr int total = vec + (8 * 64 + 16) * 4;
+    // g, beta, zk, dE, dotq, dotk (6 x 64); decay-gradient row sums [2 phases][2 halves][64] and column sums
+    // [2 phases][4 row blocks][64]; dbeta parts [2 halves + value part][64]; + 16
+    static constexpr int total = vec + ((6 + 4 + 8 + 3) * 64 + 16) * 4;
 };
 
 // In-place solve of (I + A)^T X = R for 32 columns [col0, col0+32) of a [64][COLS] bf16 tile by one warp:
@@ -627,13 +634,14 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
     float* Xs = reinterpret_cast<float*>(smem + L::Xs);
     float* s_g = reinterpret_cast<float*>(smem + L::vec);
     float* s_b = s_g + 64;
-    float* s_dg = s_b + 64;
-    float* s_db = s_dg + 64;
-    float* s_zk = s_db + 64;
+    float* s_zk = s_b + 64;
     float* s_dE = s_zk + 64;
     float* s_dotq = s_dE + 64;
     float* s_dotk = s_dotq + 64;
-    float* s_red = s_dotk + 64;
+    float* s_dgr = s_dotk + 64;                              // [phase][half][64]: one writer per slot, fixed summation order
+    float* s_dgc = s_dgr + 4 * 64;                           // [phase][row block][64]
+    float* s_dbp = s_dgc + 8 * 64;                           // [half 0 | half 1 | value part][64]
+    float* s_red = s_dbp + 3 * 64;
 
     load_tile_async<64, K, LB_THREADS>(qns, qn + (tok0 * H + h) * K, (long)H * K, valid, tid);
     load_tile_async<64, K, LB_THREADS>(kns, kn + (tok0 * H + h) * K, (long)H * K, valid, tid);
@@ -655,7 +663,8 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
             bv = beta_dtype == NATSL_DT_F32 ? reinterpret_cast<const float*>(beta)[gi]
                                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(beta)[gi]);
         s_b[tid] = bv;
-        s_dg[tid] = 0.f; s_db[tid] = 0.f; s_zk[tid] = 0.f; s_dE[tid] = 0.f; s_dotq[tid] = 0.f; s_dotk[tid] = 0.f;
+        s_zk[tid] = 0.f; s_dE[tid] = 0.f; s_dotq[tid] = 0.f; s_dotk[tid] = 0.f;
+        for (int i = 0; i < 15; ++i) s_dgr[i * 64 + tid] = 0.f;
     }
     if (tid < 16) s_red[tid] = 0.f;
     cp_async_wait<0>();
@@ -696,15 +705,15 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
             cs0 = colgroup_sum(cs0);
             cs1 = colgroup_sum(cs1);
             if (gq == 0) {
-                atomicAdd(&s_dg[c0 + nt * 8 + qd * 2], -cs0);
-                atomicAdd(&s_dg[c0 + nt * 8 + qd * 2 + 1], -cs1);
+                s_dgc[(0 * 4 + rw) * 64 + c0 + nt * 8 + qd * 2] = -cs0;
+                s_dgc[(0 * 4 + rw) * 64 + c0 + nt * 8 + qd * 2 + 1] = -cs1;
             }
         }
         rs_a = quad_sum(rs_a);
         rs_b = quad_sum(rs_b);
         if (qd == 0) {
-            atomicAdd(&s_dg[ia], rs_a);
-            atomicAdd(&s_dg[ib], rs_b);
+            s_dgr[(0 * 2 + half) * 64 + ia] = rs_a;
+            s_dgr[(0 * 2 + half) * 64 + ib] = rs_b;
         }
         store_acc_bf16<128, 4>(m1_p, dpr, r0, c0, lane);
     }
@@ -786,17 +795,17 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
                 cs0 = colgroup_sum(cs0);
                 cs1 = colgroup_sum(cs1);
                 if (gq == 0) {
-                    atomicAdd(&s_dg[c0 + nt * 8 + qd * 2], -cs0);
-                    atomicAdd(&s_dg[c0 + nt * 8 + qd * 2 + 1], -cs1);
+                    s_dgc[(1 * 4 + rw) * 64 + c0 + nt * 8 + qd * 2] = -cs0;
+                    s_dgc[(1 * 4 + rw) * 64 + c0 + nt * 8 + qd * 2 + 1] = -cs1;
                 }
             }
             rs_a = quad_sum(rs_a); rs_b = quad_sum(rs_b);
             db_a = quad_sum(db_a); db_b = quad_sum(db_b);
             if (qd == 0) {
-                atomicAdd(&s_dg[ia], rs_a);
-                atomicAdd(&s_dg[ib], rs_b);
-                atomicAdd(&s_db[ia], db_a);
-                atomicAdd(&s_db[ib], db_b);
+                s_dgr[(1 * 2 + half) * 64 + ia] = rs_a;
+                s_dgr[(1 * 2 + half) * 64 + ib] = rs_b;
+                s_dbp[half * 64 + ia] = db_a;
+                s_dbp[half * 64 + ib] = db_b;
             }
             store_acc_bf16<128, 4>(m2_p, dar, r0, c0, lane);
         }
@@ -828,7 +837,7 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
                 *pz = z;
 #pragma unroll
                 for (int o = CPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (cc == 0) atomicAdd(&s_db[r], s);
+                if (cc == 0) s_dbp[2 * 64 + r] = s;
             }
         }
     }
@@ -925,10 +934,13 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
         const float dE = s_dE[tid];
         if (tid < valid) {
             const long gi = (tok0 + tid) * H + h;
-            float dgt = s_dg[tid] + dE - dkd[gi];
+            float dgt = (s_dgr[tid] + s_dgr[64 + tid]) +
+                        ((s_dgc[tid] + s_dgc[64 + tid]) + (s_dgc[128 + tid] + s_dgc[192 + tid])) + dE - dkd[gi];
             if (GDN) {
+                dgt += (s_dgr[128 + tid] + s_dgr[192 + tid]) +
+                       ((s_dgc[256 + tid] + s_dgc[320 + tid]) + (s_dgc[384 + tid] + s_dgc[448 + tid]));
                 dgt += s_zk[tid] * s_b[tid] * eg;
-                dbeta[gi] = s_db[tid] + eg * s_zk[tid];
+                dbeta[gi] = (s_dbp[tid] + s_dbp[64 + tid]) + s_dbp[128 + tid] + eg * s_zk[tid];
             }
             dg_tok[gi] = dgt;
         }

@@ -51,21 +51,35 @@ def test_selection_decisions_bit_exact(nat, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_selection_decisions_near_ties(nat, dtype):
-    """Pairs of logits one unit in the last place apart, at many magnitudes, in both orders: whether the rounded
-    probabilities tie (first operation wins) or not is decided identically on the device and in the oracle."""
+    """Pairs of logits one unit in the last place apart, at many magnitudes, in both orders.  Whether the two rounded
+    probabilities tie (then the first operation wins, torch.max) depends on the last-place rounding of the exponential
+    inside softmax, which differs between the CPU and the CUDA math libraries; the reference itself runs this softmax
+    on the device.  So the oracle pins these cases only up to that rounding: every device decision must be one-hot and
+    admissible (the larger logit, or the first operation on a tie of the probabilities), and away from the
+    one-unit-apart cases it is bit-exact (previous test).  In bf16 the rounded probabilities tie the same way on both
+    sides and the decisions are equal."""
     base = torch.cat([torch.linspace(-8, 8, 4001), torch.logspace(-6, 1, 2000), -torch.logspace(-6, 1, 2000)]).to(dtype)
-    up = torch.nextafter(base.float(), torch.full_like(base.float(), 1e9)) if dtype == torch.float32 else None
-    if dtype == torch.bfloat16:
+    if dtype == torch.float32:
+        up = torch.nextafter(base, torch.full_like(base, 1e9))
+    else:
         bits = base.view(torch.int16).int()
         up = torch.where(base >= 0, bits + 1, bits - 1).to(torch.int16).view(torch.bfloat16)
         up = torch.where(base == 0, torch.full_like(base, 1e-30), up)
-    up = up.to(dtype)
     n = base.numel()
     logits = torch.stack([torch.stack([base, up], -1), torch.stack([up, base], -1)], 0).view(2, n, 1, 2)
     logits = torch.cat([logits, logits[:, :1]], 1)             # one more block: the forced last block is not a test case
-    got = _decide_on_device(logits)
-    ref = otab.force_last_block(otab.hard_softmax(logits))
-    assert torch.equal(got.float(), ref.float()), f"{int((got.float() != ref.float()).sum())} decisions differ"
+    got = _decide_on_device(logits).float()[:, :-1]
+    ref = otab.force_last_block(otab.hard_softmax(logits)).float()[:, :-1]
+    assert bool((got.sum(-1) == 1).all()) and set(got.unique().tolist()) <= {0.0, 1.0}
+    larger = logits[:, :-1].float().argmax(-1)
+    picked = got.argmax(-1)
+    assert bool(((picked == larger) | (picked == 0)).all()), "a decision is neither the larger logit nor a tie"
+    if dtype == torch.bfloat16:
+        assert torch.equal(got, ref)
+    else:
+        # the oracle (CPU softmax) is admissible in the same sense; the two may differ only on these near-ties
+        picked_ref = ref.argmax(-1)
+        assert bool(((picked_ref == larger) | (picked_ref == 0)).all())
 
 
 # ------------------------------------------------------------------------------------------------ chunk-inference states
