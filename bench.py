@@ -551,6 +551,161 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------- model-level workloads (optional)
+MODEL_CFGS = {
+    # 24 layers, hidden 1024, 16 heads of dim 64, SwiGLU 2816, vocab 32000, block 64; global batch 16 x 4096 (prefill)
+    "model_prefill": dict(hidden_size=1024, head_dim=64, num_heads=16, num_attn_heads=16, global_batch=16, per_gpu_batch=None),
+    # 1.3B: 24 layers, hidden 2048, 16 heads of dim 128, SwiGLU 5632; 8 x 4096 tokens per GPU, forward + backward
+    "model_fwdbwd": dict(hidden_size=2048, head_dim=128, num_heads=16, num_attn_heads=16, global_batch=None, per_gpu_batch=8),
+}
+
+
+def run_model(args, rank: int, world: int, local_rank: int):
+    """Decoder model around the NAtSL-GDN layer, random init (seed 0), uniform random token ids.
+    model_prefill: bf16 forward under eval, global batch 16 split over the ranks (strong scaling, no collective).
+    model_fwdbwd: forward + backward of the next-token loss under train, 8 sequences per GPU (weak scaling), gradients
+    averaged with torch's bucketed NCCL all-reduce overlapped with the backward pass (DistributedDataParallel)."""
+    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200.models import (NeuralAttentionSearchLineraAttnGDNConfig,
+                                                         NeuralAttentionSearchLinearAttnGDNForCausalLM)
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = init_process_group_quiet(dev) if world > 1 else None
+    mc = MODEL_CFGS[args.workload]
+    train = args.workload == "model_fwdbwd"
+    T = 4096
+    layers = args.layers or 24
+    cfg = NeuralAttentionSearchLineraAttnGDNConfig(
+        hidden_size=mc["hidden_size"], expand_v=1.0, head_dim=mc["head_dim"], num_heads=mc["num_heads"],
+        num_attn_heads=mc["num_attn_heads"], num_hidden_layers=layers, vocab_size=32000, nats_block_size=64,
+        ops_for_incomplete_chunks="all", gdn_layers=[], attn_apply_pos_encoding=False, attn_qk_norm=True,
+        attn_with_short_conv=True, decay_for_non_gdn_blocks=True, norm_eps=1e-6)
+    torch.manual_seed(0)
+    model = NeuralAttentionSearchLinearAttnGDNForCausalLM(cfg).to(dev).bfloat16()
+    n_params = sum(p.numel() for p in model.parameters())
+    if train:
+        B = mc["per_gpu_batch"]
+        model.train()
+        net = model
+        if dist is not None:
+            net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+    else:
+        assert mc["global_batch"] % world == 0, "the global batch of 16 must divide over the ranks"
+        B = mc["global_batch"] // world
+        model.eval()
+        net = model
+    gen = torch.Generator().manual_seed(100 + rank)
+    ids_host = torch.randint(0, 32000, (B, T), generator=gen).pin_memory()
+    ids = ids_host.to(dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def step(x):
+        if train:
+            net.zero_grad(set_to_none=True)
+            out = net(input_ids=x, labels=x)
+            out["loss"].backward()
+            return out["loss"].detach()
+        with torch.no_grad():
+            return net(input_ids=x, logits_to_keep=1)["logits"]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    clocks = ClockSampler(vis.split(",")[local_rank].strip() if vis else local_rank)
+    if rank == 0:
+        clocks.start()
+    for _ in range(max(3, args.warmup)):
+        res = step(ids)
+    barrier()
+    if rank == 0:
+        clocks.rows.clear()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        res = step(ids)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # end to end: the token ids come from pinned host memory and the result (loss / last-token logits) goes back
+    host_out = torch.empty_like(res, device="cpu").pin_memory()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record(stream)
+    for _ in range(args.steps):
+        x = ids_host.to(dev, non_blocking=True)
+        host_out.copy_(step(x), non_blocking=True)
+    e3.record(stream)
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = (float(x) for x in t.tolist())
+    clk = clocks.stop() if rank == 0 else None
+    # share of the step spent in the hybrid attention op: the op alone on one layer's shapes, times the layer count
+    import neuralattentionsearchlinear_b200 as nat
+    H, D = mc["num_heads"], mc["head_dim"]
+    g_ = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *sh: torch.randn(*sh, device=dev, generator=g_).bfloat16()
+    q, k, v = rnd(B, T, H, D), rnd(B, T, H, D), rnd(B, T, H, D)
+    gdec = -torch.nn.functional.softplus(torch.randn(B, T, H, device=dev, generator=g_))
+    beta = torch.rand(B, T, H, device=dev, generator=g_).bfloat16()
+    types = torch.zeros(B, T // 64, H, 2, device=dev)
+    types[..., 1] = 1
+    types[:, ::4, :, 0], types[:, ::4, :, 1] = 1, 0
+    types[:, -1] = 1
+    if train:
+        q, k, v, gdec, beta = (x.requires_grad_(True) for x in (q, k, v, gdec, beta))
+
+    def op_step():
+        o_l, o_a, _ = nat.nats_mixed_attn_gdn(q, k, v, q, k, v, None, gdec, beta, types, None, nats_block_size=64,
+                                              ops_for_incomplete_chunks="all", decay_for_non_gdn_blocks=True)
+        if train:
+            (o_l.float().sum() + o_a.float().sum()).backward()
+
+    for _ in range(3):
+        op_step()
+    torch.cuda.synchronize(dev)
+    e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e4.record(stream)
+    for _ in range(5):
+        op_step()
+    e5.record(stream)
+    torch.cuda.synchronize(dev)
+    op_ms = e4.elapsed_time(e5) / 5
+    status = _lib.load().natsl_device_status()
+    if rank == 0:
+        ms_step = ms / args.steps
+        tokens = world * B * T
+        # dense FLOPs per token of the matrix products outside the hybrid op (projections, MLP, LM head for training)
+        hs, inter = mc["hidden_size"], 256 * ((int(mc["hidden_size"] * 4 * 2 / 3) + 255) // 256)
+        per_layer = 2 * hs * (3 * hs + hs + hs) + 2 * 3 * hs * inter
+        dense = layers * per_layer + (2 * hs * 32000 if train else 0)
+        mult = 3 if train else 1
+        print(json.dumps({
+            "metric": "train_tokens_per_s" if train else "prefill_tokens_per_s", "value": tokens / (ms_step * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak" if train else "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (uniform random token ids, random-init weights, seed 0)",
+            "config": {"workload": f"natsl_gdn_decoder {'fwd+bwd' if train else 'prefill'} layers={layers} hidden={hs} "
+                                   f"heads={H}x{D} vocab=32000 block=64 T=4096", "per_gpu_batch": B, "parameters": n_params,
+                       "parallelism": (f"data-parallel x{world}" + (", bucketed NCCL gradient all-reduce overlapped with backward"
+                                                                   if train and world > 1 else ""))},
+            "clocks": clk,
+            "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8,
+                    "d2h_bytes_per_step": host_out.numel() * host_out.element_size(), "ms_per_step": ms_e2e / args.steps},
+            "hybrid_attention_op": {"ms_per_layer": op_ms, "share_of_step": layers * op_ms / ms_step,
+                                    "note": "the op alone (forward" + (" + backward" if train else "") + ") on one layer's shapes x layers"},
+            "dense_matmul_tflops_outside_op": mult * dense * tokens / world / (max(ms_step - layers * op_ms, 1e-6) * 1e-3) / 1e12,
+            "device_status": status}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -572,9 +727,11 @@ def main():
                          "reading the block counts back every step")
     ap.add_argument("--sp-plain-op", action="store_true",
                     help="mamba_long on one GPU through nats_mixed_attn_mamba (no sub-segment split, one stream)")
-    ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long"],
+    ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long", "model_prefill", "model_fwdbwd"],
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
-                         "Mamba2 layer, sequence-parallel over the ranks")
+                         "Mamba2 layer, sequence-parallel over the ranks; model_prefill / model_fwdbwd: the 24-layer "
+                         "decoder models (prefill of 16 x 4096 tokens; forward + backward of 8 x 4096 tokens per GPU)")
+    ap.add_argument("--layers", type=int, default=0, help="model workloads: number of layers (default 24)")
     args = ap.parse_args()
     CFG["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
@@ -585,6 +742,8 @@ def main():
         run_reference(args, rank)
     elif args.workload == "mamba_long":
         run_mamba_long(args, rank, world, local_rank)
+    elif args.workload in MODEL_CFGS:
+        run_model(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
