@@ -38,6 +38,13 @@ CFG = dict(B=8, T=4096, H=16, K=128, V=128, nbs=64, p_attn=0.25)
 WORKLOAD = "natsl_gdn_layer_fwd B={B} T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25"
 
 
+def layer_config(world: int, B: int) -> dict:
+    """The ``config`` object of the JSON line: the same for both arms (the reference arm times the same workload)."""
+    return {"workload": WORKLOAD.format(B=B), "per_gpu_batch": B,
+            "parallelism": f"replicas x{world} (batch sharded, no collective)",
+            "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"}
+
+
 def init_process_group_quiet(dev):
     """NCCL process group; whatever the libraries print while the communicator comes up (NCCL's version banner) goes
     to stderr, so that stdout carries the one JSON line only."""
@@ -185,8 +192,8 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": "prefill_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-        "config": {"workload": WORKLOAD.format(B=8), "note": "reference algorithm restated in PyTorch on host cores "
-                   "(the reference's own implementation is Triton-only)"},
+        "config": layer_config(args.gpus, CFG["B"]),
+        "note": "reference algorithm restated in PyTorch on host cores (the reference's own implementation is Triton-only)",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -247,10 +254,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- device-resident throughput
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = _lib.kernel_launches()
     e0.record(stream)
     for _ in range(args.steps):
         out = step(d)
     e1.record(stream)
+    gpu_launches = _lib.kernel_launches() - launches_before      # kernels of this library launched in the timed region
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     if rank == 0 and len(clocks.rows) < 3 and args.min_warm_seconds > 0:
@@ -317,7 +326,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- end to end: host (pinned) inputs -> device -> op -> host outputs, every step
     h2d = sum(t.numel() * t.element_size() for t in pinned.values())
     d2h = 2 * B * T * H * V * 2 + B * H * K * V * 4
-    e2e_steps = max(4, min(args.steps, 10))
+    e2e_steps = args.steps
 
     # Every step copies its inputs from pinned host memory and its outputs back; the copies of neighbouring steps
     # overlap the compute (PCIe is full duplex): an upload stream, the compute stream and a download stream, two
@@ -367,6 +376,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
     e2e_value = world * B * T / (e2e_ms * 1e-3)
 
+    # ---- N > 1: the long-context layer split over the ranks (the configuration the multi-GPU target is about), and
+    # the same layer on one GPU, measured in this run: every rank runs the one-GPU case side by side on its own GPU
+    sp_info = None
+    if dist is not None and not args.no_sp:
+        lin_group = dist.new_group()
+        solo = None
+        for r in range(world):
+            gr = dist.new_group([r])
+            if r == rank:
+                solo = gr
+        r_n = mamba_long_measure(args, rank, world, dev, group=None, lin_group=lin_group, plan=True, parity=True)
+        r_1 = mamba_long_measure(args, 0, 1, dev, group=solo, lin_group=None, plan=False, parity=False)
+        one = max_over_ranks(r_1["ms_per_step"])
+        sp_info = {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 p_softmax=0.10",
+                   "scaling": "strong", "n_gpus": world, "ms_per_step": r_n["ms_per_step"], "tokens_per_s": r_n["tokens_per_s"],
+                   "one_gpu_ms_per_step": one, "speedup_vs_one_gpu": one / r_n["ms_per_step"], "launch": r_n["launch"],
+                   "layout": r_n["layout"], "host_issue_ms_per_step": r_n["host_issue_ms_per_step"],
+                   "parity": r_n.get("parity"), "device_status": _lib.load().natsl_device_status()}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -382,10 +409,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     n_tok = B * T * H
     frac_lin = float(host["types"][..., 1].float().mean())
     state_bytes = B * NT * H * K * V * 2
-    # ncu dram__bytes_read+write per launch, captured at B=4 (profiles/ncu_full_hot_kernels_B4.md), scaled by B/4:
-    # traffic grows in proportion to the batch (independent (batch, head) units)
-    ncu_traffic_b4 = {"attn_fwd": 249.1e6, "gdn_prep": 330.3e6, "scan_fwd_h": 259.5e6, "out_fwd_o": 460.4e6,
-                      "walk_fused": 357.7e6}
+    # DRAM bytes per launch from a profiler capture at a smaller batch (tracked file; it names the build it was taken
+    # from), scaled by the batch: traffic grows in proportion to the independent (batch, head) units
+    traffic_path = os.path.join(ROOT, "profiles", "dram_traffic_per_launch.json")
+    ncu_traffic, ncu_batch = {}, 1
+    if os.path.exists(traffic_path):
+        tr = json.load(open(traffic_path))
+        ncu_traffic, ncu_batch = tr["bytes_per_launch"], tr["batch"]
     # the step runs tables, attn_fwd, gdn_prep, walk_fused; scan_fwd_h + out_fwd_o are the two-kernel path the fused
     # walk replaces at this shape (still used for other head dims / block sizes) and are timed for comparison
     in_step = ("attn_fwd", "gdn_prep", "walk_fused")
@@ -405,7 +435,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         else:
             ach, peak, unit = amount / sec / 1e9, peak_bw, "GB/s"
         roofs[n] = {"kernel": kname, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-                    "traffic": (ncu_traffic_b4[n] * B / 4.0) if ncu_traffic_b4[n] else None, "algorithmic_per_launch": amount,
+                    "traffic": (ncu_traffic[n] * B / ncu_batch) if ncu_traffic.get(n) else None, "algorithmic_per_launch": amount,
                     "ms_per_launch": kernel_ms[n]}
     dom = max(in_step, key=lambda n: kernel_ms[n])
     roofline = dict(roofs[dom], peak_source=peak_src, dominant_stage=dom)
@@ -419,15 +449,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "metric": "prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, generated on the host)",
-        "config": {"workload": WORKLOAD.format(B=B), "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)",
-                   "l2": "inputs and intermediates (>0.9 GB per step) exceed the 126 MB L2; no explicit flush"},
-        "clocks": clk, "gpu_launches": 5 * args.steps,
+        "config": layer_config(world, B),
+        "clocks": clk, "gpu_launches": gpu_launches,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "pipelining": "uploads, compute and downloads of neighbouring steps overlap (three streams, two buffer sets)"},
         "kernel_ms": kernel_ms, "roofline": roofline, "roofline_all": roofs,
         "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": cpu_sample},
+        "sp_long_context": sp_info,
         "parity": {"max_abs_err_o_gdn": err_l, "max_abs_err_o_attn": err_a, "max_abs_ref": mag, "tolerance": "rtol=atol=1e-2",
                    "sample": f"sequence 0, heads 0..{hs - 1}, device outputs of the timed step vs the fp32 CPU oracle"},
     }
@@ -440,47 +470,66 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 MAMBA_LONG = dict(T=65536, H=32, K=128, V=64, nbs=256, p_attn=0.10)
 
 
-def run_mamba_long(args, rank: int, world: int, local_rank: int):
-    """NAtSL-Mamba2 hybrid layer, B=1, T=65536, H=32, state dim 128, head dim 64, block 256, ~10 % softmax blocks,
-    sequence-parallel over the ranks (strong scaling: the sequence is split, one contiguous segment per rank)."""
-    import neuralattentionsearchlinear_b200 as nat
-    from neuralattentionsearchlinear_b200 import _lib
-    from neuralattentionsearchlinear_b200.sequence_parallel import nats_mixed_attn_mamba_sp
-    _lib.load()
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    dist = None
-    if world > 1:
-        dist = init_process_group_quiet(dev)
+def mamba_long_segment(sid: int, n_glob: int, L: int):
+    """Host tensors of segment ``sid`` of the long-context input, generated from the segment's own seed."""
     c = MAMBA_LONG
-    T, H, K, V, nbs = c["T"], c["H"], c["K"], c["V"], c["nbs"]
-    from neuralattentionsearchlinear_b200.sequence_parallel import segment_ids
-    layout = args.sp_layout if world > 1 else "contiguous"
-    ids = segment_ids(rank, world, layout)
-    n_glob = world * len(ids)
-    L = T // n_glob
+    H, K, V, nbs = c["H"], c["K"], c["V"], c["nbs"]
     A = -torch.exp(torch.rand(H, generator=torch.Generator().manual_seed(4)) * torch.log(torch.tensor(16.0)))
     shift = (2.0 ** 0.5) * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(c["p_attn"])).item()
-    parts = {n: [] for n in ("q", "k", "v", "g", "types")}
-    for sid in ids:                                     # every segment is generated from its own seed
-        gen = torch.Generator().manual_seed(4000 + sid)
-        x = torch.randn(1, L, H, V, generator=gen)
-        dt = torch.nn.functional.softplus(torch.randn(1, L, H, generator=gen) - 2.0)
-        parts["k"].append((torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16())
-        parts["q"].append((torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16())
-        parts["v"].append((x * dt[..., None]).bfloat16())
-        parts["g"].append(A.view(1, 1, H) * dt)
-        logits = torch.randn(1, L // nbs, H, 2, generator=gen)
-        logits[..., 0] += shift
-        ty = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
-        if sid == n_glob - 1:
-            ty[:, -1] = 1
-        parts["types"].append(ty)
-    q, k, v, g, types = (torch.cat(parts[n], 1).to(dev) for n in ("q", "k", "v", "g", "types"))
-    stream = torch.cuda.current_stream(dev)
+    gen = torch.Generator().manual_seed(4000 + sid)
+    x = torch.randn(1, L, H, V, generator=gen)
+    dt = torch.nn.functional.softplus(torch.randn(1, L, H, generator=gen) - 2.0)
+    k = (torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16()
+    q = (torch.randn(1, L, H, K, generator=gen) * K ** -0.5).bfloat16()
+    logits = torch.randn(1, L // nbs, H, 2, generator=gen)
+    logits[..., 0] += shift
+    ty = torch.zeros_like(logits).scatter_(-1, logits.softmax(-1).max(-1, keepdim=True)[1], 1.0)
+    if sid == n_glob - 1:
+        ty[:, -1] = 1
+    return dict(q=q, k=k, v=(x * dt[..., None]).bfloat16(), g=A.view(1, 1, H) * dt, types=ty)
 
+
+def mamba_long_parity(o_m, o_a, ids, n_glob: int, L: int, heads: int = 2, win: int = 128):
+    """Rank 0: regenerates the whole sequence on the host (every segment from its seed), evaluates the oracle for
+    ``heads`` heads, and compares one ``win``-token window at the start of this rank's last local segment (linear branch:
+    chunk form over the whole sequence; softmax branch: masked SDPA for the window's queries against all keys)."""
+    from oracle import attn as oattn
+    from oracle import gdn as ogdn
+    c = MAMBA_LONG
+    T, K, nbs = c["T"], c["K"], c["nbs"]
+    segs = [mamba_long_segment(sid, n_glob, L) for sid in range(n_glob)]
+    cat = lambda n: torch.cat([sg[n][:, :, :heads] for sg in segs], 1)
+    q, k, v = (cat(n).float().contiguous() for n in ("q", "k", "v"))
+    g, types = cat("g").contiguous(), cat("types").contiguous()
+    o_ref, _ = ogdn.linear_chunk(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=True, use_l2norm=False,
+                                 rule="mamba", reference_trailing_carry=False)
+    t0 = ids[-1] * L                                              # global position of the window
+    loc = (len(ids) - 1) * L                                      # its position in this rank's tensors
+    mask = oattn.attn_mask_rows(types[..., 0], T, nbs, heads, t0, t0 + win)
+    oa_ref, _ = oattn.attn_sdpa(q[:, t0:t0 + win], k, v, mask, K ** -0.5)
+    err_l = float((o_m[:, loc:loc + win, :heads].float().cpu() - o_ref[:, t0:t0 + win]).abs().max())
+    err_a = float((o_a[:, loc:loc + win, :heads].float().cpu() - oa_ref).abs().max())
+    mag = float(max(o_ref[:, t0:t0 + win].abs().max(), oa_ref.abs().max()))
+    return {"max_abs_err_o_mamba": err_l, "max_abs_err_o_attn": err_a, "max_abs_ref": mag, "tolerance": "rtol=atol=1e-2",
+            "sample": f"tokens {t0}..{t0 + win - 1}, heads 0..{heads - 1}, device outputs vs the fp32 CPU oracle over the whole sequence"}
+
+
+def mamba_long_measure(args, rank: int, world: int, dev, group=None, lin_group=None, plan: bool = True,
+                       parity: bool = True):
+    """One measurement of the long-context NAtSL-Mamba2 layer (B=1, T=65536, H=32, state dim 128, head dim 64, block 256,
+    ~10 % softmax blocks) split over the ``world`` ranks of ``group``; world = 1 runs the same op on one GPU (the
+    recurrence cut into parallel sub-segments).  -> dict(ms_per_step, host_issue_ms_per_step, launch, parity (rank 0))."""
+    import neuralattentionsearchlinear_b200 as nat
     from neuralattentionsearchlinear_b200 import sequence_parallel as sp
-    lin_group = dist.new_group() if dist is not None else None      # own communicator for the state exchange
+    c = MAMBA_LONG
+    T, H, K, V, nbs = c["T"], c["H"], c["K"], c["V"], c["nbs"]
+    layout = args.sp_layout if world > 1 else "contiguous"
+    ids = sp.segment_ids(rank, world, layout)
+    n_glob = world * len(ids)
+    L = T // n_glob
+    segs = [mamba_long_segment(sid, n_glob, L) for sid in ids]
+    q, k, v, g, types = (torch.cat([sg[n] for sg in segs], 1).to(dev) for n in ("q", "k", "v", "g", "types"))
+    stream = torch.cuda.current_stream(dev)
     kv_cap = None
 
     def step():
@@ -488,64 +537,80 @@ def run_mamba_long(args, rank: int, world: int, local_rank: int):
             return nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5, nats_block_size=nbs,
                                              ops_for_incomplete_chunks="all", output_final_state_mamba=True,
                                              decay_for_non_mamba_blocks=True)
-        return nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
-                                        decay_for_non_mamba_blocks=True, layout=layout,
-                                        linear_splits=args.sp_linear_splits or None, kv_capacity=kv_cap,
-                                        linear_group=lin_group)
+        return sp.nats_mixed_attn_mamba_sp(q, k, v, q, k, v, g, types, nats_block_size=nbs, scale_attn=K ** -0.5,
+                                           decay_for_non_mamba_blocks=True, layout=layout,
+                                           linear_splits=args.sp_linear_splits or None, kv_capacity=kv_cap, group=group,
+                                           linear_group=lin_group)
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
+        if world > 1:
+            torch.distributed.barrier(group)
         torch.cuda.synchronize(dev)
 
     for _ in range(max(3, args.warmup)):
-        step()
+        out = step()
     barrier()
     run_step, mode = step, "eager, gather capacity read back every step (one host synchronisation)"
-    if args.sp_fixed_capacity:
+    if args.sp_fixed_capacity and world > 1:
         # gather capacity fixed to the exact maxima of this input (read back by the warm-up steps): no host read
         kv_cap = sp.last_kv_capacity
         mode = "eager, caller-given gather capacity (no host synchronisation)"
         for _ in range(3):
-            step()
+            out = step()
         barrier()
-    if args.sp_plan and world > 1:
-        # plan / replay: the compute stages replay from CUDA graphs, the five all-gathers stay eager between them
-        plan = sp.GraphedMambaSP(q, k, v, q, k, v, g, types, kv_capacity=sp.last_kv_capacity, nats_block_size=nbs,
-                                 scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
-                                 linear_splits=args.sp_linear_splits or None, linear_group=lin_group,
-                                 gather_under_linear={"auto": None, "gather-under-linear": True,
-                                                      "branches-side-by-side": False}[args.sp_plan_order])
-        plan.capture()
-        run_step = plan.run
-        mode = ("plan: compute replayed from four CUDA graphs, eager NCCL all-gathers between them, "
-                + ("key/value gather under the linear branch" if plan.gather_under_linear else "branches side by side"))
+    if plan and world > 1:
+        # plan / replay: the compute stages replay from CUDA graphs, the all-gathers stay eager between them
+        pl = sp.GraphedMambaSP(q, k, v, q, k, v, g, types, kv_capacity=sp.last_kv_capacity, nats_block_size=nbs,
+                               scale_attn=K ** -0.5, decay_for_non_mamba_blocks=True, layout=layout,
+                               linear_splits=args.sp_linear_splits or None, group=group, linear_group=lin_group,
+                               gather_under_linear={"auto": None, "gather-under-linear": True,
+                                                    "branches-side-by-side": False}[args.sp_plan_order])
+        pl.capture()
+        run_step = pl.run
+        mode = ("plan: compute replayed from CUDA graphs, eager NCCL all-gathers between them, "
+                + ("key/value gather under the linear branch" if pl.gather_under_linear else "branches side by side"))
         for _ in range(3):
-            run_step()
+            out = run_step()
         barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_host0 = time.perf_counter()
     e0.record(stream)
     for _ in range(args.steps):
-        run_step()
+        out = run_step()
     e1.record(stream)
     host_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps      # host time to issue one step
     barrier()
     ms = e0.elapsed_time(e1)
-    if dist is not None:
+    if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
         ms = float(t.item())
-    ms_step = ms / args.steps
+    res = {"ms_per_step": ms / args.steps, "tokens_per_s": T / (ms / args.steps * 1e-3), "host_issue_ms_per_step": host_ms,
+           "launch": mode, "layout": layout}
+    if parity and rank == 0:
+        res["parity"] = mamba_long_parity(out[0], out[1], ids, n_glob, L)
+    return res
+
+
+def run_mamba_long(args, rank: int, world: int, local_rank: int):
+    """``--workload mamba_long``: the long-context layer, sequence-parallel over the ranks (strong scaling)."""
+    from neuralattentionsearchlinear_b200 import _lib
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = init_process_group_quiet(dev) if world > 1 else None
+    lin_group = dist.new_group() if dist is not None else None      # own communicator for the state exchange
+    res = mamba_long_measure(args, rank, world, dev, group=None, lin_group=lin_group, plan=args.sp_plan)
     status = _lib.load().natsl_device_status()
     if rank == 0:
-        print(json.dumps({"metric": "prefill_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-                          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        print(json.dumps({"metric": "prefill_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": res["ms_per_step"],
                           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                           "data": "synthetic (seeded, generated per rank)",
                           "config": {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 "
-                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({layout} segments)", "launch": mode},
-                          "host_issue_ms_per_step": host_ms,
+                                     "p_softmax=0.10", "parallelism": f"sequence-parallel x{world} ({res['layout']} segments)",
+                                     "launch": res["launch"]},
+                          "host_issue_ms_per_step": res["host_issue_ms_per_step"], "parity": res.get("parity"),
                           "device_status": status}))
     if dist is not None:
         dist.destroy_process_group()
@@ -731,6 +796,8 @@ def main():
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
                          "Mamba2 layer, sequence-parallel over the ranks; model_prefill / model_fwdbwd: the 24-layer "
                          "decoder models (prefill of 16 x 4096 tokens; forward + backward of 8 x 4096 tokens per GPU)")
+    ap.add_argument("--no-sp", action="store_true",
+                    help="gdn_layer with N > 1: leave out the sequence-parallel long-context measurement (sp_long_context)")
     ap.add_argument("--layers", type=int, default=0, help="model workloads: number of layers (default 24)")
     args = ap.parse_args()
     CFG["B"] = args.batch

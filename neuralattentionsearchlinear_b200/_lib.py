@@ -81,9 +81,22 @@ def load() -> C.CDLL:
     return lib
 
 
+# kernels one successful call of an entry point launches (for launch accounting; entry points not listed launch one)
+KERNELS_PER_CALL = {"natsl_build_tables": 2, "natsl_attn_bwd": 2, "natsl_gdn_fwd_noalloc": 3, "natsl_abi_version": 0,
+                    "natsl_device_status": 0}
+_launches = 0
+
+
+def kernel_launches() -> int:
+    """Number of kernels this process has launched through ``call`` so far."""
+    return _launches
+
+
 def call(name: str, *args) -> None:
+    global _launches
     lib = load()
     status = getattr(lib, name)(*args)
+    _launches += KERNELS_PER_CALL.get(name, 1)
     if status != 0:
         raise NatslError(f"{name} failed with status {status}: {lib.natsl_last_error().decode()}")
 
