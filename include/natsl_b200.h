@@ -58,6 +58,11 @@ int natsl_abi_version(void);
  * (natsl_pack_selected_pairs).  Non-zero means the outputs of the kernels since the last call are invalid. */
 int natsl_device_status(void);
 
+/* Diagnostic: launches one warp that waits, with the kernels' bounded-wait loop and a limit of `polls` polls, on a
+ * barrier nobody arrives at.  The wait runs out, the kernel returns, and natsl_device_status() then reads 1 (and
+ * clears it).  Shows that an expired wait is reported and leaves the context usable.  No reference counterpart. */
+int natsl_bounded_wait_selftest(int polls, void* stream);
+
 /* Selection tables from the op types [B,TN,HN,2] (column 0 softmax, column 1 linear).
  * Replaces: round / index sort / block counts, src/nats/ops/mixed_ops/mixed_attn_gdn.py:88-100;
  * prepare_nats_block_indices src/nats/ops/nats_util.py:6-32; prepare_nats_chunk_offsets :35-64;
@@ -171,6 +176,18 @@ int natsl_linear_recurrent_fwd(int rule, int dtype, const void* q, const void* k
                                const void* beta, const int32_t* types_i, const float* h0, void* o, float* ht,
                                float* hstart, int B, int T, int H, int HN, int K, int V, int nbs, float scale,
                                int flags, int use_l2norm, void* stream);
+/* Decoding step of the linear branch: T new tokens (T < nbs typically 1) continue a block that already holds t_off
+ * tokens.  h_cur = current state, h_start = state at the start of the current block, gsum [B,H] = log decay of the
+ * block so far (all fp32); types_i [B, cdiv(t_off + T, nbs), HN, 2] are the types of the blocks these tokens touch,
+ * read only where a block ends inside the call.  Outputs: o [B,T,H,V], h_cur_out, h_start_out (may alias the inputs'
+ * buffers only if distinct tensors are not needed; each thread reads its elements before writing them).  The caller
+ * keeps gsum (adds the new tokens' g, resets it where a block ends).
+ * Replaces: fused_recurrent_gated_delta_rule_fwd_nats_kernel with initial_state / initial_state_current / g_cumsum /
+ * n_tokens_in_current_block, src/nats/ops/gated_delta_rule/fused_recurrent.py:28-358 (Mamba2: src/nats/ops/mamba/fused_recurrent.py:28-322). */
+int natsl_linear_recurrent_step(int rule, int dtype, const void* q, const void* k, const void* v, const float* g,
+                                const void* beta, const int32_t* types_i, const float* h_cur, const float* h_start,
+                                const float* gsum, int t_off, void* o, float* h_cur_out, float* h_start_out, int B, int T,
+                                int H, int HN, int K, int V, int nbs, float scale, int flags, int use_l2norm, void* stream);
 int natsl_attn_fwd_fp32(int dtype, const void* q, const void* k, const void* v, const int32_t* types_i, void* o,
                         float* lse, int B, int T, int HQ, int HKV, int HN, int DK, int DV, int nbs, float scale,
                         int flags, void* stream);
@@ -272,6 +289,37 @@ int natsl_linear_bwd_dg(const float* dg_tok, const float* scal, const int32_t* t
 int natsl_norm_gate_mix_bwd(const void* x1, const void* x2, const void* g, const void* xw, int xw_dtype, const void* w1,
                             const void* w2, int w_dtype, const void* dy, void* dx1, void* dx2, void* dg, float* dxw,
                             float* dw_part, int n_part, long rows, int D, float eps, int activation, void* stream);
+
+/* ---- layer steps around the hybrid attention op (bandwidth kernels; bf16 tensors, fp32 math) ------------------- */
+
+/* Short causal depthwise convolution over time + SiLU: x, y [B,T,D]; w [D,W] (W = 4); bias [D] or NULL; silu 0/1.
+ * y[b,t,d] = act(bias[d] + sum_j w[d,j] x[b,t-(W-1)+j,d]).  Backward: dx [B,T,D] and per-(batch, token range)
+ * partial sums dw_part [B*cdiv(T,span), D, W+1] fp32 of the weight (columns 0..W-1) and bias (column W) gradients,
+ * which the caller adds up.
+ * Replaces: fla ShortConvolution as used at src/nats/layers/natsl_attn_gdn.py:329-348, 430-447. */
+int natsl_short_conv_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int D, int W, int silu,
+                         void* stream);
+int natsl_short_conv_bwd(const void* x, const void* w, const void* bias, const void* dy, void* dx, float* dw_part, int B,
+                         int T, int D, int W, int silu, int span, void* stream);
+
+/* RMSNorm over rows of D (64 ... 2048) elements, optionally fused with a residual add in front of it:
+ * s = x (+ res), y = s * rsqrt(mean(s^2) + eps) * w; sum_out (or NULL) receives s.  Backward: dx = gradient w.r.t. s
+ * (+ dadd, the gradient arriving at s from elsewhere, or NULL) and dw_part [n_part, D] fp32 per-CTA partial sums.
+ * Replaces: fla RMSNorm (src/nats/layers/natsl_attn_gdn.py:233-235, 504-505; the fused pre-norm residual at
+ * src/nats/models/natsl_attn_gdn/modeling_natsl_attn_gdn.py:138-139). */
+int natsl_rmsnorm_fwd(const void* x, const void* res, const void* w, int w_dtype, void* y, void* sum_out, long rows, int D,
+                      float eps, void* stream);
+int natsl_rmsnorm_bwd(const void* s, const void* w, int w_dtype, const void* dy, const void* dadd, void* dx, float* dw_part,
+                      int n_part, long rows, int D, float eps, void* stream);
+
+/* SwiGLU: y = silu(a) * b over n elements (a multiple of 8); backward da, db.
+ * Replaces: the activation of fla GatedMLP, src/nats/models/natsl_attn_gdn/modeling_natsl_attn_gdn.py:111-117. */
+int natsl_swiglu_fwd(const void* a, const void* b, void* y, long n, void* stream);
+int natsl_swiglu_bwd(const void* a, const void* b, const void* dy, void* da, void* db, long n, void* stream);
+
+/* Mean of x [B,T,D] over each block of nbs tokens (the last block may be shorter): y [B,cdiv(T,nbs),D].
+ * Replaces: fla mean_pooling, src/nats/layers/natsl_attn_gdn.py:412-416 (src/nats/ops/utils/pooling.py:26-57). */
+int natsl_block_mean(const void* x, void* y, int B, int T, int D, int nbs, void* stream);
 
 /* Gated-delta-rule branch forward (prep -> recurrence -> output) that allocates nothing and asks
  * the caller for no intermediate buffers: they live in a fixed NATSL_NOALLOC_SCRATCH_BYTES array

@@ -22,6 +22,7 @@ _p, _i, _f = C.c_void_p, C.c_int, C.c_float
 PROTOTYPES = {
     "natsl_abi_version": [],
     "natsl_device_status": [],
+    "natsl_bounded_wait_selftest": [_i, _p],
     "natsl_build_tables": [_p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     "natsl_attn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_attn_fwd_ex": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
@@ -40,6 +41,8 @@ PROTOTYPES = {
     "natsl_gdn_chunk_prep_ex": [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "natsl_gdn_walk_fused": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_linear_recurrent_fwd": [_i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "natsl_linear_recurrent_step": [_i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
+                                    _i, _i, _p],
     "natsl_attn_fwd_fp32": [_i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_norm_gate_mix": [_p, _p, _p, _p, _i, _p, _p, _i, _p, C.c_long, _i, _f, _i, _p],
     "natsl_attn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
@@ -51,6 +54,13 @@ PROTOTYPES = {
                                _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "natsl_linear_bwd_dg": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
     "natsl_norm_gate_mix_bwd": [_p, _p, _p, _p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, C.c_long, _i, _f, _i, _p],
+    "natsl_short_conv_fwd": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _p],
+    "natsl_short_conv_bwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "natsl_rmsnorm_fwd": [_p, _p, _p, _i, _p, _p, C.c_long, _i, _f, _p],
+    "natsl_rmsnorm_bwd": [_p, _p, _i, _p, _p, _p, _p, _i, C.c_long, _i, _f, _p],
+    "natsl_swiglu_fwd": [_p, _p, _p, C.c_long, _p],
+    "natsl_swiglu_bwd": [_p, _p, _p, _p, _p, C.c_long, _p],
+    "natsl_block_mean": [_p, _p, _i, _i, _i, _i, _p],
     "natsl_gdn_fwd_noalloc": [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20

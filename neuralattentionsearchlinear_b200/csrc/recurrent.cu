@@ -33,7 +33,12 @@ linear_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
                         const float* __restrict__ g, const T* __restrict__ beta, const int* __restrict__ types_i,
                         const float* __restrict__ h0, T* __restrict__ o, float* __restrict__ ht,
                         float* __restrict__ hstart, int Tlen, int H, int HN, int V, int TN, int nbs, float scale,
-                        int gdn, int decay, int use_l2norm) {
+                        int gdn, int decay, int use_l2norm, const float* __restrict__ hstart_in,
+                        const float* __restrict__ gsum_in, int t_off, int step_mode) {
+    // step_mode (decoding): the Tlen tokens continue a block that already holds t_off tokens; h0 is the current state,
+    // hstart_in the state at the start of that block, gsum_in [B,H] its log decay so far.  A block only ends where
+    // (t_off + t + 1) is a multiple of nbs, and ht receives the current state instead of the state after the last
+    // selected block (fused_recurrent.py:128-358 with initial_state / initial_state_current / g_cumsum).
     constexpr int K = KPL * 32;
     const int lane = threadIdx.x;
     const int v0 = blockIdx.x * REC_BV, h = blockIdx.y, b = blockIdx.z;
@@ -43,10 +48,12 @@ linear_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     for (int i = 0; i < KPL; ++i)
 #pragma unroll
         for (int j = 0; j < REC_BV; ++j) {
-            float x = h0 ? h0[(((long)b * H + h) * K + lane + 32 * i) * V + v0 + j] : 0.f;
-            S[i][j] = S0[i][j] = Sfin[i][j] = x;
+            const long idx = (((long)b * H + h) * K + lane + 32 * i) * V + v0 + j;
+            float x = h0 ? h0[idx] : 0.f;
+            S[i][j] = Sfin[i][j] = x;
+            S0[i][j] = hstart_in ? hstart_in[idx] : x;
         }
-    float gsum = 0.f;
+    float gsum = gsum_in ? gsum_in[(long)b * H + h] : 0.f;
     for (int t = 0; t < Tlen; ++t) {
         const long tok = (long)b * Tlen + t;
         float qk[KPL], kk[KPL];
@@ -96,8 +103,8 @@ linear_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
             d = warp_sum(d) * scale;
             if (lane == 0) stf(o, (tok * H + h) * V + v0 + j, d);
         }
-        if ((t + 1) % nbs == 0 || t == Tlen - 1) {
-            const int sel = types_i[(((long)b * TN + t / nbs) * HN + hn) * 2 + 1];
+        if ((t_off + t + 1) % nbs == 0 || (!step_mode && t == Tlen - 1)) {
+            const int sel = types_i[(((long)b * TN + (t_off + t) / nbs) * HN + hn) * 2 + 1];
             const float roll = decay ? __expf(gsum) : 1.f;
 #pragma unroll
             for (int i = 0; i < KPL; ++i)
@@ -114,7 +121,7 @@ linear_recurrent_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
 #pragma unroll
         for (int j = 0; j < REC_BV; ++j) {
             const long idx = (((long)b * H + h) * K + lane + 32 * i) * V + v0 + j;
-            if (ht) ht[idx] = Sfin[i][j];
+            if (ht) ht[idx] = step_mode ? S[i][j] : Sfin[i][j];
             if (hstart) hstart[idx] = S0[i][j];
         }
 }
@@ -171,12 +178,15 @@ attn_fp32_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
 template <typename T>
 static int launch_recurrent(const void* q, const void* k, const void* v, const float* g, const void* beta,
                             const int* types_i, const float* h0, void* o, float* ht, float* hstart, int B, int T_, int H,
-                            int HN, int K, int V, int nbs, float scale, int gdn, int decay, int l2, cudaStream_t st) {
-    const int TN = (T_ + nbs - 1) / nbs;
+                            int HN, int K, int V, int nbs, float scale, int gdn, int decay, int l2, cudaStream_t st,
+                            const float* hstart_in = nullptr, const float* gsum_in = nullptr, int t_off = 0,
+                            int step_mode = 0) {
+    const int TN = (t_off + T_ + nbs - 1) / nbs;
     dim3 grid(V / REC_BV, H, B);
 #define NATSL_REC(KPL) linear_recurrent_kernel<T, KPL><<<grid, 32, 0, st>>>( \
         reinterpret_cast<const T*>(q), reinterpret_cast<const T*>(k), reinterpret_cast<const T*>(v), g, \
-        reinterpret_cast<const T*>(beta), types_i, h0, reinterpret_cast<T*>(o), ht, hstart, T_, H, HN, V, TN, nbs, scale, gdn, decay, l2)
+        reinterpret_cast<const T*>(beta), types_i, h0, reinterpret_cast<T*>(o), ht, hstart, T_, H, HN, V, TN, nbs, scale, gdn, decay, l2, \
+        hstart_in, gsum_in, t_off, step_mode)
     if (K == 32) NATSL_REC(1);
     else if (K == 64) NATSL_REC(2);
     else if (K == 128) NATSL_REC(4);
@@ -231,6 +241,31 @@ extern "C" int natsl_linear_recurrent_fwd(int rule, int dtype, const void* q, co
     if (dtype == NATSL_DT_BF16)
         return launch_recurrent<__nv_bfloat16>(q, k, v, g, beta, types_i, h0, o, ht, hstart, B, T, H, HN, K, V, nbs, scale, gdn, decay, use_l2norm, st);
     set_error("natsl_linear_recurrent_fwd: dtype must be f32 or bf16");
+    return NATSL_ERR_UNSUPPORTED;
+}
+
+extern "C" int natsl_linear_recurrent_step(int rule, int dtype, const void* q, const void* k, const void* v, const float* g,
+                                           const void* beta, const int32_t* types_i, const float* h_cur,
+                                           const float* h_start, const float* gsum, int t_off, void* o, float* h_cur_out,
+                                           float* h_start_out, int B, int T, int H, int HN, int K, int V, int nbs,
+                                           float scale, int flags, int use_l2norm, void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(q && k && v && g && types_i && h_cur && h_start && gsum && o && h_cur_out && h_start_out, NATSL_ERR_NULL,
+                  "natsl_linear_recurrent_step: null pointer");
+    NATSL_REQUIRE(rule == NATSL_RULE_GDN || rule == NATSL_RULE_MAMBA, NATSL_ERR_UNSUPPORTED, "natsl_linear_recurrent_step: bad rule");
+    NATSL_REQUIRE(rule != NATSL_RULE_GDN || beta, NATSL_ERR_NULL, "natsl_linear_recurrent_step: beta is required for the delta rule");
+    NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && HN > 0 && H % HN == 0 && V % REC_BV == 0 && nbs > 0 && t_off >= 0 && t_off < nbs,
+                  NATSL_ERR_BAD_SHAPE, "natsl_linear_recurrent_step: bad shape (V a multiple of 8, 0 <= t_off < nbs)");
+    NATSL_REQUIRE(H <= 65535 && B <= 65535, NATSL_ERR_TOO_LARGE, "natsl_linear_recurrent_step: B, H <= 65535");
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int gdn = rule == NATSL_RULE_GDN, decay = (flags & NATSL_FLAG_DECAY_SKIPPED) ? 1 : 0;
+    if (dtype == NATSL_DT_F32)
+        return launch_recurrent<float>(q, k, v, g, beta, types_i, h_cur, o, h_cur_out, h_start_out, B, T, H, HN, K, V, nbs, scale,
+                                       gdn, decay, use_l2norm, st, h_start, gsum, t_off, 1);
+    if (dtype == NATSL_DT_BF16)
+        return launch_recurrent<__nv_bfloat16>(q, k, v, g, beta, types_i, h_cur, o, h_cur_out, h_start_out, B, T, H, HN, K, V, nbs,
+                                               scale, gdn, decay, use_l2norm, st, h_start, gsum, t_off, 1);
+    set_error("natsl_linear_recurrent_step: dtype must be f32 or bf16");
     return NATSL_ERR_UNSUPPORTED;
 }
 

@@ -76,7 +76,33 @@ int encode_bthd_map(CUtensorMap* out, const void* base, int B, int T, int H, int
     return NATSL_OK;
 }
 
+// Self-test of the bounded-wait path: one warp waits on an mbarrier that nobody arrives at, with the same wait loop
+// the tensor-core kernels use but a caller-given (short) poll limit.  The wait runs out, the status word is set and
+// the kernel returns normally: the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int polls, int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    bool ok = false;
+    for (int i = 0; i < polls && !ok; ++i) ok = mbar_try_wait(b, 0);
+    if (!ok && threadIdx.x == 0) atomicExch(status, NATSL_DEV_WAIT_TIMEOUT);
+}
+
 }  // namespace natsl
+
+extern "C" int natsl_bounded_wait_selftest(int polls, void* stream) {
+    using namespace natsl;
+    NATSL_REQUIRE(polls > 0 && polls <= (1 << 20), NATSL_ERR_BAD_SHAPE, "natsl_bounded_wait_selftest: 1 <= polls <= 2^20");
+    int* status = nullptr;
+    int rc = status_word_ptr(&status);
+    if (rc != NATSL_OK) return rc;
+    bounded_wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(polls, status);
+    return check_launch("natsl_bounded_wait_selftest");
+}
 
 extern "C" int natsl_device_status(void) {
     using namespace natsl;

@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .modules import RMSNorm
+from .modules import RMSNorm, swiglu
 from .natsl_attn_gdn import NeuralAttentionSearchLinearAttnGDN
 
 
@@ -91,7 +91,7 @@ class GatedMLP(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x, **kwargs):
-        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        return self.down_proj(swiglu(self.gate_proj(x), self.up_proj(x)))
 
 
 class NeuralAttentionSearchLinearAttnGDNBlock(nn.Module):
@@ -131,8 +131,7 @@ class NeuralAttentionSearchLinearAttnGDNBlock(nn.Module):
         hidden_states, attentions, past_key_values = self.attn(
             hidden_states=hidden_states, attention_mask=attention_mask, past_key_values=past_key_values,
             use_cache=use_cache, output_attentions=output_attentions, **kwargs)
-        residual = residual + hidden_states                      # the fused pre-norm residual of :138-139
-        hidden_states = self.mlp_norm(residual)
+        hidden_states, residual = self.mlp_norm(hidden_states, residual, True)      # fused pre-norm residual, :138-139
         hidden_states = residual + self.mlp(hidden_states, **kwargs)
         return hidden_states, attentions, past_key_values
 

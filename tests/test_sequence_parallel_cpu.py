@@ -146,3 +146,84 @@ def test_single_rank_sub_segment_split_matches_oracle():
         assert (o_l - o_ref).abs().max() < 1e-9
         assert (o_a - oa_ref).abs().max() < 1e-9
         assert (ht - s_ref).abs().max() < 1e-9
+
+
+# ------------------------------------------------------------------------------- failure on one rank (host side)
+class _FailingOps:
+    """Wraps the per-rank compute; on ``bad_rank`` the linear branch raises (or stalls for ``delay`` seconds) right before
+    the (a, S) exchange, after the rank has already taken part in the first collective."""
+
+    def __init__(self, inner, rank, bad_rank, delay):
+        self._inner, self._rank, self._bad, self._delay = inner, rank, bad_rank, delay
+
+    def __getattr__(self, name):
+        return getattr(self._inner, name)
+
+    def segment_decay(self, gcs, tables, decay):
+        if self._rank == self._bad:
+            if self._delay is None:
+                raise RuntimeError("injected failure before the state exchange")
+            import time
+            time.sleep(self._delay)
+        return self._inner.segment_decay(gcs, tables, decay)
+
+
+def _failing_worker(rank, world, port, delay, ret):
+    import datetime
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    try:
+        from neuralattentionsearchlinear_b200.sequence_parallel import nats_mixed_attn_mamba_sp
+        from tests.sp_helpers import OracleSegmentOps
+        B, T, H, K, V, nbs = 1, 512, 2, 16, 16, 64
+        q, k, v, g, types = _inputs(B, T, H, K, V, nbs, 5)
+        per = T // world
+        c = lambda x: x[:, rank * per:(rank + 1) * per].contiguous()
+        ty = types[:, rank * (per // nbs):(rank + 1) * (per // nbs)].contiguous()
+        ops = _FailingOps(OracleSegmentOps(), rank, bad_rank=1, delay=delay)
+        try:
+            o_l, o_a, _ = nats_mixed_attn_mamba_sp(c(q), c(k), c(v), c(q), c(k), c(v), c(g), ty, nats_block_size=nbs,
+                                                   decay_for_non_mamba_blocks=True, backend=ops)
+            ret[rank] = ("ok", bool(torch.isfinite(o_l).all() and torch.isfinite(o_a).all()))
+        except Exception as e:                       # noqa: BLE001 - the test inspects whatever surfaced
+            ret[rank] = ("error", f"{type(e).__name__}: {e}")
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                            # noqa: BLE001
+            pass
+
+
+def _run_failing(delay):
+    import time
+    world, port = 2, _free_port()
+    ret = mp.Manager().dict()
+    t0 = time.time()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, delay, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    alive = [p.is_alive() for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    return dict(ret), alive, time.time() - t0
+
+
+def test_rank_that_fails_before_the_state_exchange_surfaces_an_error():
+    """Rank 1 raises on the host between two collectives and never sends its (a, S) pair: rank 0's exchange ends with
+    an error (connection closed / process-group timeout) instead of blocking."""
+    ret, alive, dt = _run_failing(delay=None)
+    assert not any(alive), "a rank was still blocked after two minutes"
+    assert ret[1][0] == "error" and "injected failure" in ret[1][1]
+    assert ret[0][0] == "error", f"rank 0 should have seen the exchange fail, got {ret[0]}"
+    assert dt < 100
+
+
+def test_rank_that_is_late_for_the_state_exchange_is_waited_for():
+    """Rank 1 sends its (a, S) pair three seconds late (inside the process-group timeout): the step completes."""
+    ret, alive, dt = _run_failing(delay=3.0)
+    assert not any(alive)
+    assert ret[0] == ("ok", True) and ret[1] == ("ok", True)
