@@ -205,6 +205,35 @@ def linear_recurrent(rule: int, q, k, v, g, beta, tables: SelectionTables, scale
     return o, ht, hstart
 
 
+def linear_recurrent_step(rule: int, q, k, v, g, beta, block_types, state, state_block_start, g_block, t_off: int, nbs: int,
+                          scale: float, decay: bool, use_l2norm: bool):
+    """Decoding step of the linear branch: the T new tokens continue a block that already holds ``t_off`` tokens.
+    ``block_types`` [B, cdiv(t_off + T, nbs), HN, 2] (0/1 floats or ints) are read only where a block ends inside the
+    call.  -> (o [B,T,H,V], new current state, new block-start state), states fp32 [B,H,K,V]."""
+    code = _dt_code(q)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, T, H, K = q.shape
+    V = v.shape[3]
+    dev = q.device
+    g = g.float().contiguous()
+    if beta is not None:
+        beta = beta.to(q.dtype).contiguous()
+    types_i = torch.round(block_types.float()).to(torch.int32).contiguous()
+    _need(types_i.shape[1] == cdiv(t_off + T, nbs) and types_i.shape[3] == 2, "block_types must cover the blocks the step touches")
+    state = state.float().contiguous()
+    start = state_block_start.float().contiguous()
+    g_block = g_block.float().contiguous()
+    _need(tuple(state.shape) == (B, H, K, V) and tuple(start.shape) == (B, H, K, V) and tuple(g_block.shape) == (B, H),
+          "states must be [B,H,K,V] and the block decay [B,H]")
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    new_state, new_start = torch.empty_like(state), torch.empty_like(start)
+    _lib.call("natsl_linear_recurrent_step", rule, code, q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), _lib.ptr(beta),
+              types_i.data_ptr(), state.data_ptr(), start.data_ptr(), g_block.data_ptr(), int(t_off), o.data_ptr(),
+              new_state.data_ptr(), new_start.data_ptr(), B, T, H, types_i.shape[2], K, V, int(nbs), float(scale),
+              _lib.FLAG_DECAY_SKIPPED if decay else 0, int(use_l2norm), current_stream_ptr(dev))
+    return o, new_state, new_start
+
+
 def attn_fwd_fp32(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool):
     """Reference-precision softmax branch (fp32 math; fp32 or bf16 tensors).  Returns (o, lse base-2)."""
     _need(q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype", TypeError)

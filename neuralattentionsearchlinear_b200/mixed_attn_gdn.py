@@ -284,3 +284,65 @@ def nats_mixed_attn_gdn_chunk_inference(
         start = _chunk_start_state(inter, ht, inter['gcs'], tables, op_type_last_chunk, T, nats_block_size,
                                    decay_for_non_gdn_blocks)
     return o_gdn, o_attn, ht, start
+
+
+def repeat_masks(attn_msk: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """[B, HN, q, k] -> [B, HN * n_rep, q, k] (src/nats/ops/attns/attn_utils.py:3-13)."""
+    return attn_msk if n_rep == 1 else attn_msk.repeat_interleave(n_rep, dim=1)
+
+
+def _masked_sdpa(q_attn, k_attn, v_attn, attn_msk, scale_attn):
+    """Softmax branch of a decoding step: the new queries against all cached keys under the cache's visibility mask
+    (mixed_attn_gdn.py:475-483 of the reference does the same with torch's SDPA)."""
+    HQ, HKV = q_attn.shape[2], k_attn.shape[2]
+    msk = repeat_masks(attn_msk, HQ // attn_msk.shape[1])
+    kk, vv = k_attn.transpose(1, 2), v_attn.transpose(1, 2)
+    if HKV != HQ:
+        kk, vv = kk.repeat_interleave(HQ // HKV, dim=1), vv.repeat_interleave(HQ // HKV, dim=1)
+    o = torch.nn.functional.scaled_dot_product_attention(q_attn.transpose(1, 2), kk, vv, attn_mask=msk, scale=scale_attn)
+    o = torch.where(msk.any(-1, keepdim=True), o, torch.zeros_like(o))       # a query without any visible key gives 0
+    return o.transpose(1, 2).contiguous()
+
+
+def nats_mixed_attn_gdn_recurrent(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        attn_msk: torch.Tensor,
+        initial_state_gated_delta: torch.Tensor,
+        initial_state_gated_delta_chunk_start: torch.Tensor,
+        g: torch.Tensor,
+        g_cumsum: torch.Tensor,
+        beta: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        n_tokens_in_current_block: int = 0,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        attn_sw_size: int | None = None,
+        ops_for_incomplete_chunks: str = 'gated_delta_net',
+        output_final_state_gated_delta: bool = False,
+        decay_for_non_gdn_blocks: bool = False,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+        lattn_use_qk_l2norm_in_kernel: bool = True,
+):
+    """Decoding step (mixed_attn_gdn.py:443-590): a few new tokens that continue a block holding
+    ``n_tokens_in_current_block`` tokens.  k_attn / v_attn are all cached keys / values including the new tokens',
+    ``attn_msk`` [B, HN or HQ, new tokens, keys] their visibility; ``initial_state_gated_delta`` is the current state,
+    ``..._chunk_start`` the state the current block started from and ``g_cumsum`` [B,H] the block's log decay so far.
+    -> (o_gated_delta, o_attn, state after the new tokens, state at the start of the then-current block)."""
+    _check_common(ops_for_incomplete_chunks, nats_block_size, attn_sw_size, cu_seqlens, use_g_for_attn, all_incomplete_ops)
+    if not all_incomplete_ops[ops_for_incomplete_chunks]['gated_delta_net'] or not incomplete_block_start_with_ht:
+        raise NotImplementedError("decoding is built for own-block linear attention starting from the carried state")
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = k_lattn.shape[-1] ** -0.5
+    with torch.no_grad():
+        o_attn = _masked_sdpa(q_attn, k_attn, v_attn, attn_msk, scale_attn)
+        B, _, H, _ = q_lattn.shape
+        o_gdn, state, start = _ops.linear_recurrent_step(
+            _lib.RULE_GDN, q_lattn, k_lattn, v_lattn, g, beta, nats_block_types, initial_state_gated_delta,
+            initial_state_gated_delta_chunk_start, g_cumsum.reshape(B, H), int(n_tokens_in_current_block), nats_block_size,
+            scale_lattn, decay_for_non_gdn_blocks, lattn_use_qk_l2norm_in_kernel)
+    return o_gdn, o_attn, state, start

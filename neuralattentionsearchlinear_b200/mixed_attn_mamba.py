@@ -143,3 +143,41 @@ def nats_mixed_attn_mamba_chunk_inference(
         start = _chunk_start_state(inter, ht, inter['gcs'], tables, op_type_last_chunk, T, nats_block_size,
                                    decay_for_non_mamba_blocks)
     return o_m, o_attn, ht, start
+
+
+def nats_mixed_attn_mamba_recurrent(
+        q_attn: torch.Tensor, k_attn: torch.Tensor, v_attn: torch.Tensor,
+        q_lattn: torch.Tensor, k_lattn: torch.Tensor, v_lattn: torch.Tensor,
+        attn_msk: torch.Tensor,
+        initial_state_mamba: torch.Tensor,
+        initial_state_mamba_chunk_start: torch.Tensor,
+        g: torch.Tensor,
+        g_cumsum: torch.Tensor,
+        nats_block_types: torch.Tensor,
+        n_tokens_in_current_block: int = 0,
+        scale_attn=None, scale_lattn=None,
+        cu_seqlens=None, cu_seqlens_nats=None,
+        nats_block_size: int = 64,
+        ops_for_incomplete_chunks: str = 'all',
+        output_final_state_mamba: bool = False,
+        decay_for_non_mamba_blocks: bool = False,
+        incomplete_block_start_with_ht: bool = True,
+        use_g_for_attn: bool = False,
+):
+    """Decoding step of the NAtSL-Mamba2 op (mixed_attn_mamba.py:460-593): see ``nats_mixed_attn_gdn_recurrent``.
+    -> (o_mamba, o_attn, state after the new tokens, state at the start of the then-current block)."""
+    _check_common(ops_for_incomplete_chunks, nats_block_size, None, cu_seqlens, use_g_for_attn, all_incomplete_ops)
+    if not all_incomplete_ops[ops_for_incomplete_chunks]['mamba'] or not incomplete_block_start_with_ht:
+        raise NotImplementedError("decoding is built for own-block linear attention starting from the carried state")
+    if scale_attn is None:
+        scale_attn = k_attn.shape[-1] ** -0.5
+    if scale_lattn is None:
+        scale_lattn = k_lattn.shape[-1] ** -0.5
+    with torch.no_grad():
+        o_attn = gdn_ops._masked_sdpa(q_attn, k_attn, v_attn, attn_msk, scale_attn)
+        B, _, H, _ = q_lattn.shape
+        o_m, state, start = _ops.linear_recurrent_step(
+            _lib.RULE_MAMBA, q_lattn, k_lattn, v_lattn, g, None, nats_block_types, initial_state_mamba,
+            initial_state_mamba_chunk_start, g_cumsum.reshape(B, H), int(n_tokens_in_current_block), nats_block_size,
+            scale_lattn, decay_for_non_mamba_blocks, False)
+    return o_m, o_attn, state, start

@@ -3,8 +3,9 @@ constructor arguments, parameter names and forward signature of the reference la
 (src/nats/layers/natsl_attn_gdn.py:64-666).  The hybrid attention itself runs in the CUDA ops of this package;
 projections and the small modules around it are plain PyTorch.
 
-Built: full-sequence prefill (``mode='chunk'``, no cache).  Decoding with a ``NAtSCache``
-(``past_key_values``), variable-length batches and rotary embeddings raise ``NotImplementedError``.
+Built: full-sequence prefill and training (``mode='chunk'``), and decoding with a ``NAtSCache`` in ``past_key_values``
+(prefill into the empty cache, then steps of fewer than 64 tokens).  Variable-length batches and rotary embeddings
+raise ``NotImplementedError``.
 """
 from __future__ import annotations
 
@@ -15,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .mixed_attn_gdn import nats_mixed_attn_gdn, nats_mixed_attn_gdn_chunk_inference
+from .mixed_attn_gdn import nats_mixed_attn_gdn, nats_mixed_attn_gdn_chunk_inference, nats_mixed_attn_gdn_recurrent
 from .modules import FusedMultiInputRMSNormGated, RMSNorm, ShortConvolution, hard_softmax, mean_pooling
 
 
@@ -151,24 +152,28 @@ class NeuralAttentionSearchLinearAttnGDN(nn.Module):
         self.attn_fraction = torch.zeros(1)
 
     # ------------------------------------------------------------------------------------------------
-    def project(self, hidden_states: torch.Tensor) -> dict:
-        """Everything the hybrid-attention op consumes, computed from the layer input
-        (natsl_attn_gdn.py:411-530, 553-555)."""
-        B, T, dim = hidden_states.shape
-        hs_reduced = self.pooling_func(hidden_states.unsqueeze(-2), chunk_size=self.nats_block_size).view(B, -1, dim)
-        logits = self.nats_layer(hs_reduced).unflatten(-1, (self.num_nats_head, self.n_ops))
-        types = self.nats_sample_func(logits)
+    def select(self, pooled: torch.Tensor) -> torch.Tensor:
+        """Block-mean layer input [B, NB, D] -> sampled 0/1 block types [B, NB, HN, n_ops] (natsl_attn_gdn.py:411-420)."""
+        logits = self.nats_layer(pooled).unflatten(-1, (self.num_nats_head, self.n_ops))
+        return self.nats_sample_func(logits)
+
+    def project_qkv(self, hidden_states: torch.Tensor, conv_state=None, want_conv_state: bool = False) -> dict:
+        """q, k, v of both branches, the mixing weights, beta and the log decay from the layer input
+        (natsl_attn_gdn.py:425-530).  ``conv_state``: the (q, k, v) convolution tails of a decoding cache."""
+        cq, ck, cv = conv_state if conv_state is not None else (None, None, None)
+        new_state = None
         if self.use_short_conv:
             if self.attn_with_short_conv:
-                q, _ = self.q_conv1d(self.q_proj(hidden_states))
-                k, _ = self.k_conv1d(self.k_proj(hidden_states))
-                v, _ = self.v_conv1d(self.v_proj(hidden_states))
+                q, sq = self.q_conv1d(self.q_proj(hidden_states), cache=cq, output_final_state=want_conv_state)
+                k, sk = self.k_conv1d(self.k_proj(hidden_states), cache=ck, output_final_state=want_conv_state)
+                v, sv = self.v_conv1d(self.v_proj(hidden_states), cache=cv, output_final_state=want_conv_state)
                 q_attn, k_attn, v_attn = q, k, v
             else:
                 q_attn, k_attn, v_attn = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
-                q, _ = self.q_conv1d(q_attn)
-                k, _ = self.k_conv1d(k_attn)
-                v, _ = self.v_conv1d(v_attn)
+                q, sq = self.q_conv1d(q_attn, cache=cq, output_final_state=want_conv_state)
+                k, sk = self.k_conv1d(k_attn, cache=ck, output_final_state=want_conv_state)
+                v, sv = self.v_conv1d(v_attn, cache=cv, output_final_state=want_conv_state)
+            new_state = (sq, sk, sv)
         else:
             if self.attn_with_short_conv:
                 q, k, v = (F.silu(p(hidden_states)) for p in (self.q_proj, self.k_proj, self.v_proj))
@@ -191,13 +196,23 @@ class NeuralAttentionSearchLinearAttnGDN(nn.Module):
         if self.allow_neg_eigval:
             beta = beta * 2.
         g = -self.A_log.float().exp() * F.softplus(self.a_proj(hidden_states).float() + self.dt_bias)
-        types = types.clone()
+        return dict(q=q, k=k, v=v, q_attn=q_attn, k_attn=k_attn, v_attn=v_attn, beta=beta, g=g, o_weights=o_weights,
+                    conv_state=new_state)
+
+    def project(self, hidden_states: torch.Tensor, want_conv_state: bool = False) -> dict:
+        """Everything the hybrid-attention op consumes, computed from the layer input
+        (natsl_attn_gdn.py:411-530, 553-555)."""
+        B, T, dim = hidden_states.shape
+        hs_reduced = self.pooling_func(hidden_states.unsqueeze(-2), chunk_size=self.nats_block_size).view(B, -1, dim)
+        types_raw = self.select(hs_reduced)
+        p = self.project_qkv(hidden_states, want_conv_state=want_conv_state)
+        types = types_raw.clone()
         op_type_last = types[:, -1].clone()
         types[:, -1] = 1                                   # natsl_attn_gdn.py:553
         n_blocks = types.int().sum(1)
         self.attn_fraction = (n_blocks.float()[..., 0] / types.shape[1]).mean(0).detach()
-        return dict(q=q, k=k, v=v, q_attn=q_attn, k_attn=k_attn, v_attn=v_attn, beta=beta, g=g, types=types,
-                    n_blocks=n_blocks, o_weights=o_weights, op_type_last=op_type_last)
+        p.update(types=types, types_raw=types_raw, n_blocks=n_blocks, op_type_last=op_type_last)
+        return p
 
     def mix(self, hidden_states, o_gated_delta, o_attn, o_weights):
         """Norm, mix, gate and project the two branch outputs (natsl_attn_gdn.py:652-666)."""
@@ -226,11 +241,13 @@ class NeuralAttentionSearchLinearAttnGDN(nn.Module):
             assert len(attention_mask.shape) == 2
             if len(attention_mask) > 1:
                 raise NotImplementedError("Attention with variable length is not supported yet!")
-        if past_key_values is not None or kwargs.get('cu_seqlens', None) is not None:
-            raise NotImplementedError("decoding with a NAtSCache / variable-length batches are not built")
+        if kwargs.get('cu_seqlens', None) is not None:
+            raise NotImplementedError("variable-length batches are not built")
         B, T, _ = hidden_states.shape
+        if past_key_values is not None:
+            return self._forward_cached(hidden_states, past_key_values)
         if T < 64 or self.mode != 'chunk':
-            raise NotImplementedError("the fused_recurrent (decode) mode is not built")
+            raise NotImplementedError("fewer than 64 tokens (decoding) need a NAtSCache in past_key_values")
         p = self.project(hidden_states)
         common = dict(scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5,
                       cu_seqlens=None, cu_seqlens_nats=None, nats_block_size=self.nats_block_size,
@@ -253,3 +270,92 @@ class NeuralAttentionSearchLinearAttnGDN(nn.Module):
                 n_nats_blocks=p['n_blocks'], output_final_state_gated_delta=use_cache, **common)
         o = self.mix(hidden_states, o_gd, o_attn, p['o_weights'])
         return o, None, past_key_values
+
+    # ------------------------------------------------------------------------------------------------ decoding
+    @torch.no_grad()
+    def _forward_cached(self, hidden_states: torch.Tensor, past_key_values):
+        """Prefill into an empty cache (64 tokens or more, chunk kernels) or a decoding step of fewer than 64 tokens
+        (token recurrence with re-roll + masked attention over the cached keys), natsl_attn_gdn.py:389-410, 576-650."""
+        if self.layer_idx is None:
+            raise ValueError("a layer used with a cache needs its layer_idx")
+        if self.ops_for_incomplete_chunks == 'attn' or not self.incomplete_block_start_with_ht:
+            raise NotImplementedError("decoding is built for the modes 'all' and 'gated_delta_net'")
+        cache = past_key_values.layer(self.layer_idx, self.nats_block_size)
+        B, T, _ = hidden_states.shape
+        nbs = self.nats_block_size
+        own_attn = self.ops_for_incomplete_chunks != 'gated_delta_net'
+        if cache.n_tokens == 0 and T >= 64:
+            p = self.project(hidden_states, want_conv_state=True)
+            o_gd, o_attn, ht, start = nats_mixed_attn_gdn_chunk_inference(
+                q_attn=p['q_attn'], k_attn=p['k_attn'], v_attn=p['v_attn'], q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
+                initial_state_gated_delta_chunk_start=None, g=p['g'], beta=p['beta'], nats_block_types=p['types'],
+                op_type_last_chunk=p['op_type_last'] if T % nbs == 0 else None, n_nats_blocks=p['n_blocks'],
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, nats_block_size=nbs,
+                ops_for_incomplete_chunks=self.ops_for_incomplete_chunks, output_final_state_gated_delta=True,
+                decay_for_non_gdn_blocks=self.decay_for_non_gdn_blocks, incomplete_block_start_with_ht=True,
+                use_g_for_attn=self.usg_for_attn, lattn_use_qk_l2norm_in_kernel=True)
+            r, n_done = T % nbs, T // nbs
+            cache.append_kv(p['k_attn'].contiguous(), p['v_attn'].contiguous())
+            if n_done:
+                cache.append_types(p['types_raw'][:, :n_done].contiguous())
+            cache.state_block_start = start
+            cache.state = start.clone() if r == 0 else ht
+            H = p['g'].shape[2]
+            cache.g_block = (p['g'][:, T - r:].float().sum(1) if r else torch.zeros(B, H, device=hidden_states.device))
+            cache.pool_sum = (hidden_states[:, T - r:].float().sum(1) if r
+                              else torch.zeros(B, hidden_states.shape[2], device=hidden_states.device))
+            cache.conv_state = p['conv_state']
+            cache.n_tokens = T
+            return self.mix(hidden_states, o_gd, o_attn, p['o_weights']), None, past_key_values
+        if T >= 64:
+            raise NotImplementedError("continuing a prefill of 64 tokens or more into a filled cache is not built; "
+                                      "feed the continuation in pieces of fewer than 64 tokens")
+        if cache.n_tokens == 0:                                 # a short prompt: start from empty states
+            dev = hidden_states.device
+            H, K, V = self.num_heads, self.head_k_dim, self.head_v_dim
+            cache.state = torch.zeros(B, H, K, V, device=dev)
+            cache.state_block_start = torch.zeros(B, H, K, V, device=dev)
+            cache.g_block = torch.zeros(B, H, device=dev)
+            cache.pool_sum = torch.zeros(B, hidden_states.shape[2], device=dev)
+        outs_l, outs_a, weights = [], [], []
+        a = 0
+        while a < T:
+            t_off = cache.n_tokens % nbs
+            b_ = min(T, a + (nbs - t_off))                      # a piece never crosses a block boundary
+            hs = hidden_states[:, a:b_]
+            n = b_ - a
+            completes = (t_off + n) == nbs
+            cache.pool_sum = cache.pool_sum + hs.float().sum(1)
+            if completes:
+                pooled = (cache.pool_sum / nbs).to(hs.dtype)[:, None, :]
+                types_new = self.select(pooled)                  # decided once the block's last token is known
+            else:
+                types_new = torch.ones(B, 1, self.num_nats_head, self.n_ops, device=hs.device, dtype=hs.dtype)
+            p = self.project_qkv(hs, conv_state=cache.conv_state, want_conv_state=True)
+            cache.append_kv(p['k_attn'].contiguous(), p['v_attn'].contiguous())
+            msk = cache.generate_msk(n, self.num_attn_heads, own_chunk=own_attn)
+            o_gd, o_attn, state, start = nats_mixed_attn_gdn_recurrent(
+                q_attn=p['q_attn'], k_attn=cache.k_attn, v_attn=cache.v_attn, q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
+                attn_msk=msk, initial_state_gated_delta=cache.state,
+                initial_state_gated_delta_chunk_start=cache.state_block_start, g=p['g'], g_cumsum=cache.g_block,
+                beta=p['beta'], nats_block_types=types_new, n_tokens_in_current_block=t_off,
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, nats_block_size=nbs,
+                ops_for_incomplete_chunks=self.ops_for_incomplete_chunks, output_final_state_gated_delta=True,
+                decay_for_non_gdn_blocks=self.decay_for_non_gdn_blocks, incomplete_block_start_with_ht=True,
+                use_g_for_attn=self.usg_for_attn, lattn_use_qk_l2norm_in_kernel=True)
+            cache.state, cache.state_block_start = state, start
+            if completes:
+                cache.append_types(types_new)
+                cache.g_block = torch.zeros_like(cache.g_block)
+                cache.pool_sum = torch.zeros_like(cache.pool_sum)
+            else:
+                cache.g_block = cache.g_block + p['g'].float().sum(1)
+            cache.conv_state = p['conv_state']
+            cache.n_tokens += n
+            outs_l.append(o_gd)
+            outs_a.append(o_attn)
+            weights.append(p['o_weights'])
+            a = b_
+        o_gd, o_attn = torch.cat(outs_l, 1), torch.cat(outs_a, 1)
+        o_w = torch.cat(weights, 1) if weights[0] is not None else None
+        return self.mix(hidden_states, o_gd, o_attn, o_w), None, past_key_values

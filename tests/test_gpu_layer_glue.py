@@ -66,6 +66,9 @@ def test_rmsnorm(D, rows_shape, with_res):
     rr = r.double().requires_grad_(True) if with_res else None
     w = norm.weight.detach().double().cpu().requires_grad_(True)
     sr = xr + rr if with_res else xr
+    if with_res:
+        # the residual stream is stored in bf16 and the stored value is what gets normalised
+        sr = sr + (sr.detach().bfloat16().double() - sr.detach())
     yr = sr * torch.rsqrt(sr.pow(2).mean(-1, keepdim=True) + 1e-6) * w
     loss = (yr * dy.double()).sum() + ((sr * ds.double()).sum() if with_res else 0.0)
     loss.backward()
