@@ -276,7 +276,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- per-kernel durations: each stage launched `steps` times back to back on the same stream between two
     # CUDA events (the queue stays full, so the events bracket device time, not host launch latency)
-    names = ["tables", "attn_fwd", "gdn_prep", "walk_fused", "scan_fwd_h", "out_fwd_o"]
+    names = ["tables", "attn_fwd", "gdn_prep", "walk_fused", "walk_vsplit", "scan_fwd_h", "out_fwd_o"]
     NT = T // 64
     tb = nat.build_selection_tables(d["types"], T, nbs)
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
@@ -301,6 +301,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                         tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
                                         o.data_ptr(), ht.data_ptr(), B, T, H, H, K, V, nbs, K ** -0.5,
                                         _lib.FLAG_DECAY_SKIPPED, sp),
+        "walk_vsplit": lambda: _lib.call("natsl_gdn_walk_fused_vsplit", d["q"].data_ptr(), d["k"].data_ptr(), w.data_ptr(),
+                                         u.data_ptr(), pmat.data_ptr(), gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(),
+                                         tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
+                                         o.data_ptr(), ht.data_ptr(), B, T, H, H, K, V, nbs, K ** -0.5,
+                                         _lib.FLAG_DECAY_SKIPPED, sp),
         "scan_fwd_h": lambda: _lib.call("natsl_linear_fwd_h", _lib.RULE_GDN, d["k"].data_ptr(), w.data_ptr(), u.data_ptr(),
                                         gcs.data_ptr(), krs.data_ptr(), tb.types_i.data_ptr(), tb.indices.data_ptr(),
                                         tb.n_blocks.data_ptr(), None, hbuf.data_ptr(), carry.data_ptr(), ht.data_ptr(),
@@ -387,13 +392,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             if r == rank:
                 solo = gr
         r_n = mamba_long_measure(args, rank, world, dev, group=None, lin_group=lin_group, plan=True, parity=True)
-        r_1 = mamba_long_measure(args, 0, 1, dev, group=solo, lin_group=None, plan=False, parity=False)
-        one = max_over_ranks(r_1["ms_per_step"])
-        sp_info = {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 p_softmax=0.10",
-                   "scaling": "strong", "n_gpus": world, "ms_per_step": r_n["ms_per_step"], "tokens_per_s": r_n["tokens_per_s"],
-                   "one_gpu_ms_per_step": one, "speedup_vs_one_gpu": one / r_n["ms_per_step"], "launch": r_n["launch"],
-                   "layout": r_n["layout"], "host_issue_ms_per_step": r_n["host_issue_ms_per_step"],
-                   "parity": r_n.get("parity"), "device_status": _lib.load().natsl_device_status()}
+        barrier()
+        # the same layer on one GPU, in this run: rank 0 alone, the other ranks wait at the barrier (no host contention)
+        r_1 = mamba_long_measure(args, 0, 1, dev, group=solo, lin_group=None, plan=False, parity=False) if rank == 0 else None
+        barrier()
+        if rank == 0:
+            one = r_1["ms_per_step"]
+            sp_info = {"workload": "natsl_mamba2_layer_fwd B=1 T=65536 H=32 dstate=128 dhead=64 block=256 p_softmax=0.10",
+                       "scaling": "strong", "n_gpus": world, "ms_per_step": r_n["ms_per_step"],
+                       "tokens_per_s": r_n["tokens_per_s"], "one_gpu_ms_per_step": one,
+                       "one_gpu_host_issue_ms_per_step": r_1["host_issue_ms_per_step"],
+                       "speedup_vs_one_gpu": one / r_n["ms_per_step"], "launch": r_n["launch"], "layout": r_n["layout"],
+                       "host_issue_ms_per_step": r_n["host_issue_ms_per_step"], "parity": r_n.get("parity"),
+                       "device_status": _lib.load().natsl_device_status()}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -418,10 +429,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         ncu_traffic, ncu_batch = tr["bytes_per_launch"], tr["batch"]
     # the step runs tables, attn_fwd, gdn_prep, walk_fused; scan_fwd_h + out_fwd_o are the two-kernel path the fused
     # walk replaces at this shape (still used for other head dims / block sizes) and are timed for comparison
-    in_step = ("attn_fwd", "gdn_prep", "walk_fused")
+    walk_stage = "walk_vsplit" if _ops.WALK_VSPLIT else "walk_fused"
+    in_step = ("attn_fwd", "gdn_prep", walk_stage)
     work = {
         # reads q, k, w, u, P once, writes o
         "walk_fused": ("hbm", n_tok * (3 * K + V + 64) * 2 + n_tok * V * 2, "gdn_walk_tc_kernel"),
+        "walk_vsplit": ("hbm", n_tok * (3 * K + V + 64) * 2 + n_tok * V * 2, "gdn_walk_half_kernel"),
         "attn_fwd": ("tensor", attention_tile_flops(host["types"], H, K, V), "attn_fwd_tc_kernel<128,128>"),
         "gdn_prep": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (K + V + 64) * 2 + n_tok * 18, "gdn_prep_kernel<128,128>"),
         "scan_fwd_h": ("hbm", frac_lin * n_tok * (2 * K + V) * 2 + state_bytes, "linear_scan_kernel<128,32,gdn>"),

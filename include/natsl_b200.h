@@ -165,6 +165,14 @@ int natsl_gdn_walk_fused(const void* q, const void* k, const void* w, const void
                          const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht, int B,
                          int T, int H, int HN, int K, int V, int nbs, float scale, int flags, void* stream);
 
+/* The same walk with the value dimension split over two CTAs per (batch, head): 256 tensor-memory columns and about
+ * 107 KB of shared memory per CTA, so that two of them, or one of them and one attention CTA, share an SM (the two
+ * branches of the layer then overlap).  Same arguments and results; T <= 8192. */
+int natsl_gdn_walk_fused_vsplit(const void* q, const void* k, const void* w, const void* u, const void* pmat,
+                                const float* gcs, const float* k_rstd, const float* q_rstd, const int32_t* types_i,
+                                const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht,
+                                int B, int T, int H, int HN, int K, int V, int nbs, float scale, int flags, void* stream);
+
 /* Reference-precision (fp32 math, CUDA cores) path for fp32 or bf16 tensors (dtype = NATSL_DT_F32 / _BF16 for
  * q, k, v, beta, o): token-by-token linear recurrence with re-roll to the block-start state, and plain masked
  * softmax attention.  ht = state after the last selected block, hstart = block-start state at the end (both

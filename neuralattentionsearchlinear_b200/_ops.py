@@ -1,6 +1,8 @@
 """Thin launch wrappers: allocate outputs with torch, pass raw pointers to the C ABI."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -8,6 +10,10 @@ from .nats_util import SelectionTables, cdiv, current_stream_ptr
 
 BF16 = torch.bfloat16
 USE_FUSED_WALK = True        # K = V = 128, block 64: recurrence + output fused on tcgen05 (natsl_gdn_walk_fused)
+# value dimension of the fused walk split over two CTAs (natsl_gdn_walk_fused_vsplit, T <= 8192): half an SM per CTA.
+# Off by default: measured alone it is no faster than the one-CTA walk (0.204 vs 0.189 ms at B=8, T=4096, H=16), and
+# the kernels of the two branches do not overlap in practice (the block scheduler drains one grid before the next).
+WALK_VSPLIT = os.environ.get("NATSL_WALK_VSPLIT", "0") == "1"
 
 
 def _need(cond: bool, msg: str, exc=ValueError):
@@ -147,7 +153,8 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     if fused:
         # recurrence + output in one tcgen05 walk; the per-chunk states are never materialised
         o = torch.empty(B, T, H, V, dtype=BF16, device=dev)
-        _lib.call("natsl_gdn_walk_fused", q.data_ptr(), k.data_ptr(), w.data_ptr(), u.data_ptr(), pmat.data_ptr(),
+        entry = "natsl_gdn_walk_fused_vsplit" if (WALK_VSPLIT and NT <= 128) else "natsl_gdn_walk_fused"
+        _lib.call(entry, q.data_ptr(), k.data_ptr(), w.data_ptr(), u.data_ptr(), pmat.data_ptr(),
                   gcs.data_ptr(), krstd.data_ptr(), qrstd.data_ptr(), tables.types_i.data_ptr(),
                   tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht),
                   B, T, H, HN, K, V, nbs, float(scale), flags, st)

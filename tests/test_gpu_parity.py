@@ -297,13 +297,16 @@ def test_full_size_layer_config(nat):
     assert torch.equal(o_l2, o_l[3:5]) and torch.equal(o_a2, o_a[3:5]) and torch.equal(ht2, ht[3:5])
 
 
+@pytest.mark.parametrize("vsplit", [False, True])
 @pytest.mark.parametrize("B,T,H,HN,decay,use_h0", [(2, 512, 4, 4, True, False), (1, 700, 4, 2, True, True),
                                                     (2, 384, 2, 2, False, True), (1, 64, 2, 2, True, True),
                                                     (1, 50, 2, 1, True, False), (1, 2048, 2, 2, True, True)])
-def test_gdn_fused_walk(nat, B, T, H, HN, decay, use_h0):
+def test_gdn_fused_walk(nat, B, T, H, HN, decay, use_h0, vsplit, monkeypatch):
     """Recurrence + output fused on tcgen05 (K = V = 128, block 64) against the oracle, and against the
-    two-kernel path it replaces."""
+    two-kernel path it replaces; both forms of the walk (one CTA per (batch, head), and the value dimension split
+    over two CTAs)."""
     from neuralattentionsearchlinear_b200 import _lib, _ops
+    monkeypatch.setattr(_ops, "WALK_VSPLIT", vsplit)
     K = V = 128
     q, k, v, g, beta, h0 = synth_gdn_inputs(B, T, H, K, V, seed=T + 5, normalize_qk=False)
     if not use_h0:
