@@ -784,6 +784,137 @@ def run_model(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------- layer forward + backward (optional)
+def run_layer_fwdbwd(args, rank: int, world: int, local_rank: int):
+    """One step = forward + backward of ``nats_mixed_attn_gdn`` on the layer configuration (B=8, T=4096, H=16, d=128,
+    block 64) with every differentiable input requiring a gradient; per-stage device times and rooflines of the backward
+    kernels; gradients of a (sequence, head) sample checked against the oracle."""
+    import neuralattentionsearchlinear_b200 as nat
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = init_process_group_quiet(dev) if world > 1 else None
+    B, T, H, K, V, nbs = (CFG[n] for n in ("B", "T", "H", "K", "V", "nbs"))
+    host = make_inputs(1000 * rank, B, H)
+    gen = torch.Generator().manual_seed(77 + rank)
+    do_l = torch.randn(B, T, H, V, generator=gen).bfloat16()
+    do_a = torch.randn(B, T, H, V, generator=gen).bfloat16()
+    leaf = lambda n: host[n].to(dev).requires_grad_(True)
+    q, k, v, g, beta, types = (leaf(n) for n in ("q", "k", "v", "g", "beta", "types"))
+    dl, da = do_l.to(dev), do_a.to(dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def step():
+        for t_ in (q, k, v, g, beta, types):
+            t_.grad = None
+        o_l, o_a, _ = nat.nats_mixed_attn_gdn(q, k, v, q, k, v, None, g, beta, types, None, nats_block_size=nbs,
+                                              ops_for_incomplete_chunks="all", decay_for_non_gdn_blocks=True)
+        torch.autograd.backward([o_l, o_a], [dl, da])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    clocks = ClockSampler(vis.split(",")[local_rank].strip() if vis else local_rank)
+    if rank == 0:
+        clocks.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize(dev)
+    t_w = time.perf_counter()
+    while time.perf_counter() - t_w < args.min_warm_seconds:
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize(dev)
+    if rank == 0:
+        clocks.rows.clear()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = _lib.kernel_launches()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    gpu_launches = _lib.kernel_launches() - launches_before
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clk = clocks.stop() if rank == 0 else None
+    ms_step = ms / args.steps
+    # ---- per-stage device times of the backward pass (CUDA events around every C-ABI call)
+    tb = nat.build_selection_tables(types.detach(), T, nbs)
+    with torch.no_grad():
+        o_attn, lse = _ops.attn_fwd(q, k, v, tb, K ** -0.5, True)
+        timer = _ops.StageTimer()
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            _ops.attn_bwd(q, k, v, o_attn, lse, da, tb, K ** -0.5, True, timer=timer)
+            res = _ops.linear_bwd(_lib.RULE_GDN, q, k, v, g.detach(), beta.detach(), tb, K ** -0.5, None, True, True, dl, timer=timer)
+        stage_ms = {n: t_ / reps for n, t_ in timer.result().items()}
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peaks = json.load(open(peaks_path))
+        peak_tf, peak_bw, peak_src = float(peaks["bf16_tflops_sustained"]), float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    else:
+        peak_tf, peak_bw, peak_src = 1400.0, 6650.0, "fallback"
+    n_tok = B * T * H
+    NT = T // 64
+    st_b = B * NT * H * K * V * 2                         # one K x V bf16 state per chunk
+    frac_lin = float(host["types"][..., 1].float().mean())
+    work = {
+        # five products per visible (query chunk, key chunk) pair: S, dP, dQ, dK, dV
+        "attn_bwd": ("tensor", 2.5 * attention_tile_flops(host["types"], H, K, V), "attn_bwd_dq_kernel + attn_bwd_dkdv_kernel"),
+        "recompute_prep": ("hbm", n_tok * (K + V) * 2 + n_tok * (K + V) * 2 + n_tok * 14, "gdn_prep_kernel<128,128>"),
+        "recompute_scan": ("hbm", frac_lin * n_tok * (2 * K + V) * 2 + st_b, "linear_scan_kernel<128,32,gdn>"),
+        "bwd_pre": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (2 * K + V) * 2, "linear_bwd_pre_kernel<128,128>"),
+        "bwd_dh": ("hbm", n_tok * (3 * K + 2 * V) * 2 + frac_lin * st_b + n_tok * V * 2, "linear_bwd_dh_kernel<128,32,gdn>"),
+        "bwd_state": ("hbm", n_tok * (2 * K + 3 * V) * 2 + st_b + frac_lin * st_b + n_tok * (3 * K + V) * 2,
+                      "linear_bwd_state_kernel<128,128,gdn>"),
+        "bwd_intra": ("hbm", n_tok * (6 * K + 5 * V) * 2 + n_tok * (2 * K + V) * 2, "linear_bwd_intra_kernel<128,128,gdn>"),
+        "bwd_dg": ("hbm", n_tok * 8 + B * NT * H * 16, "linear_bwd_dg_kernel"),
+    }
+    roofs = {}
+    for n, (bound, amount, kname) in work.items():
+        sec = stage_ms[n] * 1e-3
+        ach, peak, unit = (amount / sec / 1e12, peak_tf, "TFLOP/s") if bound == "tensor" else (amount / sec / 1e9, peak_bw, "GB/s")
+        roofs[n] = {"kernel": kname, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                    "traffic": None, "algorithmic_per_launch": amount, "ms_per_launch": stage_ms[n]}
+    dom = max(stage_ms, key=lambda n: stage_ms[n])
+    # ---- parity of the timed gradients: one sequence, a few heads, against the oracle in float64
+    from oracle import grad as ograd
+    hs = 2
+    sl = lambda x: x[:1, :, :hs].detach().double().cpu().contiguous()
+    ty = host["types"][:1, :, :hs].float()
+    ra = ograd.attn_grads(sl(q), sl(k), sl(v), ty[..., 0], do_a[:1, :, :hs].double(), nbs=nbs)
+    rl = ograd.linear_chunk_backward(sl(q), sl(k), sl(v), sl(g), sl(beta), ty[..., 1], do_l[:1, :, :hs].double(), None, decay=True)
+    got_q = q.grad[:1, :, :hs].double().cpu()
+    ref_q = ra["dq"] + rl["dq"]
+    got_g, ref_g = g.grad[:1, :, :hs].double().cpu(), rl["dg"]
+    par = {"max_abs_err_dq": float((got_q - ref_q).abs().max()), "max_abs_dq": float(ref_q.abs().max()),
+           "max_abs_err_dg": float((got_g - ref_g).abs().max()), "max_abs_dg": float(ref_g.abs().max()),
+           "sample": f"sequence 0, heads 0..{hs - 1}: dq (both branches) and dg of the timed step vs the float64 CPU oracle"}
+    print(json.dumps({
+        "metric": "train_tokens_per_s", "value": world * B * T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded, generated on the host)",
+        "config": {"workload": "natsl_gdn_layer_fwd+bwd B={} T=4096 H=HQ=16 dk=dv=128 block=64 bf16 p_softmax=0.25".format(B),
+                   "per_gpu_batch": B, "parallelism": f"replicas x{world} (batch sharded, no collective)"},
+        "clocks": clk, "gpu_launches": gpu_launches, "kernel_ms": stage_ms,
+        "roofline": dict(roofs[dom], peak_source=peak_src, dominant_stage=dom), "roofline_all": roofs, "parity": par}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -805,7 +936,7 @@ def main():
                          "reading the block counts back every step")
     ap.add_argument("--sp-plain-op", action="store_true",
                     help="mamba_long on one GPU through nats_mixed_attn_mamba (no sub-segment split, one stream)")
-    ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "mamba_long", "model_prefill", "model_fwdbwd"],
+    ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "gdn_layer_fwdbwd", "mamba_long", "model_prefill", "model_fwdbwd"],
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
                          "Mamba2 layer, sequence-parallel over the ranks; model_prefill / model_fwdbwd: the 24-layer "
                          "decoder models (prefill of 16 x 4096 tokens; forward + backward of 8 x 4096 tokens per GPU)")
@@ -822,6 +953,8 @@ def main():
         run_reference(args, rank)
     elif args.workload == "mamba_long":
         run_mamba_long(args, rank, world, local_rank)
+    elif args.workload == "gdn_layer_fwdbwd":
+        run_layer_fwdbwd(args, rank, world, local_rank)
     elif args.workload in MODEL_CFGS:
         run_model(args, rank, world, local_rank)
     else:

@@ -259,7 +259,37 @@ def attn_fwd_fp32(q, k, v, tables: SelectionTables, scale: float, own_chunk: boo
 
 
 # ------------------------------------------------------------------------------------------------ backward
-def attn_bwd(q, k, v, o, lse, do, tables: SelectionTables, scale: float, own_chunk: bool, reference_compat: bool = False):
+class StageTimer:
+    """Optional per-stage device timing of the backward pass: CUDA events on the launching stream around every C-ABI
+    call; ``result()`` synchronises and returns {stage: milliseconds} (summed over repeated calls)."""
+
+    def __init__(self):
+        self.events = []
+
+    def call(self, stage: str, name: str, *args):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.call(name, *args)
+        e1.record()
+        self.events.append((stage, e0, e1))
+
+    def result(self) -> dict:
+        torch.cuda.synchronize()
+        out = {}
+        for stage, e0, e1 in self.events:
+            out[stage] = out.get(stage, 0.0) + e0.elapsed_time(e1)
+        return out
+
+
+def _call(timer, stage, name, *args):
+    if timer is None:
+        _lib.call(name, *args)
+    else:
+        timer.call(stage, name, *args)
+
+
+def attn_bwd(q, k, v, o, lse, do, tables: SelectionTables, scale: float, own_chunk: bool, reference_compat: bool = False,
+             timer: StageTimer | None = None):
     """Backward of the softmax branch.  -> (dq, dk, dv bf16, dnats_attn [B,TN,HN] fp32): ``dnats_attn`` is the sum of the
     score gradients of the keys of a softmax-selected block over the queries of later blocks, summed over the heads
     of a selection group and zero for the other blocks (src/nats/ops/attns/attns.py:922, 975-978, 1625-1629, 1749-1755).
@@ -280,7 +310,7 @@ def attn_bwd(q, k, v, o, lse, do, tables: SelectionTables, scale: float, own_chu
     delta = torch.empty(B, T, HQ, dtype=torch.float32, device=dev)
     part = torch.empty(B, NT, HQ, dtype=torch.float32, device=dev)
     flags = (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_BWD_REFERENCE_COMPAT if reference_compat else 0)
-    _lib.call("natsl_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+    _call(timer, "attn_bwd", "natsl_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
               tables.types_i.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), part.data_ptr(),
               B, T, HQ, HKV, HN, DK, DV, nbs, float(scale), flags, current_stream_ptr(dev))
     cpb = nbs // 64
@@ -292,7 +322,8 @@ def attn_bwd(q, k, v, o, lse, do, tables: SelectionTables, scale: float, own_chu
 
 
 def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: float, h0, decay: bool, use_l2norm: bool,
-               do, dht=None, invalid_dnats: bool = True, trailing_quirk: bool = True, return_intermediates: bool = False):
+               do, dht=None, invalid_dnats: bool = True, trailing_quirk: bool = True, return_intermediates: bool = False,
+               timer: StageTimer | None = None):
     """Backward of the linear branch (block size 64).  Recomputes the forward's preparation and recurrence, then runs the
     five backward stages.  -> dict(dq, dk, dv bf16; dg fp32; dbeta fp32 or None; dh0 fp32 or None; dnats [B,NT,HN] fp32
     = the reference's dnats column for the linear branch, src/nats/ops/common/chunk_o.py:440-443, 459-492, 1568-1575)."""
@@ -320,18 +351,18 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
         _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
         w, u = torch.empty(B, T, H, K, **bf), torch.empty(B, T, H, V, **bf)
         krs0 = torch.empty(B, T, H, **f32)
-        _lib.call("natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        _call(timer, "recompute_prep", "natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
                   _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
                   krs0.data_ptr(), B, T, H, K, V, int(use_l2norm), st)
     else:
         w, u, krs0 = None, v, None
-        _lib.call("natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
+        _call(timer, "recompute_prep", "natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
     if h0 is not None:
         h0 = h0.float().contiguous()
     flags = (_lib.FLAG_DECAY_SKIPPED if decay else 0) | (0 if trailing_quirk else _lib.FLAG_NO_TRAILING_QUIRK)
     h = torch.empty(B, NT, H, K, V, **bf)
     carry = torch.empty(B, NT, H, **f32)
-    _lib.call("natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krs0),
+    _call(timer, "recompute_scan", "natsl_linear_fwd_h", rule, k.data_ptr(), _lib.ptr(w), u.data_ptr(), gcs.data_ptr(), _lib.ptr(krs0),
               tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
               h.data_ptr(), carry.data_ptr(), None, B, T, H, HN, K, V, 64, flags, st)
     # ---- 1: normalised q, k and the chunk-local part of dv'
@@ -342,7 +373,7 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     else:
         qn, kn, qrs, krs = q, k, None, None
     dvl = torch.empty(B, T, H, V, **bf)
-    _lib.call("natsl_linear_bwd_pre", q.data_ptr(), k.data_ptr(), do.data_ptr(), gcs.data_ptr(), _lib.ptr(qn if l2 else None),
+    _call(timer, "bwd_pre", "natsl_linear_bwd_pre", q.data_ptr(), k.data_ptr(), do.data_ptr(), gcs.data_ptr(), _lib.ptr(qn if l2 else None),
               _lib.ptr(kn if l2 else None), _lib.ptr(qrs), _lib.ptr(krs), dvl.data_ptr(), B, T, H, K, V, float(scale), int(l2), st)
     # ---- 2: reverse walk
     dS_all = torch.empty(B, NT, H, K, V, **bf)
@@ -350,7 +381,7 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     dh0 = torch.empty(B, H, K, V, **f32) if h0 is not None else None
     if dht is not None:
         dht = dht.float().contiguous()
-    _lib.call("natsl_linear_bwd_dh", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(w), do.data_ptr(), dvl.data_ptr(),
+    _call(timer, "bwd_dh", "natsl_linear_bwd_dh", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(w), do.data_ptr(), dvl.data_ptr(),
               gcs.data_ptr(), carry.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
               tables.n_blocks.data_ptr(), _lib.ptr(dht), dS_all.data_ptr(), dvp.data_ptr(), _lib.ptr(dh0), B, T, H, HN, K, V,
               float(scale), st)
@@ -361,7 +392,7 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     dkd = torch.empty(B, T, H, **f32)
     scal = torch.empty(B, NT, H, 4, **f32)
     dn_lin = torch.empty(B, NT, H, **f32)
-    _lib.call("natsl_linear_bwd_state", rule, kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w), u.data_ptr(),
+    _call(timer, "bwd_state", "natsl_linear_bwd_state", rule, kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w), u.data_ptr(),
               do.data_ptr(), dvp.data_ptr(), gcs.data_ptr(), h.data_ptr(), carry.data_ptr(), dS_all.data_ptr(),
               tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(),
               tables.starting_h_idx.data_ptr(), _lib.ptr(vp if gdn else None), _lib.ptr(dw), dq1.data_ptr(), dk1.data_ptr(),
@@ -371,7 +402,7 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     dv = torch.empty_like(v) if gdn else dvp
     dbeta = torch.empty(B, T, H, **f32) if gdn else None
     dg_tok = torch.empty(B, T, H, **f32)
-    _lib.call("natsl_linear_bwd_intra", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w),
+    _call(timer, "bwd_intra", "natsl_linear_bwd_intra", rule, qn.data_ptr(), kn.data_ptr(), _lib.ptr(v if gdn else None), _lib.ptr(w),
               _lib.ptr(u if gdn else None), vp.data_ptr(), _lib.ptr(dvp if gdn else None), _lib.ptr(dw), do.data_ptr(),
               dq1.data_ptr(), dk1.data_ptr(), gcs.data_ptr(), _lib.ptr(beta if gdn else None),
               _lib.DT_BF16 if (gdn and beta.dtype == BF16) else _lib.DT_F32, _lib.ptr(qrs), _lib.ptr(krs), dkd.data_ptr(),
@@ -379,7 +410,7 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
               dg_tok.data_ptr(), scal.data_ptr(), B, T, H, HN, K, V, float(scale), int(l2), st)
     # ---- 5: decay gradients
     dg = torch.empty(B, T, H, **f32)
-    _lib.call("natsl_linear_bwd_dg", dg_tok.data_ptr(), scal.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
+    _call(timer, "bwd_dg", "natsl_linear_bwd_dg", dg_tok.data_ptr(), scal.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
               tables.n_blocks.data_ptr(), dg.data_ptr(), B, T, H, HN, flags, st)
     dnats = dn_lin.view(B, NT, HN, H // HN).sum(-1)
     out = dict(dq=dq, dk=dk, dv=dv, dg=dg, dbeta=dbeta, dh0=dh0, dnats=dnats)
