@@ -956,26 +956,32 @@ linear_bwd_intra_kernel(const __nv_bfloat16* __restrict__ qn, const __nv_bfloat1
 }
 
 // ================================================================================================ dg
-// One CTA (64 threads) per (batch, head): the carried-decay chain over the chunks in reverse, then the reverse
+// One CTA per (batch, head): the carried-decay chain over the chunks in reverse, then the reverse
 // cumsum inside every chunk.  scal [B,NT,H,4] = (ddec, sum dkd, e^{car} <w S, dv'>, sum dE) per chunk.
-__global__ void __launch_bounds__(64)
+constexpr int DG_THREADS = 256;
+__global__ void __launch_bounds__(DG_THREADS)
 linear_bwd_dg_kernel(const float* __restrict__ dg_tok, const float* __restrict__ scal, const int* __restrict__ types_i,
                      const int* __restrict__ indices, const int* __restrict__ n_blocks, float* __restrict__ dg, int T, int H,
                      int HN, int decay, int trailing_quirk) {
     extern __shared__ float s_dgl[];
-    __shared__ float s_tot;
     const int tid = threadIdx.x, lane = tid & 31;
     const int h = blockIdx.x, b = blockIdx.y;
     const int hn = h / (H / HN);
     const int NT = (T + 63) / 64;
     const int TN = NT;
+    // stage the per-chunk scalars in shared memory (parallel loads), then one thread walks the chain
+    float* s_sc = s_dgl + NT;                               // [NT][4]
+    int* s_act = reinterpret_cast<int*>(s_sc + 4 * NT);     // [NT]
+    for (int i = tid; i < 4 * NT; i += DG_THREADS) s_sc[i] = scal[((long)b * NT + i / 4) * H * 4 + (long)h * 4 + (i & 3)];
+    for (int c = tid; c < NT; c += DG_THREADS) s_act[c] = types_i[(((long)b * TN + c) * HN + hn) * 2 + 1] != 0;
+    __syncthreads();
     if (tid == 0) {
         const int nsel = n_blocks[((long)b * HN + hn) * 2 + 1];
         const int last_sel = nsel > 0 ? indices[(((long)b * TN + (nsel - 1)) * HN + hn) * 2 + 1] : -1;
         float dcar = 0.f;                                    // gradient w.r.t. the carry after the chunk
         for (int c = NT - 1; c >= 0; --c) {
-            const float* sc = scal + (((long)b * NT + c) * H + h) * 4;
-            const bool act = types_i[(((long)b * TN + c) * HN + hn) * 2 + 1] != 0;
+            const float* sc = s_sc + 4 * c;
+            const bool act = s_act[c] != 0;
             const bool may_carry = decay && (!trailing_quirk || c < last_sel);
             float dgl;
             if (act) dgl = sc[0] + sc[1];
@@ -985,23 +991,25 @@ linear_bwd_dg_kernel(const float* __restrict__ dg_tok, const float* __restrict__
         }
     }
     __syncthreads();
-    for (int c = 0; c < NT; ++c) {
+    // reverse cumsum inside every chunk: one warp per chunk, two tokens per lane
+    const int warp = tid >> 5;
+    for (int c = warp; c < NT; c += DG_THREADS / 32) {
         const int valid = min(64, T - c * 64);
         const long tok0 = (long)b * T + (long)c * 64;
-        float x = 0.f;
-        if (tid < valid) x = dg_tok[(tok0 + tid) * H + h];
-        if (tid == valid - 1) x += s_dgl[c];
-        // suffix sum over the 64 positions
+        const int ta = 2 * lane, tb2 = 2 * lane + 1;
+        float x0 = ta < valid ? dg_tok[(tok0 + ta) * H + h] : 0.f;
+        float x1 = tb2 < valid ? dg_tok[(tok0 + tb2) * H + h] : 0.f;
+        if (ta == valid - 1) x0 += s_dgl[c];
+        if (tb2 == valid - 1) x1 += s_dgl[c];
+        float sfx = x0 + x1;                                 // inclusive suffix sum of the lanes' pair sums
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const float t = __shfl_down_sync(0xffffffffu, x, o);
-            if (lane + o < 32) x += t;
+            const float t = __shfl_down_sync(0xffffffffu, sfx, o);
+            if (lane + o < 32) sfx += t;
         }
-        if (tid == 32) s_tot = x;                            // total of the upper half
-        __syncthreads();
-        if (tid < 32) x += s_tot;
-        if (tid < valid) dg[(tok0 + tid) * H + h] = x;
-        __syncthreads();
+        const float after = sfx - (x0 + x1);                 // everything behind this lane's pair
+        if (ta < valid) dg[(tok0 + ta) * H + h] = x0 + x1 + after;
+        if (tb2 < valid) dg[(tok0 + tb2) * H + h] = x1 + after;
     }
 }
 
@@ -1185,10 +1193,10 @@ extern "C" int natsl_linear_bwd_dg(const float* dg_tok, const float* scal, const
     NATSL_REQUIRE(B > 0 && T > 0 && H > 0 && HN > 0 && H % HN == 0 && B <= 65535, NATSL_ERR_BAD_SHAPE,
                   "natsl_linear_bwd_dg: bad shape");
     const int NT = (T + 63) / 64;
-    NATSL_REQUIRE(NT * 4 <= 48 * 1024, NATSL_ERR_TOO_LARGE, "natsl_linear_bwd_dg: T=%d is too long", T);
+    NATSL_REQUIRE(NT * 24 <= 48 * 1024, NATSL_ERR_TOO_LARGE, "natsl_linear_bwd_dg: T=%d is too long", T);
     const int decay = (flags & NATSL_FLAG_DECAY_SKIPPED) ? 1 : 0;
     const int quirk = (flags & NATSL_FLAG_NO_TRAILING_QUIRK) ? 0 : 1;
-    linear_bwd_dg_kernel<<<dim3(H, B), 64, NT * 4, reinterpret_cast<cudaStream_t>(stream)>>>(dg_tok, scal, types_i, indices,
+    linear_bwd_dg_kernel<<<dim3(H, B), DG_THREADS, NT * 24, reinterpret_cast<cudaStream_t>(stream)>>>(dg_tok, scal, types_i, indices,
                                                                                            n_blocks, dg, T, H, HN, decay, quirk);
     return check_launch("natsl_linear_bwd_dg");
 }
