@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import contextlib
 import functools
+import os
 
 import torch
 import torch.distributed as dist
@@ -349,7 +350,8 @@ class GraphedMambaSP:
     At this scale a rank's share is a few hundred microseconds of GPU work, less than the host needs to issue the
     ~100 small launches of the eager function.  The plan binds to the caller's tensors (update their contents in
     place between runs), sizes the key/value gather from ``kv_capacity`` (see ``nats_mixed_attn_mamba_sp``) and
-    captures the compute in four CUDA graphs; the five NCCL all-gathers stay eager, between the graphs:
+    captures the compute in four CUDA graphs; the NCCL all-gathers (two group calls: counts + keys + values, and the
+    (a, S) pairs) stay eager, between the graphs:
 
         graph A  tables, block counts, packed selected (block, head) pairs
         gather   counts, packed keys, packed values          (asynchronous, default group; runs under B, C)
@@ -466,6 +468,7 @@ class GraphedMambaSP:
                                    own, rem_base, cap)
             st['out'] = (st['o_lin'], _merge(o_attn, B, n_seg), st['final'])
 
+        self.coalesce = os.environ.get("NATSL_SP_COALESCE", "1") == "1"
         self._stages = (stage_a, stage_b, stage_c, stage_d)
         self._st = st
         self._graphs = None
@@ -476,6 +479,20 @@ class GraphedMambaSP:
     def _gather(self, out, inp, group):
         return dist.all_gather_into_tensor(out.view((-1,) + tuple(out.shape[2:])), inp, group=group, async_op=True)
 
+    def _gather_many(self, pairs, group):
+        """Several all-gathers as one group call (one launch on the communicator's stream instead of one per tensor);
+        falls back to one call per tensor where the backend has no grouped form.  -> list of handles with wait()."""
+        manager = getattr(dist, "_coalescing_manager", None)
+        if manager is not None and self.coalesce:
+            try:
+                with manager(group=group, async_ops=True) as cm:
+                    for out, inp in pairs:
+                        dist.all_gather_into_tensor(out.view((-1,) + tuple(out.shape[2:])), inp, group=group)
+                return [cm]
+            except (RuntimeError, ValueError, NotImplementedError):
+                self.coalesce = False
+        return [self._gather(out, inp, group) for out, inp in pairs]
+
     def _issue(self, a, b, c, d, first=False):
         """One step: the key/value gather (default group) runs under the whole linear branch, whose own small
         gather goes through ``linear_group``; the attention starts when the keys have arrived."""
@@ -484,13 +501,12 @@ class GraphedMambaSP:
         if first:
             for dst, src in (('n_all', 'n_loc'), ('k_all', 'pk'), ('v_all', 'pv')):
                 st[dst] = torch.empty((self.world,) + tuple(st[src].shape), dtype=st[src].dtype, device=self.dev)
-        kv = [self._gather(st['n_all'], st['n_loc'], self.group), self._gather(st['k_all'], st['pk'], self.group),
-              self._gather(st['v_all'], st['pv'], self.group)]
+        kv = self._gather_many([(st['n_all'], st['n_loc']), (st['k_all'], st['pk']), (st['v_all'], st['pv'])], self.group)
         b()
         if first:
             st['a_all'] = torch.empty((self.world,) + tuple(st['a_seg'].shape), dtype=torch.float32, device=self.dev)
             st['S_all'] = torch.empty((self.world,) + tuple(st['S_seg'].shape), dtype=torch.float32, device=self.dev)
-        lin = [self._gather(st['a_all'], st['a_seg'], self.lin_group), self._gather(st['S_all'], st['S_seg'], self.lin_group)]
+        lin = self._gather_many([(st['a_all'], st['a_seg']), (st['S_all'], st['S_seg'])], self.lin_group)
         if self.gather_under_linear:
             for h in lin:
                 h.wait()
