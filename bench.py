@@ -504,7 +504,7 @@ def mamba_long_segment(sid: int, n_glob: int, L: int):
 
 def mamba_long_parity(o_m, o_a, ids, n_glob: int, L: int, heads: int = 2, win: int = 128):
     """Rank 0: regenerates the whole sequence on the host (every segment from its seed), evaluates the oracle for
-    ``heads`` heads, and compares one ``win``-token window at the start of this rank's last local segment (linear branch:
+    ``heads`` heads, and compares the last ``win`` tokens of this rank's last local segment (linear branch:
     chunk form over the whole sequence; softmax branch: masked SDPA for the window's queries against all keys)."""
     from oracle import attn as oattn
     from oracle import gdn as ogdn
@@ -516,8 +516,8 @@ def mamba_long_parity(o_m, o_a, ids, n_glob: int, L: int, heads: int = 2, win: i
     g, types = cat("g").contiguous(), cat("types").contiguous()
     o_ref, _ = ogdn.linear_chunk(q, k, v, g, None, types[..., 1], nbs=nbs, scale=1.0, decay=True, use_l2norm=False,
                                  rule="mamba", reference_trailing_carry=False)
-    t0 = ids[-1] * L                                              # global position of the window
-    loc = (len(ids) - 1) * L                                      # its position in this rank's tensors
+    t0 = (ids[-1] + 1) * L - win                                  # the last tokens of the rank's last segment (global)
+    loc = len(ids) * L - win                                      # their position in this rank's tensors
     mask = oattn.attn_mask_rows(types[..., 0], T, nbs, heads, t0, t0 + win)
     oa_ref, _ = oattn.attn_sdpa(q[:, t0:t0 + win], k, v, mask, K ** -0.5)
     err_l = float((o_m[:, loc:loc + win, :heads].float().cpu() - o_ref[:, t0:t0 + win]).abs().max())
@@ -570,6 +570,22 @@ def mamba_long_measure(args, rank: int, world: int, dev, group=None, lin_group=N
         mode = "eager, caller-given gather capacity (no host synchronisation)"
         for _ in range(3):
             out = step()
+        barrier()
+    if world == 1 and not args.sp_plain_op and not args.sp_eager_one_gpu:
+        # one GPU: the whole step (no collective, no host read) replays from one CUDA graph, so that the figure is the
+        # device time of the step and not the host's launch rate
+        gr = torch.cuda.CUDAGraph()
+        holder = {}
+        with torch.cuda.graph(gr):
+            holder["out"] = step()
+        torch.cuda.synchronize(dev)
+
+        def run_step():
+            gr.replay()
+            return holder["out"]
+        mode = "one CUDA graph for the whole step"
+        for _ in range(3):
+            out = run_step()
         barrier()
     if plan and world > 1:
         # plan / replay: the compute stages replay from CUDA graphs, the all-gathers stay eager between them
@@ -934,6 +950,8 @@ def main():
     ap.add_argument("--sp-fixed-capacity", action="store_true",
                     help="mamba_long: size the key/value gather from a capacity fixed before the timed region instead of "
                          "reading the block counts back every step")
+    ap.add_argument("--sp-eager-one-gpu", action="store_true",
+                    help="mamba_long on one GPU: issue the step eagerly instead of replaying it from a CUDA graph")
     ap.add_argument("--sp-plain-op", action="store_true",
                     help="mamba_long on one GPU through nats_mixed_attn_mamba (no sub-segment split, one stream)")
     ap.add_argument("--workload", default="gdn_layer", choices=["gdn_layer", "gdn_layer_fwdbwd", "mamba_long", "model_prefill", "model_fwdbwd"],
