@@ -135,9 +135,9 @@ class _ShortConvFn(torch.autograd.Function):
 
 class ShortConvolution(nn.Conv1d):
     """Depthwise causal conv1d over time followed by SiLU; returns (y, final_state)
-    (src/nats/layers/natsl_attn_gdn.py:329-348, 430-447).  x: [B, T, D].  CUDA bf16 inputs with kernel size 4 and no
-    cache run ``natsl_short_conv_fwd`` / ``natsl_short_conv_bwd``; decoding with a cache (a few tokens) and other
-    inputs take PyTorch's conv1d."""
+    (src/nats/layers/natsl_attn_gdn.py:329-348, 430-447).  x: [B, T, D].  CUDA bf16 inputs with kernel size 4 run
+    ``natsl_short_conv_fwd`` / ``natsl_short_conv_bwd`` (with a cache: over the cached tail followed by the new tokens);
+    other inputs take PyTorch's conv1d."""
 
     def __init__(self, hidden_size: int, kernel_size: int, bias: bool = False, activation: Optional[str] = 'silu'):
         super().__init__(hidden_size, hidden_size, kernel_size, groups=hidden_size, bias=bias, padding=kernel_size - 1)
@@ -156,8 +156,13 @@ class ShortConvolution(nn.Conv1d):
             if cache is not None:
                 xt = torch.cat([cache.to(xt.dtype), xt], -1)
             final = F.pad(xt, (max(0, W - xt.shape[-1]), 0))[..., -W:].contiguous()
-        if cache is None and _kernel_ok(x) and W == 4 and D % 8 == 0:
-            return _ShortConvFn.apply(x.contiguous(), self.weight, self.bias, silu), final
+        if _kernel_ok(x) and W == 4 and D % 8 == 0:
+            if cache is None:
+                return _ShortConvFn.apply(x.contiguous(), self.weight, self.bias, silu), final
+            # decoding: the cached tail in front of the new tokens, so that every output is computed from the same four
+            # inputs in the same order as in a one-shot pass (bit-identical q, k, v between the two)
+            xc = torch.cat([cache[..., 1 - W:].transpose(1, 2).to(x.dtype), x], 1).contiguous()
+            return _ShortConvFn.apply(xc, self.weight, self.bias, silu)[:, W - 1:].contiguous(), final
         xt = x.transpose(1, 2)
         if cache is not None:
             xt = torch.cat([cache.to(xt.dtype), xt], -1)

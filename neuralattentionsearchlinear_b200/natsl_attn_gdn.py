@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .mixed_attn_gdn import nats_mixed_attn_gdn, nats_mixed_attn_gdn_chunk_inference, nats_mixed_attn_gdn_recurrent
+from .decoding import forward_cached
 from .modules import FusedMultiInputRMSNormGated, RMSNorm, ShortConvolution, hard_softmax, mean_pooling
 
 
@@ -272,90 +273,32 @@ class NeuralAttentionSearchLinearAttnGDN(nn.Module):
         return o, None, past_key_values
 
     # ------------------------------------------------------------------------------------------------ decoding
-    @torch.no_grad()
-    def _forward_cached(self, hidden_states: torch.Tensor, past_key_values):
-        """Prefill into an empty cache (64 tokens or more, chunk kernels) or a decoding step of fewer than 64 tokens
-        (token recurrence with re-roll + masked attention over the cached keys), natsl_attn_gdn.py:389-410, 576-650."""
-        if self.layer_idx is None:
-            raise ValueError("a layer used with a cache needs its layer_idx")
-        if self.ops_for_incomplete_chunks == 'attn' or not self.incomplete_block_start_with_ht:
-            raise NotImplementedError("decoding is built for the modes 'all' and 'gated_delta_net'")
-        cache = past_key_values.layer(self.layer_idx, self.nats_block_size)
-        B, T, _ = hidden_states.shape
-        nbs = self.nats_block_size
-        own_attn = self.ops_for_incomplete_chunks != 'gated_delta_net'
-        if cache.n_tokens == 0 and T >= 64:
-            p = self.project(hidden_states, want_conv_state=True)
-            o_gd, o_attn, ht, start = nats_mixed_attn_gdn_chunk_inference(
+    def _ops_for_cache(self) -> dict:
+        """The two ops the cached forward (``decoding.forward_cached``) runs for this layer."""
+        common = dict(nats_block_size=self.nats_block_size, ops_for_incomplete_chunks=self.ops_for_incomplete_chunks,
+                      output_final_state_gated_delta=True, decay_for_non_gdn_blocks=self.decay_for_non_gdn_blocks,
+                      incomplete_block_start_with_ht=True, use_g_for_attn=self.usg_for_attn, lattn_use_qk_l2norm_in_kernel=True)
+
+        def chunk(p, T):
+            return nats_mixed_attn_gdn_chunk_inference(
                 q_attn=p['q_attn'], k_attn=p['k_attn'], v_attn=p['v_attn'], q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
                 initial_state_gated_delta_chunk_start=None, g=p['g'], beta=p['beta'], nats_block_types=p['types'],
-                op_type_last_chunk=p['op_type_last'] if T % nbs == 0 else None, n_nats_blocks=p['n_blocks'],
-                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, nats_block_size=nbs,
-                ops_for_incomplete_chunks=self.ops_for_incomplete_chunks, output_final_state_gated_delta=True,
-                decay_for_non_gdn_blocks=self.decay_for_non_gdn_blocks, incomplete_block_start_with_ht=True,
-                use_g_for_attn=self.usg_for_attn, lattn_use_qk_l2norm_in_kernel=True)
-            r, n_done = T % nbs, T // nbs
-            cache.append_kv(p['k_attn'].contiguous(), p['v_attn'].contiguous())
-            if n_done:
-                cache.append_types(p['types_raw'][:, :n_done].contiguous())
-            cache.state_block_start = start
-            cache.state = start.clone() if r == 0 else ht
-            H = p['g'].shape[2]
-            cache.g_block = (p['g'][:, T - r:].float().sum(1) if r else torch.zeros(B, H, device=hidden_states.device))
-            cache.pool_sum = (hidden_states[:, T - r:].float().sum(1) if r
-                              else torch.zeros(B, hidden_states.shape[2], device=hidden_states.device))
-            cache.conv_state = p['conv_state']
-            cache.n_tokens = T
-            return self.mix(hidden_states, o_gd, o_attn, p['o_weights']), None, past_key_values
-        if T >= 64:
-            raise NotImplementedError("continuing a prefill of 64 tokens or more into a filled cache is not built; "
-                                      "feed the continuation in pieces of fewer than 64 tokens")
-        if cache.n_tokens == 0:                                 # a short prompt: start from empty states
-            dev = hidden_states.device
-            H, K, V = self.num_heads, self.head_k_dim, self.head_v_dim
-            cache.state = torch.zeros(B, H, K, V, device=dev)
-            cache.state_block_start = torch.zeros(B, H, K, V, device=dev)
-            cache.g_block = torch.zeros(B, H, device=dev)
-            cache.pool_sum = torch.zeros(B, hidden_states.shape[2], device=dev)
-        outs_l, outs_a, weights = [], [], []
-        a = 0
-        while a < T:
-            t_off = cache.n_tokens % nbs
-            b_ = min(T, a + (nbs - t_off))                      # a piece never crosses a block boundary
-            hs = hidden_states[:, a:b_]
-            n = b_ - a
-            completes = (t_off + n) == nbs
-            cache.pool_sum = cache.pool_sum + hs.float().sum(1)
-            if completes:
-                pooled = (cache.pool_sum / nbs).to(hs.dtype)[:, None, :]
-                types_new = self.select(pooled)                  # decided once the block's last token is known
-            else:
-                types_new = torch.ones(B, 1, self.num_nats_head, self.n_ops, device=hs.device, dtype=hs.dtype)
-            p = self.project_qkv(hs, conv_state=cache.conv_state, want_conv_state=True)
-            cache.append_kv(p['k_attn'].contiguous(), p['v_attn'].contiguous())
-            msk = cache.generate_msk(n, self.num_attn_heads, own_chunk=own_attn)
-            o_gd, o_attn, state, start = nats_mixed_attn_gdn_recurrent(
+                op_type_last_chunk=p['op_type_last'] if T % self.nats_block_size == 0 else None, n_nats_blocks=p['n_blocks'],
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, **common)
+
+        def step(p, cache, msk, types_new, t_off):
+            return nats_mixed_attn_gdn_recurrent(
                 q_attn=p['q_attn'], k_attn=cache.k_attn, v_attn=cache.v_attn, q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
                 attn_msk=msk, initial_state_gated_delta=cache.state,
                 initial_state_gated_delta_chunk_start=cache.state_block_start, g=p['g'], g_cumsum=cache.g_block,
                 beta=p['beta'], nats_block_types=types_new, n_tokens_in_current_block=t_off,
-                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, nats_block_size=nbs,
-                ops_for_incomplete_chunks=self.ops_for_incomplete_chunks, output_final_state_gated_delta=True,
-                decay_for_non_gdn_blocks=self.decay_for_non_gdn_blocks, incomplete_block_start_with_ht=True,
-                use_g_for_attn=self.usg_for_attn, lattn_use_qk_l2norm_in_kernel=True)
-            cache.state, cache.state_block_start = state, start
-            if completes:
-                cache.append_types(types_new)
-                cache.g_block = torch.zeros_like(cache.g_block)
-                cache.pool_sum = torch.zeros_like(cache.pool_sum)
-            else:
-                cache.g_block = cache.g_block + p['g'].float().sum(1)
-            cache.conv_state = p['conv_state']
-            cache.n_tokens += n
-            outs_l.append(o_gd)
-            outs_a.append(o_attn)
-            weights.append(p['o_weights'])
-            a = b_
-        o_gd, o_attn = torch.cat(outs_l, 1), torch.cat(outs_a, 1)
-        o_w = torch.cat(weights, 1) if weights[0] is not None else None
-        return self.mix(hidden_states, o_gd, o_attn, o_w), None, past_key_values
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=p['k'].shape[-1] ** -0.5, **common)
+
+        return dict(chunk=chunk, step=step)
+
+    def _forward_cached(self, hidden_states: torch.Tensor, past_key_values):
+        """Prefill into an empty cache (64 tokens or more, chunk kernels) or a decoding step of fewer than 64 tokens
+        (token recurrence with re-roll + masked attention over the cached keys), natsl_attn_gdn.py:389-410, 576-650."""
+        o_gd, o_attn, o_w = forward_cached(self, hidden_states, past_key_values)
+        with torch.no_grad():
+            return self.mix(hidden_states, o_gd, o_attn, o_w), None, past_key_values

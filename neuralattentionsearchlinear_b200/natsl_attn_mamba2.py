@@ -3,7 +3,8 @@ constructor arguments, parameter names and forward signature of the reference la
 (src/nats/layers/natsl_attn_mamba2.py:66-599).  q = C and k = B are L2-normalised by the layer,
 dt = softplus(a_proj + dt_bias), v <- v * dt, g = -exp(A_log) * dt (natsl_attn_mamba2.py:469-474).
 
-Built: full-sequence prefill (``mode='chunk'``, no cache); forward returns the projected output like the reference.
+Built: full-sequence training / prefill (``mode='chunk'``) and, with a ``NAtSCache`` in ``cache_params``, prefill into the
+cache followed by decoding steps of fewer than 64 tokens; forward returns the projected output like the reference.
 """
 from __future__ import annotations
 
@@ -14,7 +15,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .mixed_attn_mamba import nats_mixed_attn_mamba, nats_mixed_attn_mamba_chunk_inference
+from .decoding import forward_cached
+from .mixed_attn_mamba import (nats_mixed_attn_mamba, nats_mixed_attn_mamba_chunk_inference,
+                               nats_mixed_attn_mamba_recurrent)
 from .modules import FusedMultiInputRMSNormGated, L2Norm, RMSNorm, ShortConvolution, hard_softmax, mean_pooling
 
 
@@ -126,23 +129,28 @@ class NeuralAttentionSearchLinearAttnMamba(nn.Module):
         self.o_proj = nn.Linear(self.value_dim, hidden_size, bias=False)
         self.attn_fraction = torch.zeros(1)
 
-    def project(self, hidden_states: torch.Tensor) -> dict:
-        """natsl_attn_mamba2.py:355-474."""
-        B, T, dim = hidden_states.shape
-        hs_reduced = self.pooling_func(hidden_states.unsqueeze(-2), chunk_size=self.nats_block_size).view(B, -1, dim)
-        logits = self.nats_layer(hs_reduced).unflatten(-1, (self.num_nats_head, self.n_ops))
-        types = self.nats_sample_func(logits)
+    def select(self, pooled: torch.Tensor) -> torch.Tensor:
+        """Block-mean layer input [B, NB, D] -> sampled 0/1 block types [B, NB, HN, n_ops] (natsl_attn_mamba2.py:352-365)."""
+        logits = self.nats_layer(pooled).unflatten(-1, (self.num_nats_head, self.n_ops))
+        return self.nats_sample_func(logits)
+
+    def project_qkv(self, hidden_states: torch.Tensor, conv_state=None, want_conv_state: bool = False) -> dict:
+        """q = C, k = B, v = x * dt of the linear branch, q/k/v of the softmax branch, the mixing weights and the log decay
+        from the layer input (natsl_attn_mamba2.py:366-474).  ``conv_state``: the (q, k, v) convolution tails of a cache."""
+        cq, ck, cv = conv_state if conv_state is not None else (None, None, None)
+        new_state = None
         if self.use_short_conv:
             if self.attn_with_short_conv:
-                q, _ = self.q_conv1d(self.q_proj(hidden_states))
-                k, _ = self.k_conv1d(self.k_proj(hidden_states))
-                v, _ = self.v_conv1d(self.v_proj(hidden_states))
+                q, sq = self.q_conv1d(self.q_proj(hidden_states), cache=cq, output_final_state=want_conv_state)
+                k, sk = self.k_conv1d(self.k_proj(hidden_states), cache=ck, output_final_state=want_conv_state)
+                v, sv = self.v_conv1d(self.v_proj(hidden_states), cache=cv, output_final_state=want_conv_state)
                 q_attn, k_attn, v_attn = q, k, v
             else:
                 q_attn, k_attn, v_attn = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
-                q, _ = self.q_conv1d(q_attn)
-                k, _ = self.k_conv1d(k_attn)
-                v, _ = self.v_conv1d(v_attn)
+                q, sq = self.q_conv1d(q_attn, cache=cq, output_final_state=want_conv_state)
+                k, sk = self.k_conv1d(k_attn, cache=ck, output_final_state=want_conv_state)
+                v, sv = self.v_conv1d(v_attn, cache=cv, output_final_state=want_conv_state)
+            new_state = (sq, sk, sv)
         else:
             if self.attn_with_short_conv:
                 q, k, v = (F.silu(p(hidden_states)) for p in (self.q_proj, self.k_proj, self.v_proj))
@@ -165,13 +173,45 @@ class NeuralAttentionSearchLinearAttnMamba(nn.Module):
         dt = F.softplus(self.a_proj(hidden_states).float() + self.dt_bias)
         v = (v * dt.unsqueeze(-1)).to(v.dtype)
         g = -self.A_log.float().exp() * dt
-        types = types.clone()
+        return dict(q=q, k=k, v=v, q_attn=q_attn, k_attn=k_attn, v_attn=v_attn, g=g, o_weights=o_weights,
+                    conv_state=new_state)
+
+    def project(self, hidden_states: torch.Tensor, want_conv_state: bool = False) -> dict:
+        """Everything the hybrid-attention op consumes, computed from the layer input (natsl_attn_mamba2.py:355-474)."""
+        B, T, dim = hidden_states.shape
+        hs_reduced = self.pooling_func(hidden_states.unsqueeze(-2), chunk_size=self.nats_block_size).view(B, -1, dim)
+        types_raw = self.select(hs_reduced)
+        p = self.project_qkv(hidden_states, want_conv_state=want_conv_state)
+        types = types_raw.clone()
         op_type_last = types[:, -1].clone()
         types[:, -1] = 1
         n_blocks = types.int().sum(1)
         self.attn_fraction = (n_blocks.float()[..., 0] / types.shape[1]).mean(0).detach()
-        return dict(q=q, k=k, v=v, q_attn=q_attn, k_attn=k_attn, v_attn=v_attn, g=g, types=types, n_blocks=n_blocks,
-                    o_weights=o_weights, op_type_last=op_type_last)
+        p.update(types=types, types_raw=types_raw, n_blocks=n_blocks, op_type_last=op_type_last)
+        return p
+
+    # ------------------------------------------------------------------------------------------------ decoding
+    def _ops_for_cache(self) -> dict:
+        """The two ops the cached forward (``decoding.forward_cached``) runs for this layer."""
+        common = dict(nats_block_size=self.nats_block_size, ops_for_incomplete_chunks=self.ops_for_incomplete_chunks,
+                      output_final_state_mamba=True, decay_for_non_mamba_blocks=self.decay_for_non_mamba_blocks,
+                      incomplete_block_start_with_ht=True, use_g_for_attn=self.usg_for_attn, scale_lattn=1)
+
+        def chunk(p, T):
+            return nats_mixed_attn_mamba_chunk_inference(
+                q_attn=p['q_attn'], k_attn=p['k_attn'], v_attn=p['v_attn'], q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
+                initial_state_mamba_start=None, g=p['g'], nats_block_types=p['types'],
+                op_type_last_chunk=p['op_type_last'] if T % self.nats_block_size == 0 else None, n_nats_blocks=p['n_blocks'],
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, **common)
+
+        def step(p, cache, msk, types_new, t_off):
+            return nats_mixed_attn_mamba_recurrent(
+                q_attn=p['q_attn'], k_attn=cache.k_attn, v_attn=cache.v_attn, q_lattn=p['q'], k_lattn=p['k'], v_lattn=p['v'],
+                attn_msk=msk, initial_state_mamba=cache.state, initial_state_mamba_chunk_start=cache.state_block_start,
+                g=p['g'], g_cumsum=cache.g_block, nats_block_types=types_new, n_tokens_in_current_block=t_off,
+                scale_attn=p['k_attn'].shape[-1] ** -0.5, **common)
+
+        return dict(chunk=chunk, step=step)
 
     def mix(self, hidden_states, o_mamba, o_attn, o_weights):
         g = self.g_proj(hidden_states)
@@ -192,11 +232,15 @@ class NeuralAttentionSearchLinearAttnMamba(nn.Module):
     ):
         if attention_mask is not None:
             assert len(attention_mask.shape) == 2
-        if cache_params is not None or kwargs.get('cu_seqlens', None) is not None:
-            raise NotImplementedError("decoding with a NAtSCache / variable-length batches are not built")
+        if kwargs.get('cu_seqlens', None) is not None:
+            raise NotImplementedError("variable-length batches are not built")
         B, T, _ = hidden_states.shape
+        if cache_params is not None:                        # prefill into / decode from a NAtSCache
+            o_m, o_attn, o_w = forward_cached(self, hidden_states, cache_params)
+            with torch.no_grad():
+                return self.mix(hidden_states, o_m, o_attn, o_w)
         if T < 64 or self.mode != 'chunk':
-            raise NotImplementedError("the fused_recurrent (decode) mode is not built")
+            raise NotImplementedError("fewer than 64 tokens (decoding) need a NAtSCache in cache_params")
         p = self.project(hidden_states)
         common = dict(scale_attn=p['k_attn'].shape[-1] ** -0.5, scale_lattn=1, cu_seqlens=None, cu_seqlens_nats=None,
                       nats_block_size=self.nats_block_size, ops_for_incomplete_chunks=self.ops_for_incomplete_chunks,

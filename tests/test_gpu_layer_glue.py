@@ -103,3 +103,22 @@ def test_swiglu_and_block_mean():
     (pr * dyp.double()).sum().backward()
     close(p, pr, "block mean")
     close(xg.grad, xr.grad, "d(block mean)")
+
+
+def test_short_conv_with_cache_is_bit_identical_to_one_pass():
+    """Decoding feeds the convolution piece by piece with the cached tail; every output must equal the one-pass output bit
+    for bit (the linear branch's q, k, v are then the same in both, whatever the conditioning of what follows)."""
+    from neuralattentionsearchlinear_b200.modules import ShortConvolution
+    torch.manual_seed(5)
+    conv = ShortConvolution(256, 4, bias=False, activation='silu').cuda().bfloat16()
+    x = torch.randn(2, 150, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        full, fin = conv(x, output_final_state=True)
+        outs, state, t = [], None, 0
+        for n in (70, 1, 1, 5, 2, 64, 7):
+            y, state = conv(x[:, t:t + n], cache=state, output_final_state=True)
+            outs.append(y)
+            t += n
+    assert t == 150
+    assert torch.equal(torch.cat(outs, 1), full)
+    assert torch.equal(state, fin)

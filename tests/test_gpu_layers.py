@@ -98,5 +98,7 @@ def test_layers_refuse_unbuilt_paths():
         layer(torch.randn(1, 128, 128, device="cuda", dtype=torch.bfloat16), past_key_values=nat.NAtSCache())
     mamba = nat.NeuralAttentionSearchLinearAttnMamba(hidden_size=128, expand_v=1, head_dim=64, num_heads=2,
                                                      num_attn_heads=2).cuda().bfloat16()
-    with pytest.raises(NotImplementedError):             # the Mamba2 layer decodes through its recurrent op only
+    with pytest.raises(ValueError):
         mamba(torch.randn(1, 128, 128, device="cuda", dtype=torch.bfloat16), cache_params=nat.NAtSCache())
+    with pytest.raises(NotImplementedError):             # fewer than 64 tokens without a cache
+        mamba(x)
