@@ -276,7 +276,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- per-kernel durations: each stage launched `steps` times back to back on the same stream between two
     # CUDA events (the queue stays full, so the events bracket device time, not host launch latency)
-    names = ["tables", "attn_fwd", "gdn_prep", "walk_fused", "walk_vsplit", "scan_fwd_h", "out_fwd_o"]
+    names = ["tables", "attn_fwd", "gdn_prep", "gdn_prep_mma_sync", "walk_fused", "walk_vsplit", "scan_fwd_h", "out_fwd_o"]
     NT = T // 64
     tb = nat.build_selection_tables(d["types"], T, nbs)
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
@@ -293,9 +293,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     stages = {
         "tables": lambda: nat.build_selection_tables(d["types"], T, nbs),
         "attn_fwd": lambda: _ops.attn_fwd(d["q"], d["k"], d["v"], tb, K ** -0.5, True),
-        "gdn_prep": lambda: _lib.call("natsl_gdn_chunk_prep_ex", d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
+        "gdn_prep": lambda: _lib.call(_ops.prep_entry(K, V), d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(),
                                       d["g"].data_ptr(), d["beta"].data_ptr(), _lib.DT_BF16, w.data_ptr(), u.data_ptr(),
                                       gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(), pmat.data_ptr(), B, T, H, K, V, 1, sp),
+        "gdn_prep_mma_sync": lambda: _lib.call("natsl_gdn_chunk_prep_ex", d["q"].data_ptr(), d["k"].data_ptr(),
+                                               d["v"].data_ptr(), d["g"].data_ptr(), d["beta"].data_ptr(), _lib.DT_BF16,
+                                               w.data_ptr(), u.data_ptr(), gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(),
+                                               pmat.data_ptr(), B, T, H, K, V, 1, sp),
         "walk_fused": lambda: _lib.call("natsl_gdn_walk_fused", d["q"].data_ptr(), d["k"].data_ptr(), w.data_ptr(),
                                         u.data_ptr(), pmat.data_ptr(), gcs.data_ptr(), krs.data_ptr(), qrs.data_ptr(),
                                         tb.types_i.data_ptr(), tb.indices.data_ptr(), tb.n_blocks.data_ptr(), None,
@@ -436,7 +440,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "walk_fused": ("hbm", n_tok * (3 * K + V + 64) * 2 + n_tok * V * 2, "gdn_walk_tc_kernel"),
         "walk_vsplit": ("hbm", n_tok * (3 * K + V + 64) * 2 + n_tok * V * 2, "gdn_walk_half_kernel"),
         "attn_fwd": ("tensor", attention_tile_flops(host["types"], H, K, V), "attn_fwd_tc_kernel<128,128>"),
-        "gdn_prep": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (K + V + 64) * 2 + n_tok * 18, "gdn_prep_kernel<128,128>"),
+        "gdn_prep": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (K + V + 64) * 2 + n_tok * 18,
+                     "gdn_prep_tc_kernel" if _ops.prep_entry(K, V).endswith("_tc") else "gdn_prep_kernel<128,128>"),
+        "gdn_prep_mma_sync": ("hbm", n_tok * (2 * K + V) * 2 + n_tok * (K + V + 64) * 2 + n_tok * 18, "gdn_prep_kernel<128,128>"),
         "scan_fwd_h": ("hbm", frac_lin * n_tok * (2 * K + V) * 2 + state_bytes, "linear_scan_kernel<128,32,gdn>"),
         "out_fwd_o": ("hbm", n_tok * (3 * K + V) * 2 + state_bytes + n_tok * V * 2, "linear_out_kernel<128,128,gdn>"),
     }

@@ -155,6 +155,14 @@ int natsl_gdn_chunk_prep_ex(const void* q, const void* k, const void* v, const f
                             int beta_dtype, void* w, void* u, float* gcs, float* k_rstd, float* q_rstd, void* pmat,
                             int B, int T, int H, int K, int V, int use_l2norm, void* stream);
 
+/* The same preparation on tcgen05 for K = V = 128 (other head dims: natsl_gdn_chunk_prep_ex): TMA tile loads, one stacked
+ * [k ; q] k^T product into TMEM, (I + A)^-1 formed like the reference's solve_tril (fp32 diagonal blocks, block
+ * recursion below them) and applied as one product with the raw v / k tiles as operands.  Same arguments and outputs.
+ * Replaces the same reference functions as natsl_gdn_chunk_prep / natsl_gdn_chunk_prep_ex. */
+int natsl_gdn_chunk_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                            int beta_dtype, void* w, void* u, float* gcs, float* k_rstd, float* q_rstd, void* pmat,
+                            int B, int T, int H, int K, int V, int use_l2norm, void* stream);
+
 /* State recurrence and chunk output in one walk on tcgen05 (state kept in TMEM, never written to memory):
  * inputs from natsl_gdn_chunk_prep_ex, outputs o [B,T,H,V] bf16 and ht [B,H,K,V] fp32 (or NULL).
  * Built for K = V = 128 and nats_block_size = 64.

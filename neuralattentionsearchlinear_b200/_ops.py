@@ -14,6 +14,13 @@ USE_FUSED_WALK = True        # K = V = 128, block 64: recurrence + output fused 
 # Off by default: measured alone it is no faster than the one-CTA walk (0.204 vs 0.189 ms at B=8, T=4096, H=16), and
 # the kernels of the two branches do not overlap in practice (the block scheduler drains one grid before the next).
 WALK_VSPLIT = os.environ.get("NATSL_WALK_VSPLIT", "0") == "1"
+# chunk preparation on tcgen05 for K = V = 128 (natsl_gdn_chunk_prep_tc); "0" keeps the mma.sync kernel for every shape
+PREP_TC = os.environ.get("NATSL_PREP_TC", "1") != "0"
+
+
+def prep_entry(K: int, V: int) -> str:
+    """Name of the chunk-preparation entry point for these head dims (both take the arguments of ``..._prep_ex``)."""
+    return "natsl_gdn_chunk_prep_tc" if (PREP_TC and K == 128 and V == 128) else "natsl_gdn_chunk_prep_ex"
 
 
 def _need(cond: bool, msg: str, exc=ValueError):
@@ -137,7 +144,7 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
         krstd = torch.empty(B, T, H, dtype=torch.float32, device=dev)
         qrstd = torch.empty(B, T, H, dtype=torch.float32, device=dev) if fused else None
         pmat = torch.empty(B, T, H, 64, dtype=BF16, device=dev) if fused else None
-        _lib.call("natsl_gdn_chunk_prep_ex", q.data_ptr() if fused else None, k.data_ptr(), v.data_ptr(), g.data_ptr(),
+        _lib.call(prep_entry(K, V), q.data_ptr() if fused else None, k.data_ptr(), v.data_ptr(), g.data_ptr(),
                   beta.data_ptr(), _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(),
                   gcs.data_ptr(), krstd.data_ptr(), _lib.ptr(qrstd), _lib.ptr(pmat), B, T, H, K, V, int(use_l2norm), st)
     else:
@@ -351,9 +358,9 @@ def linear_bwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
         _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
         w, u = torch.empty(B, T, H, K, **bf), torch.empty(B, T, H, V, **bf)
         krs0 = torch.empty(B, T, H, **f32)
-        _call(timer, "recompute_prep", "natsl_gdn_chunk_prep", k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        _call(timer, "recompute_prep", prep_entry(K, V), None, k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
                   _lib.DT_BF16 if beta.dtype == BF16 else _lib.DT_F32, w.data_ptr(), u.data_ptr(), gcs.data_ptr(),
-                  krs0.data_ptr(), B, T, H, K, V, int(use_l2norm), st)
+                  krs0.data_ptr(), None, None, B, T, H, K, V, int(use_l2norm), st)
     else:
         w, u, krs0 = None, v, None
         _call(timer, "recompute_prep", "natsl_chunk_local_cumsum", g.data_ptr(), gcs.data_ptr(), B, T, H, st)
