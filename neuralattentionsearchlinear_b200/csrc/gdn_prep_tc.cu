@@ -5,8 +5,9 @@
 // (src/nats/ops/common/chunk_scaled_dot_kkt.py:105-126, src/nats/ops/utils/solve_tril.py:350-447,
 //  src/nats/ops/gated_delta_rule/wy_fast.py:123-153, src/nats/ops/common/chunk_o.py:166,188,202-203).
 //
-// One CTA per (batch, head, 64-token chunk), 160 threads, 128 TMEM columns, ~70 KB of shared memory (three CTAs per SM):
-//   warp 4      TMA producer (k, q, v tiles, 128-byte swizzle) and single-thread MMA issuer;
+// One CTA per (batch, head, 64-token chunk), 160 threads, 128 TMEM columns, ~52 KB of shared memory (four CTAs per SM):
+//   warp 4      TMA producer (k, q tiles at the start, the v tile once A is no longer needed; 128-byte swizzle)
+//               and single-thread MMA issuer;
 //   warps 0-3   one thread per TMEM lane.
 // Steps:
 //   1. D1 = [k ; q] k^T            one stacked 128 x 64 x 128 product into TMEM (rows 0-63: K K^T, rows 64-127: Q K^T);
@@ -19,8 +20,8 @@
 //      right-hand sides never have to be scaled in shared memory;
 //   4. D2 = [v^T (Ai diag beta)^T | k^T (Ai diag(..))^T]: the raw v and k tiles are the (MN-major) A operands,
 //      features in the TMEM lanes, tokens in the columns: no accumulator row is wasted;
-//   5. u, w rows go from TMEM to global memory, two neighbouring lanes exchanging values so that every store is a
-//      pair of features.
+//   5. w, then u, go from TMEM through a [token][feature] staging tile (written feature by feature, which is
+//      conflict-free) to global memory with TMA stores; P leaves the same way.
 // The decay carried over skipped blocks multiplies w by one scalar per chunk and is applied by the consumers.
 // Every mbarrier wait is bounded: on expiry the status word is set and the CTA runs on to its teardown.
 #include "tc_common.cuh"
@@ -35,18 +36,36 @@ constexpr int PT_A_LD = 68;                  // fp32 row pitch of A: conflict-fr
 
 struct PtSmem {
     // [k sub-tile 0][q sub-tile 0][k sub-tile 1][q sub-tile 1], each [64 tokens][64 features] = 8 KB: the stacked
-    // [k ; q] operand of the first product; the q sub-tiles are reused for the two Ai operand tiles
+    // [k ; q] operand of the first product.  The q sub-tiles are reused: first sub-tile 0 for staging P, then both for
+    // the two Ai operand tiles.
     static constexpr int kq = 0;
-    static constexpr int v = 32768;                          // v sub-tiles 0, 1
-    static constexpr int As = 49152;                         // fp32 [64][68]; diagonal blocks replaced by their inverses
+    // fp32 A [64][68] (diagonal blocks replaced by their inverses); once Ai is formed the v tile (2 sub-tiles, 16 KB)
+    // is loaded over it -- it is needed by the last product only, and this is what lets four CTAs share an SM
+    static constexpr int As = 32768;
+    static constexpr int v = As;
     static constexpr int scr = As + 64 * PT_A_LD * 4;        // per warp [16][8] fp32: accumulator -> B-fragment exchange
     static constexpr int vec = scr + 4 * 512;                // gcs, beta, k rstd, w scale, q rstd: 5 x 64 floats
     static constexpr int bars = vec + 5 * 64 * 4;
     static constexpr int total = bars + 64;
     static constexpr int aiu = kq + 8192, aiw = kq + 24576;  // Ai diag(beta), Ai diag(beta rstd e^{gcs}): [64][64] bf16
+    static constexpr int pst = kq + 8192;                    // P staging [64][64] bf16
+    static_assert(As % 1024 == 0 && 64 * PT_A_LD * 4 >= 16384, "the v tile must fit over A, 1024-byte aligned");
+    static_assert(4 * (total + 1024) <= 232448, "four CTAs per SM");
 };
 
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+#ifdef NATSL_PREP_TIMING
+// scratch builds only: cycle stamps of thread 0 (slots 0-9) and thread 64 (slots 10-19) of every CTA
+__device__ long long* g_prep_ts = nullptr;
+#define PT_STAMP(slot)                                                                                        \
+    do {                                                                                                      \
+        if (g_prep_ts && (tid == 0 || tid == 64))                                                             \
+            g_prep_ts[(((long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 20 + (tid ? 10 : 0) + (slot)] = clock64(); \
+    } while (0)
+#else
+#define PT_STAMP(slot)
+#endif
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
     uint32_t r;
@@ -143,15 +162,15 @@ __device__ __forceinline__ void inverse_panel(const float* As, float* scr, unsig
     }
 }
 
-__global__ void __launch_bounds__(PT_THREADS, 3)
+__global__ void __launch_bounds__(PT_THREADS, 4)
 gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, int has_q, const float* __restrict__ g,
-                   const void* __restrict__ beta, int beta_dtype, __nv_bfloat16* __restrict__ w,
-                   __nv_bfloat16* __restrict__ u, float* __restrict__ gcs_out, float* __restrict__ krstd_out,
-                   float* __restrict__ qrstd_out, __nv_bfloat16* __restrict__ p_out, int T, int H, int use_l2norm,
-                   int* status) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_p, int has_q,
+                   const float* __restrict__ g, const void* __restrict__ beta, int beta_dtype,
+                   float* __restrict__ gcs_out, float* __restrict__ krstd_out, float* __restrict__ qrstd_out, int T,
+                   int H, int use_l2norm, int* status) {
     using L = PtSmem;
-    constexpr int K = 128, V = 128;
+    constexpr int K = 128;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t sbase = smem_u32(smem);
@@ -170,14 +189,18 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float* s_rstd = s_beta + 64;
     float* s_wsc = s_rstd + 64;
     float* s_qr = s_wsc + 64;
-    const uint32_t bar_load = sbase + L::bars, bar_d1 = bar_load + 8, bar_ai = bar_load + 16, bar_d2 = bar_load + 24;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 32);
+    const uint32_t bar_load = sbase + L::bars, bar_d1 = bar_load + 8, bar_ai = bar_load + 16, bar_d2w = bar_load + 24,
+                   bar_v = bar_load + 32, bar_d2u = bar_load + 40;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::bars + 48);
 
+    PT_STAMP(0);
     if (tid == 0) {
         mbar_init(bar_load, 1);
         mbar_init(bar_d1, 1);
         mbar_init(bar_ai, PT_EPI);
-        mbar_init(bar_d2, 1);
+        mbar_init(bar_d2w, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_d2u, 1);
         mbar_fence_init();
     }
     if (warp == 4) tmem_alloc(smem_u32(tmem_slot), PT_TMEM_COLS);
@@ -185,17 +208,20 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    PT_STAMP(1);
 
     if (warp == 4) {
         // ------------------------------------------------------------ TMA producer + MMA issuer
         if (lane == 0) {
-            mbar_expect_tx(bar_load, has_q ? 49152 : 32768);
+            mbar_expect_tx(bar_load, has_q ? 32768 : 16384);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 tma_load_4d(sbase + L::kq + sub * 16384, &map_k, sub * 64, h, t0, b, bar_load);
                 if (has_q) tma_load_4d(sbase + L::kq + sub * 16384 + 8192, &map_q, sub * 64, h, t0, b, bar_load);
-                tma_load_4d(sbase + L::v + sub * 8192, &map_v, sub * 64, h, t0, b, bar_load);
             }
+            // v is only needed at the very end: warm L2 now, load it when A is dead
+            tma_prefetch_4d(&map_v, 0, h, t0, b);
+            tma_prefetch_4d(&map_v, 64, h, t0, b);
         }
         __syncwarp();
         mbar_wait(bar_load, 0, status);
@@ -213,6 +239,23 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_wait(bar_ai, 0, status);
         if (lane == 0) {
             constexpr uint32_t id_2 = umma_idesc_bf16(128, 64, false) | (1u << 15);      // A MN-major (features x tokens)
+            // every thread has finished with A (and fenced): the v tile may land on it
+            mbar_expect_tx(bar_v, 16384);
+            tma_load_4d(sbase + L::v, &map_v, 0, h, t0, b, bar_v);
+            tma_load_4d(sbase + L::v + 8192, &map_v, 64, h, t0, b, bar_v);
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const uint64_t ak = umma_desc(sbase + L::kq + kk * 2048, 16384, 1024);
+                const uint64_t bw = umma_desc(sbase + L::aiw + kk * 32, 16, 1024);
+                umma_ss(tmem + 64, ak, bw, id_2, kk > 0);
+            }
+            umma_commit(bar_d2w);
+        }
+        __syncwarp();
+        mbar_wait(bar_v, 0, status);
+        if (lane == 0) {
+            constexpr uint32_t id_2 = umma_idesc_bf16(128, 64, false) | (1u << 15);
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
@@ -220,13 +263,7 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint64_t bu = umma_desc(sbase + L::aiu + kk * 32, 16, 1024);
                 umma_ss(tmem, av, bu, id_2, kk > 0);
             }
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const uint64_t ak = umma_desc(sbase + L::kq + kk * 2048, 16384, 1024);
-                const uint64_t bw = umma_desc(sbase + L::aiw + kk * 32, 16, 1024);
-                umma_ss(tmem + 64, ak, bw, id_2, kk > 0);
-            }
-            umma_commit(bar_d2);
+            umma_commit(bar_d2u);
         }
         __syncwarp();
     } else {
@@ -264,6 +301,7 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (lane + 32 < valid) gcs_out[g1] = x1;
         }
         mbar_wait(bar_load, 0, status);
+        PT_STAMP(2);
         if (warp >= 2 && has_q) {
             // q row norms (one row per thread; the swizzle makes the 16-byte reads of eight rows conflict-free)
             const int r = row - 64;
@@ -286,6 +324,7 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         mbar_wait(bar_d1, 0, status);
         tc_fence_after();
+        PT_STAMP(3);
         if (warp < 2) {
             // k row norms from the diagonal of K K^T: row i of warp w has its diagonal in columns [32 w, 32 w + 32)
             uint32_t r[32];
@@ -300,6 +339,7 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (row < valid) krstd_out[(tok0 + row) * H + h] = rs;
         }
         epi_barrier();                      // gcs, beta, both row norms are known; the q tile has been read for the last time
+        PT_STAMP(4);
         if (warp < 2) {
             const float gi = s_gcs[row];
             const float bi = s_beta[row] * s_rstd[row];
@@ -314,19 +354,21 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const int j = 32 * hh + j4;
                     const float4 gj = *reinterpret_cast<const float4*>(s_gcs + j);
                     const float4 rj = *reinterpret_cast<const float4*>(s_rstd + j);
+                    // strictly below the diagonal; the exponent is clamped so that the masked entries stay finite
                     float4 a;
-                    a.x = row > j ? bi * rj.x * __uint_as_float(r[j4]) * __expf(gi - gj.x) : 0.f;
-                    a.y = row > j + 1 ? bi * rj.y * __uint_as_float(r[j4 + 1]) * __expf(gi - gj.y) : 0.f;
-                    a.z = row > j + 2 ? bi * rj.z * __uint_as_float(r[j4 + 2]) * __expf(gi - gj.z) : 0.f;
-                    a.w = row > j + 3 ? bi * rj.w * __uint_as_float(r[j4 + 3]) * __expf(gi - gj.w) : 0.f;
+                    a.x = (row > j ? bi : 0.f) * rj.x * __uint_as_float(r[j4]) * __expf(fminf(gi - gj.x, 0.f));
+                    a.y = (row > j + 1 ? bi : 0.f) * rj.y * __uint_as_float(r[j4 + 1]) * __expf(fminf(gi - gj.y, 0.f));
+                    a.z = (row > j + 2 ? bi : 0.f) * rj.z * __uint_as_float(r[j4 + 2]) * __expf(fminf(gi - gj.z, 0.f));
+                    a.w = (row > j + 3 ? bi : 0.f) * rj.w * __uint_as_float(r[j4 + 3]) * __expf(fminf(gi - gj.w, 0.f));
                     *reinterpret_cast<float4*>(As + row * PT_A_LD + j) = a;
                 }
             }
         } else if (has_q) {
-            // P = tril(qn kn^T e^{gcs_i - gcs_j}): one 128-byte row per thread
+            // P = tril(qn kn^T e^{gcs_i - gcs_j}): one row per thread into the staging tile (the q sub-tile is free);
+            // one TMA store writes the tile after the next barrier
             const int i = row - 64;
             const float gi = s_gcs[i], qi = s_qr[i];
-            __nv_bfloat16* prow = p_out + ((tok0 + i) * H + h) * 64;
+            unsigned char* pst = smem + L::pst;
 #pragma unroll 1
             for (int hh = 0; hh < 2; ++hh) {
                 uint32_t r[32];
@@ -340,18 +382,23 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     for (int e4 = 0; e4 < 8; e4 += 4) {
                         const float4 gj = *reinterpret_cast<const float4*>(s_gcs + j + e4);
                         const float4 rj = *reinterpret_cast<const float4*>(s_rstd + j + e4);
-                        pv[e4] = i >= j + e4 ? qi * rj.x * __uint_as_float(r[j8 + e4]) * __expf(gi - gj.x) : 0.f;
-                        pv[e4 + 1] = i >= j + e4 + 1 ? qi * rj.y * __uint_as_float(r[j8 + e4 + 1]) * __expf(gi - gj.y) : 0.f;
-                        pv[e4 + 2] = i >= j + e4 + 2 ? qi * rj.z * __uint_as_float(r[j8 + e4 + 2]) * __expf(gi - gj.z) : 0.f;
-                        pv[e4 + 3] = i >= j + e4 + 3 ? qi * rj.w * __uint_as_float(r[j8 + e4 + 3]) * __expf(gi - gj.w) : 0.f;
+                        pv[e4] = (i >= j + e4 ? qi : 0.f) * rj.x * __uint_as_float(r[j8 + e4]) * __expf(fminf(gi - gj.x, 0.f));
+                        pv[e4 + 1] = (i >= j + e4 + 1 ? qi : 0.f) * rj.y * __uint_as_float(r[j8 + e4 + 1]) * __expf(fminf(gi - gj.y, 0.f));
+                        pv[e4 + 2] = (i >= j + e4 + 2 ? qi : 0.f) * rj.z * __uint_as_float(r[j8 + e4 + 2]) * __expf(fminf(gi - gj.z, 0.f));
+                        pv[e4 + 3] = (i >= j + e4 + 3 ? qi : 0.f) * rj.w * __uint_as_float(r[j8 + e4 + 3]) * __expf(fminf(gi - gj.w, 0.f));
                     }
-                    if (i < valid)
-                        *reinterpret_cast<uint4*>(prow + j) = make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]),
-                                                                         pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
+                    *reinterpret_cast<uint4*>(pst + swz<128>(i, j >> 3)) =
+                        make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
                 }
             }
+            fence_async_smem();
         }
-        epi_barrier();                      // A complete, the w scale known, D1 read for the last time
+        PT_STAMP(5);
+        epi_barrier();                      // A complete, the w scale known, D1 read for the last time, P staged
+        if (tid == 64 && has_q) {
+            tma_store_4d(&map_p, sbase + L::pst, 0, h, t0, b);
+            tma_store_commit();
+        }
         if (lane < 16) {
             // X_dd = (I + A_dd)^-1 by forward substitution, lane = column; written over A_dd
             const int d0 = warp * 16, cidx = lane;
@@ -376,6 +423,8 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
             for (int i = 0; i < 16; ++i) As[(d0 + i) * PT_A_LD + d0 + cidx] = xcol[i];
         }
+        PT_STAMP(6);
+        if (tid == 64 && has_q) tma_store_wait_read();      // the P tile has been read: its place becomes Ai diag(beta)
         epi_barrier();
         {
             float* scr = reinterpret_cast<float*>(smem + L::scr) + warp * 128;
@@ -388,31 +437,47 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int j = 1; j < 4; ++j) inverse_panel(As, scr, aiu, aiw, s_beta, s_wsc, j, warp - 2, lane);
             }
         }
+        PT_STAMP(7);
         fence_async_smem();
         tc_fence_before();
         mbar_arrive(bar_ai);
-        mbar_wait(bar_d2, 0, status);
-        tc_fence_after();
-        // ---- u (columns 0-63) and w (columns 64-127): lane = feature, column = token; neighbouring lanes pair up
-        const bool odd = lane & 1;
-        const int f2 = row & ~1;
-#pragma unroll 1
-        for (int part = 0; part < 4; ++part) {
-            uint32_t r[32];
-            tmem_ld32(t_lane + 32 * part, r);
-            tmem_ld_wait();
-            __nv_bfloat16* dst = (part < 2 ? u + (tok0 * H + h) * V : w + (tok0 * H + h) * K) + f2;
-            const long tstride = (long)H * (part < 2 ? V : K);
-            const int tb = 32 * (part & 1);
+        PT_STAMP(8);
+        // ---- w (columns 64-127, its product does not wait for the v tile) then u (columns 0-63): lane = feature,
+        // column = token.  Each thread writes its feature's 64 values as single bf16 into a [token][feature] staging
+        // tile (32 lanes = 64 contiguous bytes of one row: conflict-free), then one thread stores the tiles with TMA.
+        // Staging: w over the k sub-tiles (dead once its product is done), u over the two Ai tiles.
+        {
+            const int sub = row >> 6, cf = row & 63;
+            uint32_t off[8];                             // byte offset of this feature inside a row, by (token & 7)
 #pragma unroll
-            for (int tt = 0; tt < 32; tt += 2) {
-                const float a = __uint_as_float(r[tt]), bb = __uint_as_float(r[tt + 1]);
-                const float recv = __shfl_xor_sync(0xffffffffu, odd ? a : bb, 1);
-                const int tok = tb + tt + (odd ? 1 : 0);
-                const uint32_t pk = odd ? pack_bf16(recv, bb) : pack_bf16(a, recv);
-                if (tok < valid) *reinterpret_cast<uint32_t*>(dst + tok * tstride) = pk;
+            for (int x = 0; x < 8; ++x) off[x] = (uint32_t)((((cf >> 3) ^ x) << 4) + (cf & 7) * 2);
+#pragma unroll 1
+            for (int arr = 0; arr < 2; ++arr) {          // 0: w, 1: u
+                mbar_wait(arr == 0 ? bar_d2w : bar_d2u, 0, status);
+                tc_fence_after();
+                unsigned char* stg = smem + L::kq + sub * 16384 + (arr == 0 ? 0 : 8192);
+#pragma unroll 1
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t r[32];
+                    tmem_ld32(t_lane + (arr == 0 ? 64 : 0) + 32 * hh, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int tt = 0; tt < 32; ++tt)
+                        *reinterpret_cast<__nv_bfloat16*>(stg + (32 * hh + tt) * 128 + off[tt & 7]) =
+                            __float2bfloat16(__uint_as_float(r[tt]));
+                }
+                fence_async_smem();
+                epi_barrier();
+                if (tid == 0) {
+                    const CUtensorMap* mp = arr == 0 ? &map_w : &map_u;
+                    tma_store_4d(mp, sbase + L::kq + (arr == 0 ? 0 : 8192), 0, h, t0, b);
+                    tma_store_4d(mp, sbase + L::kq + 16384 + (arr == 0 ? 0 : 8192), 64, h, t0, b);
+                    tma_store_commit();
+                }
             }
+            if (tid == 0) tma_store_wait_read();
         }
+        PT_STAMP(9);
         tc_fence_before();
     }
     __syncthreads();
@@ -420,6 +485,12 @@ gdn_prep_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 }  // namespace natsl
+
+#ifdef NATSL_PREP_TIMING
+extern "C" int natsl_prep_tc_set_timing(long long* p) {
+    return cudaMemcpyToSymbol(natsl::g_prep_ts, &p, sizeof(p)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int natsl_gdn_chunk_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* beta,
                                        int beta_dtype, void* w, void* u, float* gcs, float* k_rstd, float* q_rstd,
@@ -440,17 +511,20 @@ extern "C" int natsl_gdn_chunk_prep_tc(const void* q, const void* k, const void*
         set_error("natsl_gdn_chunk_prep_tc: cannot reserve %d B of shared memory (%s)", PtSmem::total, cudaGetErrorString(e));
         return NATSL_ERR_CUDA;
     }
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mw, mu, mp;
     int rc = encode_bthd_map(&mk, k, B, T, H, K, 64, "natsl_gdn_chunk_prep_tc(k)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mv, v, B, T, H, V, 64, "natsl_gdn_chunk_prep_tc(v)");
     if (rc == NATSL_OK) rc = encode_bthd_map(&mq, q ? q : k, B, T, H, K, 64, "natsl_gdn_chunk_prep_tc(q)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mw, w, B, T, H, K, 64, "natsl_gdn_chunk_prep_tc(w)");
+    if (rc == NATSL_OK) rc = encode_bthd_map(&mu, u, B, T, H, V, 64, "natsl_gdn_chunk_prep_tc(u)");
+    if (rc == NATSL_OK) rc = pmat ? encode_bthd_map(&mp, pmat, B, T, H, 64, 64, "natsl_gdn_chunk_prep_tc(P)") : NATSL_OK;
+    if (!pmat) mp = mk;
     int* status = nullptr;
     if (rc == NATSL_OK) rc = status_word_ptr(&status);
     if (rc != NATSL_OK) return rc;
     const int NT = (T + 63) / 64;
     dim3 grid(NT, H, B);
     kern<<<grid, PT_THREADS, PtSmem::total, reinterpret_cast<cudaStream_t>(stream)>>>(
-        mq, mk, mv, q ? 1 : 0, g, beta, beta_dtype, reinterpret_cast<__nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(u),
-        gcs, k_rstd, q_rstd, reinterpret_cast<__nv_bfloat16*>(pmat), T, H, use_l2norm, status);
+        mq, mk, mv, mw, mu, mp, q ? 1 : 0, g, beta, beta_dtype, gcs, k_rstd, q_rstd, T, H, use_l2norm, status);
     return check_launch("natsl_gdn_chunk_prep_tc");
 }
