@@ -37,6 +37,7 @@ extern "C" {
 #define NATSL_FLAG_ATTN_OWN_CHUNK 2     /* softmax branch also covers the query's own block ('all', 'attn') */
 #define NATSL_FLAG_NO_TRAILING_QUIRK 4  /* carry the decay also over skipped blocks after the last selected one */
 #define NATSL_FLAG_ATTN_MMA_SYNC 8      /* natsl_attn_fwd: use the mma.sync comparison kernel instead of tcgen05 */
+#define NATSL_FLAG_ATTN_PERSISTENT 32   /* natsl_attn_fwd*: two resident CTAs per SM work through the query tiles (measured slower; off by default) */
 #define NATSL_FLAG_BWD_REFERENCE_COMPAT 16 /* natsl_attn_bwd: drop the own-block terms, as the reference's default backward does */
 
 #define NATSL_ATTN_BT 128 /* query rows per attention tile; the attn_n_iters table is built for it */

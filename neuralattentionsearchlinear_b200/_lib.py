@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libnatsl_b200.so")
 DT_BF16, DT_F32, DT_F16, DT_I32 = 0, 1, 2, 3
 RULE_GDN, RULE_MAMBA = 0, 1
 FLAG_DECAY_SKIPPED, FLAG_ATTN_OWN_CHUNK, FLAG_NO_TRAILING_QUIRK, FLAG_ATTN_MMA_SYNC = 1, 2, 4, 8
+FLAG_ATTN_PERSISTENT = 32
 FLAG_BWD_REFERENCE_COMPAT = 16
 ATTN_BT = 128
 

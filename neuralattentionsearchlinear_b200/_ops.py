@@ -18,6 +18,15 @@ WALK_VSPLIT = os.environ.get("NATSL_WALK_VSPLIT", "0") == "1"
 PREP_TC = os.environ.get("NATSL_PREP_TC", "1") != "0"
 
 
+# softmax branch with persistent CTAs (two per SM working through the query tiles) instead of one CTA per query tile.
+# Off by default: parity-green but measured slower (0.43 vs 0.29 ms at B=8, T=4096, H=16).
+ATTN_PERSISTENT = os.environ.get("NATSL_ATTN_PERSISTENT", "0") == "1"
+
+
+def _attn_flags(own_chunk: bool) -> int:
+    return (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_ATTN_PERSISTENT if ATTN_PERSISTENT else 0)
+
+
 def prep_entry(K: int, V: int) -> str:
     """Name of the chunk-preparation entry point for these head dims (both take the arguments of ``..._prep_ex``)."""
     return "natsl_gdn_chunk_prep_tc" if (PREP_TC and K == 128 and V == 128) else "natsl_gdn_chunk_prep_ex"
@@ -58,7 +67,7 @@ def attn_fwd(q, k, v, tables: SelectionTables, scale: float, own_chunk: bool, mm
     HN = tables.types_i.shape[2]
     o = torch.empty(B, Tq, HQ, DV, dtype=BF16, device=q.device)
     lse = torch.empty(B, Tq, HQ, dtype=torch.float32, device=q.device)
-    flags = (_lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0) | (_lib.FLAG_ATTN_MMA_SYNC if mma_sync else 0)
+    flags = _attn_flags(own_chunk) | (_lib.FLAG_ATTN_MMA_SYNC if mma_sync else 0)
     _lib.call("natsl_attn_fwd_ex", q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(),
               tables.indices.data_ptr(), tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(),
               B, T, Tq, int(q_off), HQ, HKV, HN, DK, DV, tables.nats_block_size, float(scale), flags,
@@ -91,8 +100,7 @@ def attn_fwd_split(q, k_rem, v_rem, k, v, tables: SelectionTables, scale: float,
     _lib.call("natsl_attn_fwd_split", q.data_ptr(), k_rem.data_ptr(), v_rem.data_ptr(), _lib.ptr(rem_base), int(rem_slots),
               int(rem_tokens), k.data_ptr(), v.data_ptr(), tables.types_i.data_ptr(), tables.indices.data_ptr(),
               tables.attn_n_iters.data_ptr(), o.data_ptr(), lse.data_ptr(), B, B_rem, S + L, L, S, S, HQ, HKV,
-              tables.types_i.shape[2], DK, DV, nbs, float(scale), _lib.FLAG_ATTN_OWN_CHUNK if own_chunk else 0,
-              current_stream_ptr(q.device))
+              tables.types_i.shape[2], DK, DV, nbs, float(scale), _attn_flags(own_chunk), current_stream_ptr(q.device))
     return o
 
 

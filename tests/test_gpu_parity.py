@@ -80,7 +80,7 @@ def test_dense_mask_bit_exact(nat, B, T, HQ, HN, nbs, own):
 @pytest.mark.parametrize("B,T,HQ,HKV,HN,DK,DV,nbs,own", [
     (2, 512, 4, 4, 4, 64, 64, 64, True), (1, 700, 4, 2, 2, 128, 128, 64, True), (2, 1024, 2, 2, 2, 64, 128, 128, True),
     (1, 1100, 2, 2, 1, 128, 64, 256, True), (2, 512, 4, 4, 4, 64, 64, 64, False), (1, 2048, 2, 2, 2, 128, 128, 64, True)])
-def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own):
+def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own, monkeypatch):
     from neuralattentionsearchlinear_b200 import _ops
     gen = torch.Generator().manual_seed(T + DK)
     q = torch.randn(B, T, HQ, DK, generator=gen).bfloat16()
@@ -99,6 +99,11 @@ def test_attention_forward(nat, B, T, HQ, HKV, HN, DK, DV, nbs, own):
     o2, lse2 = _ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), tb, DK ** -0.5, own, mma_sync=True)
     assert_close(o2, o_ref, TOL, "o_attn (mma.sync)")
     assert_close(lse2, lse_ref, TOL, "lse (mma.sync)")
+    # the persistent form (optional) walks the same tiles in the same order with the same arithmetic: identical bits
+    monkeypatch.setattr(_ops, "ATTN_PERSISTENT", not _ops.ATTN_PERSISTENT)
+    o3, lse3 = _ops.attn_fwd(q.cuda(), k.cuda(), v.cuda(), tb, DK ** -0.5, own)
+    assert _lib.load().natsl_device_status() == 0
+    assert torch.equal(o3, o) and torch.equal(lse3, lse)
 
 
 @pytest.mark.parametrize("DK,DV,nbs", [(128, 128, 64), (128, 64, 256), (64, 64, 128)])
