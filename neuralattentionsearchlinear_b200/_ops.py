@@ -139,6 +139,17 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     _need(H % HN == 0, f"{H} heads over {HN} selection heads")
     NT = cdiv(T, 64)
     nbs = tables.nats_block_size
+    if K not in (64, 128) or V not in (64, 128, 256):
+        # head dims the chunk kernels have no tiles for (the 760M configuration: K = 192, V = 384): the token recurrence
+        # with re-roll computes the same function for any K in {32, 64, 96, 128, 192, 256} and V a multiple of 8 --
+        # correct, not fast, forward only
+        if return_intermediates or skip_out or not own_chunk:
+            raise NotImplementedError(f"head dims K={K}, V={V} run the token recurrence, which has no chunk intermediates "
+                                      "(backward pass, state-only and mode 'attn' need K in {64,128}, V in {64,128,256})")
+        if tables_event is not None:
+            torch.cuda.current_stream(dev).wait_event(tables_event)
+        o, ht, _ = linear_recurrent(rule, q, k, v, g, beta, tables, scale, h0, decay, use_l2norm)
+        return o, (ht if output_final_state else None), None
     st = current_stream_ptr(dev)
     g = g.float().contiguous()
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)

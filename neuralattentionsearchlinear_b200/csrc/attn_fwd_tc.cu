@@ -92,11 +92,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(bar_pv, 1);
         mbar_init(bar_pv + 8, 1);
         mbar_fence_init();
-        // the query tile depends on nothing else: its load starts before the tables are read
+        // the query tile and the first own-span key / value tiles depend on no table: their loads start at once
         prefetch_tensormap(&map_q);
         mbar_expect_tx(bar_q, 128 * DK * 2);
 #pragma unroll
         for (int sub = 0; sub < DK / 64; ++sub) tma_load_4d(s_q + sub * 16384, &map_q, sub * 64, hq, q0 - q_off, b, bar_q);
+        const TileWalk w0 = make_walk(q0, T, nbs, 0);
+        const int hkv0 = hq / (HQ / HKV);
+        for (int j = 0; j < min(w0.n_span, TcTmem<DV>::KST); ++j) {
+            mbar_expect_tx(bar_k_full + j * 8, 64 * DK * 2);
+#pragma unroll
+            for (int sub = 0; sub < DK / 64; ++sub)
+                tma_load_4d(s_k + j * (64 * DK * 2) + sub * 8192, &map_k, sub * 64, hkv0, w0.span_start + j * ATT_BN - k_split, b,
+                            bar_k_full + j * 8);
+        }
+        for (int j = 0; j < min(w0.n_span, TC_VST); ++j) {
+            mbar_expect_tx(bar_v_full + j * 8, 64 * DV * 2);
+#pragma unroll
+            for (int sub = 0; sub < DV / 64; ++sub)
+                tma_load_4d(s_v + j * (64 * DV * 2) + sub * 8192, &map_v, sub * 64, hkv0, w0.span_start + j * ATT_BN - k_split, b,
+                            bar_v_full + j * 8);
+        }
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
     const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
@@ -162,9 +178,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // K stage of tile i + NSB (Q K_{i+NSB}^T is issued right behind P_i V_i).  Every wait is for the next event
         // of that sequence, so the producer sleeps in the barrier instead of polling two rings.
         int jk = min(TC_KST, n_tiles), jv = min(TC_VST, n_tiles);
-        if (lane == 0) {
-            for (int j = 0; j < jk; ++j) load_k(j);
-            for (int j = 0; j < jv; ++j) load_v(j);
+        if (lane == 0) {                               // the own-span tiles among these were requested at kernel start
+            for (int j = min(walk.n_span, TC_KST); j < jk; ++j) load_k(j);
+            for (int j = min(walk.n_span, TC_VST); j < jv; ++j) load_v(j);
         }
         bool ok = true;
         auto next_k = [&]() {

@@ -102,8 +102,10 @@ __device__ __forceinline__ void ps_peek(PsCursor& c, int G, const PsArgs& a, int
     c.nxt_n_past = ps_n_past(y, a);
     const int* idx = a.indices + ((long)y.b * a.TN * a.HN + y.hn) * 2;
     const int cpb = a.nbs / ATT_BN;
+    const int n_span = make_walk(y.q0, a.T, a.nbs, 0).n_span;        // the own span comes first and needs no table
 #pragma unroll
-    for (int r = 0; r < 4; ++r) c.nxt_blk[r] = idx[(long)min((lane + 32 * r) / cpb, a.TN - 1) * a.HN * 2];
+    for (int r = 0; r < 4; ++r)
+        c.nxt_blk[r] = idx[(long)min(max(lane + 32 * r - n_span, 0) / cpb, a.TN - 1) * a.HN * 2];
 }
 // move to the next item: everything is computed from the entries requested by ps_peek
 __device__ __forceinline__ void ps_next(PsCursor& c, int G, const PsArgs& a, int lane) {
@@ -125,8 +127,8 @@ __device__ __forceinline__ void ps_next(PsCursor& c, int G, const PsArgs& a, int
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         const int j = lane + 32 * r;
-        const bool past = j < x.walk.n_past_tiles;
-        const int s0 = past ? c.nxt_blk[r] * a.nbs + (j % x.walk.cpb) * ATT_BN : x.walk.span_start + (j - x.walk.n_past_tiles) * ATT_BN;
+        const bool past = j >= x.walk.n_span;
+        const int s0 = past ? c.nxt_blk[r] * a.nbs + ((j - x.walk.n_span) % x.walk.cpb) * ATT_BN : x.walk.span_start + j * ATT_BN;
         int coord = s0 - a.k_split, rem = 0;
         if (j < x.n_tiles && s0 < a.k_split) {
             rem = 1;
@@ -475,9 +477,9 @@ attn_fwd_tc_persist_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 uint32_t sr[32];
                 tmem_ld_16x256b_x8(t_s, sr);
                 tmem_ld_wait();
-                if (j >= walk.n_past_tiles) {
+                if (j < walk.n_span) {
                     // own-span tile: per row the visible keys are columns [0, limit] (attn_walk.cuh: visible())
-                    const int ms = j - walk.n_past_tiles;
+                    const int ms = j;
                     const int s0 = walk.span_start + ms * ATT_BN;
                     const bool selb = (sel_mask >> ms) & 1;
                     const int blk_end = (s0 / nbs + 1) * nbs;

@@ -189,10 +189,12 @@ static int launch_recurrent(const void* q, const void* k, const void* v, const f
         hstart_in, gsum_in, t_off, step_mode)
     if (K == 32) NATSL_REC(1);
     else if (K == 64) NATSL_REC(2);
+    else if (K == 96) NATSL_REC(3);
     else if (K == 128) NATSL_REC(4);
+    else if (K == 192) NATSL_REC(6);
     else if (K == 256) NATSL_REC(8);
     else {
-        set_error("natsl_linear_recurrent_fwd: unsupported key dim K=%d (32, 64, 128 or 256)", K);
+        set_error("natsl_linear_recurrent_fwd: unsupported key dim K=%d (32, 64, 96, 128, 192 or 256)", K);
         return NATSL_ERR_UNSUPPORTED;
     }
 #undef NATSL_REC

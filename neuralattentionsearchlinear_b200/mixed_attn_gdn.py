@@ -186,6 +186,8 @@ class NAtSMixedAttentionGDN(torch.autograd.Function):
             ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is not built for ops_for_incomplete_chunks='attn'"
         elif nats_block_size != CHUNK_SIZE:
             ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for nats_block_size = 64"
+        elif q_lattn.shape[-1] not in (64, 128) or v_lattn.shape[-1] not in (64, 128):
+            ctx.bwd_ok, ctx.bwd_why = False, "the backward pass is built for linear-branch head dims 64 and 128"
         ctx.save_for_backward(q_attn, k_attn, v_attn, o_attn, lse, q_lattn, k_lattn, v_lattn, g, beta,
                               initial_state_gated_delta)
         ctx.tables = tables

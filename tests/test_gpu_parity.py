@@ -364,3 +364,28 @@ def test_fp32_path_matches_naive_recurrent_form(nat, nbs, decay, T):
                                            scale=1.0, h0=h0.double(), decay=decay, use_l2norm=False, rule="mamba")
     assert_close(o_m, om_ref.float(), 1e-4, "o_mamba fp32")
     assert_close(htm, sm_ref.float(), 1e-4, "mamba final_state fp32")
+
+
+def test_gdn_op_with_the_760m_head_dims(nat):
+    """K = 192, V = 384 (experiments/configs/natsl_760M.json: head_dim 192, expand_v 2; softmax heads 64 / 128): no chunk
+    kernel has tiles for these; the op takes the token recurrence for the linear branch -- correct, not fast, forward only."""
+    B, T, H, HQ, K, V, nbs = 1, 300, 2, 6, 192, 384, 64
+    q, k, v, g, beta, _ = synth_gdn_inputs(B, T, H, K, V, seed=7)
+    gen = torch.Generator().manual_seed(3)
+    qa = torch.randn(B, T, HQ, K * H // HQ, generator=gen).bfloat16()
+    ka = torch.randn(B, T, HQ, K * H // HQ, generator=gen).bfloat16()
+    va = torch.randn(B, T, HQ, V * H // HQ, generator=gen).bfloat16()
+    types = otab.synth_types(B, -(-T // nbs), H, 0.3, seed=2)
+    c = lambda x: x.cuda()
+    qg = c(q).requires_grad_(True)
+    o_l, o_a, ht = nat.nats_mixed_attn_gdn(c(qa), c(ka), c(va), qg, c(k), c(v), None, c(g), c(beta), c(types), None,
+                                           nats_block_size=nbs, ops_for_incomplete_chunks="all",
+                                           output_final_state_gated_delta=True, decay_for_non_gdn_blocks=True)
+    o_ref, s_ref = ogdn.linear_chunk(q.float(), k.float(), v.float(), g, beta.float(), types[..., 1], nbs=nbs)
+    assert_close(o_l, o_ref, TOL, "o_gdn (K=192, V=384)")
+    assert_close(ht, s_ref, TOL, "final state (K=192, V=384)")
+    mask = oattn.attn_mask(types[..., 0], T, nbs, HQ)
+    oa_ref, _ = oattn.attn_sdpa(qa.float(), ka.float(), va.float(), mask)
+    assert_close(o_a, oa_ref, TOL, "o_attn (64 / 128)")
+    with pytest.raises(NotImplementedError):
+        o_l.float().sum().backward()
