@@ -105,6 +105,13 @@ def kernel_launches() -> int:
     return _launches
 
 
+# NATSL_CHECK_STATUS=1: after every entry point, wait for the device and read the status word the kernels' bounded waits
+# and capacity checks write (natsl_device_status); a non-zero word raises.  A debugging aid: it serialises host and device.
+CHECK_STATUS = os.environ.get("NATSL_CHECK_STATUS", "0") == "1"
+_DEVICE_STATUS_TEXT = {1: "a bounded wait inside a kernel ran out", 2: "a tensor-core kernel found its shared memory misaligned",
+                       3: "a caller-given capacity was too small"}
+
+
 def call(name: str, *args) -> None:
     global _launches
     lib = load()
@@ -112,6 +119,12 @@ def call(name: str, *args) -> None:
     _launches += KERNELS_PER_CALL.get(name, 1)
     if status != 0:
         raise NatslError(f"{name} failed with status {status}: {lib.natsl_last_error().decode()}")
+    if CHECK_STATUS and name not in ("natsl_device_status", "natsl_abi_version", "natsl_bounded_wait_selftest"):
+        import torch
+        torch.cuda.synchronize()
+        word = lib.natsl_device_status()
+        if word != 0:
+            raise NatslError(f"{name}: device status {word} ({_DEVICE_STATUS_TEXT.get(word, 'unknown')})")
 
 
 def ptr(t) -> int | None:
