@@ -418,6 +418,131 @@ extern "C" int natsl_short_conv_fwd(const void* x, const void* w, const void* bi
     return check_launch("natsl_short_conv_fwd");
 }
 
+// The same backward for span = 64 with the tiles staged in shared memory: one CTA = 256 channels x 64 tokens, all loads
+// of the x tile (64 + 6 halo rows) and the dy tile (64 + 3) are issued at once with cp.async (the sliding-window form
+// above has two loads in flight per thread and is bound by their latency), warp s computes the tokens 8 s .. 8 s + 7 for
+// 32 groups of 8 channels, and the eight warps' weight-gradient partials are summed in shared memory in a fixed order:
+// one partial per CTA.
+constexpr int CB_TT = 64, CB_CG = 32, CB_CH = 4;      // tokens per CTA, threads across channels, channels per thread
+__global__ void __launch_bounds__(256, 3)
+short_conv_bwd_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                           const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ dy,
+                           __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_part, int T, int D, int silu) {
+    constexpr int W = CONV_W;
+    constexpr int XR = CB_TT + 2 * (W - 1), YR = CB_TT + (W - 1);            // rows of the two tiles
+    constexpr int ROWB = CB_CG * CB_CH * 2;                                  // bytes per tile row
+    constexpr int CPR = ROWB / 16;                                          // 16-byte chunks per tile row
+    extern __shared__ __align__(16) unsigned char smem_cb[];
+    unsigned char* xs = smem_cb;
+    unsigned char* ys = smem_cb + XR * ROWB;
+    const int tid = threadIdx.x, lane = tid & 31, sr = tid >> 5;
+    const int d_cta = blockIdx.x * CB_CG * CB_CH;
+    const int t0 = blockIdx.y * CB_TT, b = blockIdx.z;
+    const int d0 = d_cta + lane * CB_CH;
+    const bool ch_ok = d0 < D;
+    {
+        const uint32_t xs_a = smem_u32(xs), ys_a = smem_u32(ys);
+        for (int i = tid; i < XR * CPR; i += 256) {
+            const int r = i / CPR, c = i % CPR;
+            const int t = t0 - (W - 1) + r, dd = d_cta + c * 8;
+            const bool ok = t >= 0 && t < T && dd < D;
+            cp_async16(xs_a + r * ROWB + c * 16, ok ? (const void*)(x + ((long)b * T + t) * D + dd) : (const void*)x, ok ? 16 : 0);
+        }
+        for (int i = tid; i < YR * CPR; i += 256) {
+            const int r = i / CPR, c = i % CPR;
+            const int t = t0 + r, dd = d_cta + c * 8;
+            const bool ok = t < T && dd < D;
+            cp_async16(ys_a + r * ROWB + c * 16, ok ? (const void*)(dy + ((long)b * T + t) * D + dd) : (const void*)dy, ok ? 16 : 0);
+        }
+        cp_async_commit();
+    }
+    float wt[CB_CH][W], bs[CB_CH], dwa[CB_CH][W + 1];
+#pragma unroll
+    for (int c = 0; c < CB_CH; ++c) {
+        bs[c] = (bias && ch_ok) ? __bfloat162float(bias[d0 + c]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < W; ++j) wt[c][j] = ch_ok ? __bfloat162float(w[(d0 + c) * W + j]) : 0.f;
+#pragma unroll
+        for (int j = 0; j <= W; ++j) dwa[c][j] = 0.f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    static_assert(CB_CH == 4, "a thread reads 8 bytes per row");
+    auto row8 = [&](const unsigned char* tile, int r, float (&f)[CB_CH]) {
+        const uint2 v = *reinterpret_cast<const uint2*>(tile + r * ROWB + lane * 8);
+        const float2 t0_ = unpack_bf16(v.x), t1_ = unpack_bf16(v.y);
+        f[0] = t0_.x; f[1] = t0_.y; f[2] = t1_.x; f[3] = t1_.y;
+    };
+    // token tt of the tile (0 .. 63 + halo): x rows tt .. tt + 3 of the x tile are its window, dy row tt its gradient.
+    // With `own` (a token of this warp's range, inside the sequence) its weight-gradient terms are added while the
+    // window is in registers.
+    auto dpre_at = [&](int tt, bool own, float (&dp)[CB_CH]) {
+        float xw[W][CB_CH];
+#pragma unroll
+        for (int j = 0; j < W; ++j) row8(xs, tt + j, xw[j]);
+        float g[CB_CH];
+        row8(ys, tt, g);                                   // zero outside the sequence
+#pragma unroll
+        for (int c = 0; c < CB_CH; ++c) {
+            float a = bs[c];
+#pragma unroll
+            for (int j = 0; j < W; ++j) a += wt[c][j] * xw[j][c];
+            if (silu) {
+                const float sg = sigmoidf_(a);
+                dp[c] = g[c] * sg * (1.f + a * (1.f - sg));
+            } else {
+                dp[c] = g[c];
+            }
+            if (own) {
+#pragma unroll
+                for (int j = 0; j < W; ++j) dwa[c][j] += dp[c] * xw[j][c];
+                dwa[c][W] += dp[c];
+            }
+        }
+    };
+    const int ts = sr * 8;                                  // first token of this warp inside the tile
+    float dps[W][CB_CH];                                        // dpre[tt .. tt + 3]
+#pragma unroll
+    for (int i = 1; i < W; ++i) dpre_at(ts + i - 1, true, dps[i]);        // dps[1..3] = dpre[ts .. ts+2] (dy = 0 past T)
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+        const int tt = ts + i;
+#pragma unroll
+        for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+            for (int c = 0; c < CB_CH; ++c) dps[k][c] = dps[k + 1][c];
+        dpre_at(tt + W - 1, i + W - 1 < 8, dps[W - 1]);
+        if (t0 + tt < T) {
+            float o[CB_CH];
+#pragma unroll
+            for (int c = 0; c < CB_CH; ++c) {
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < W; ++j) a += wt[c][j] * dps[W - 1 - j][c];
+                o[c] = a;
+            }
+            if (ch_ok)
+                *reinterpret_cast<uint2*>(dx + ((long)b * T + t0 + tt) * D + d0) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+        }
+    }
+    // ---- the eight warps' partials -> one per CTA (fixed order)
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem_cb);          // [8 warps][CB_CH * (W + 1)][32 lanes]
+#pragma unroll
+    for (int c = 0; c < CB_CH; ++c)
+#pragma unroll
+        for (int j = 0; j <= W; ++j) red[(sr * CB_CH * (W + 1) + c * (W + 1) + j) * CB_CG + lane] = dwa[c][j];
+    __syncthreads();
+    for (int o = tid; o < CB_CH * (W + 1) * CB_CG; o += 256) {
+        float a = 0.f;
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8) a += red[s8 * CB_CH * (W + 1) * CB_CG + o];
+        const int i = o / CB_CG, cgp = o % CB_CG;
+        const int dd = d_cta + cgp * CB_CH + i / (W + 1);
+        if (dd < D) dw_part[(((long)b * gridDim.y + blockIdx.y) * D + dd) * (W + 1) + i % (W + 1)] = a;
+    }
+}
+
 extern "C" int natsl_short_conv_bwd(const void* x, const void* w, const void* bias, const void* dy, void* dx, float* dw_part,
                                     int B, int T, int D, int W, int silu, int span, void* stream) {
     NATSL_REQUIRE(x && w && dy && dx && dw_part, NATSL_ERR_NULL, "natsl_short_conv_bwd: null pointer");
@@ -425,6 +550,19 @@ extern "C" int natsl_short_conv_bwd(const void* x, const void* w, const void* bi
                   "natsl_short_conv_bwd: bad shape (D a multiple of 8)");
     NATSL_REQUIRE(W == CONV_W, NATSL_ERR_UNSUPPORTED, "natsl_short_conv_bwd: kernel size %d is not built (4)", W);
     const int groups = D / 8;
+    if (span == CB_TT) {
+        constexpr int smem = ((CB_TT + 2 * (CONV_W - 1)) + (CB_TT + CONV_W - 1)) * CB_CG * CB_CH * 2;
+        static_assert(smem >= 8 * CB_CH * (CONV_W + 1) * CB_CG * 4, "the partial sums are reduced over the tiles");
+        cudaError_t e = cudaFuncSetAttribute(short_conv_bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            set_error("natsl_short_conv_bwd: cannot reserve %d B of shared memory (%s)", smem, cudaGetErrorString(e));
+            return NATSL_ERR_CUDA;
+        }
+        dim3 grid((D + CB_CG * CB_CH - 1) / (CB_CG * CB_CH), (T + CB_TT - 1) / CB_TT, B);
+        short_conv_bwd_tile_kernel<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+            bfc(x), bfc(w), bfc(bias), bfc(dy), bfm(dx), dw_part, T, D, silu);
+        return check_launch("natsl_short_conv_bwd");
+    }
     dim3 grid((groups + 127) / 128, (T + span - 1) / span, B);
     short_conv_bwd_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(bfc(x), bfc(w), bfc(bias), bfc(dy), bfm(dx),
                                                                                    dw_part, T, D, silu, span);

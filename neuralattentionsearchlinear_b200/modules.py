@@ -99,7 +99,7 @@ class L2Norm(nn.Module):
 
 class _ShortConvFn(torch.autograd.Function):
     """``natsl_short_conv_fwd`` / ``natsl_short_conv_bwd``: x [B,T,D] bf16, weight [D,1,W], bias [D] or None."""
-    SPAN = 128
+    SPAN = 64            # tokens per partial weight sum; 64 selects the shared-memory tile kernel
 
     @staticmethod
     def forward(ctx, x, weight, bias, silu):
