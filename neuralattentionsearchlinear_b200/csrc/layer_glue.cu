@@ -275,6 +275,43 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
 }
 
+// Narrow rows (D = 64, 128, 256: the per-head norms): D / 8 lanes per row with 16 bytes each, 32 / (D / 8) rows per warp,
+// one pass with the row in registers -- a warp per 128-byte row moves too few bytes per instruction.
+template <int D>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_narrow_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                          const void* __restrict__ w, int w_f32, __nv_bfloat16* __restrict__ y,
+                          __nv_bfloat16* __restrict__ sum_out, long rows, float eps) {
+    constexpr int LPR = D / 8, RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
+    const long row_raw = ((long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const bool ok = row_raw < rows;
+    const long row = ok ? row_raw : rows - 1;                 // keep every lane in the shuffles
+    float a[8], ww[8];
+    ld8(x + row * D + sub * 8, a);
+    if (res) {
+        float r[8];
+        ld8(res + row * D + sub * 8, r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = round_bf16(a[e] + r[e]);
+        if (sum_out && ok) st8(sum_out + row * D + sub * 8, a);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int col = sub * 8 + e;
+        ww[e] = w ? (w_f32 ? reinterpret_cast<const float*>(w)[col] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[col])) : 1.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = a[e] * rstd * ww[e];
+    if (ok) st8(y + row * D + sub * 8, a);
+}
+
 // dx = rstd (dy w - xhat mean(dy w xhat)) (+ dadd);  dw_part [gridDim.x, D] = per-CTA sums of dy xhat.
 template <int D>
 __global__ void __launch_bounds__(256)
@@ -406,19 +443,77 @@ static inline __nv_bfloat16* bfm(void* p) { return reinterpret_cast<__nv_bfloat1
 
 using namespace natsl;
 
+// Forward with the input tile staged in shared memory: one CTA = 128 channels x 64 tokens (+ 3 halo rows), every load
+// issued at once with cp.async; warp s computes the tokens 8 s .. 8 s + 7, a lane four channels.
+constexpr int CF_TT = 64, CF_L = 32, CF_CH = 4;
+__global__ void __launch_bounds__(256)
+short_conv_fwd_tile_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                           const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y, int T, int D, int silu) {
+    constexpr int W = CONV_W, XR = CF_TT + W - 1, ROWB = CF_L * CF_CH * 2, CPR = ROWB / 16;
+    __shared__ __align__(16) unsigned char xs[XR * ROWB];
+    const int tid = threadIdx.x, lane = tid & 31, sr = tid >> 5;
+    const int d_cta = blockIdx.x * CF_L * CF_CH, d0 = d_cta + lane * CF_CH;
+    const int t0 = blockIdx.y * CF_TT, b = blockIdx.z;
+    const bool ch_ok = d0 < D;
+    const uint32_t xs_a = smem_u32(xs);
+    for (int i = tid; i < XR * CPR; i += 256) {
+        const int r = i / CPR, c = i % CPR;
+        const int t = t0 - (W - 1) + r, dd = d_cta + c * 8;
+        const bool ok = t >= 0 && t < T && dd < D;
+        cp_async16(xs_a + r * ROWB + c * 16, ok ? (const void*)(x + ((long)b * T + t) * D + dd) : (const void*)x, ok ? 16 : 0);
+    }
+    cp_async_commit();
+    float wt[CF_CH][W], bs[CF_CH];
+#pragma unroll
+    for (int c = 0; c < CF_CH; ++c) {
+        bs[c] = (bias && ch_ok) ? __bfloat162float(bias[d0 + c]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < W; ++j) wt[c][j] = ch_ok ? __bfloat162float(w[(d0 + c) * W + j]) : 0.f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    static_assert(CF_CH == 4, "a thread reads 8 bytes per row");
+    float win[W][CF_CH];
+    auto row = [&](int r, float (&f)[CF_CH]) {
+        const uint2 v = *reinterpret_cast<const uint2*>(xs + r * ROWB + lane * 8);
+        const float2 a = unpack_bf16(v.x), c = unpack_bf16(v.y);
+        f[0] = a.x; f[1] = a.y; f[2] = c.x; f[3] = c.y;
+    };
+    const int ts = sr * 8;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) row(ts + j, win[j + 1]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+            for (int c = 0; c < CF_CH; ++c) win[j][c] = win[j + 1][c];
+        row(ts + i + W - 1, win[W - 1]);
+        float o[CF_CH];
+#pragma unroll
+        for (int c = 0; c < CF_CH; ++c) {
+            float a = bs[c];
+#pragma unroll
+            for (int j = 0; j < W; ++j) a += wt[c][j] * win[j][c];
+            o[c] = silu ? a * sigmoidf_(a) : a;
+        }
+        if (ch_ok && t0 + ts + i < T)
+            *reinterpret_cast<uint2*>(y + ((long)b * T + t0 + ts + i) * D + d0) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+    }
+}
+
 extern "C" int natsl_short_conv_fwd(const void* x, const void* w, const void* bias, void* y, int B, int T, int D, int W,
                                     int silu, void* stream) {
     NATSL_REQUIRE(x && w && y, NATSL_ERR_NULL, "natsl_short_conv_fwd: null pointer");
     NATSL_REQUIRE(B > 0 && T > 0 && D > 0 && D % 8 == 0 && B <= 65535, NATSL_ERR_BAD_SHAPE,
                   "natsl_short_conv_fwd: bad shape (D a multiple of 8)");
     NATSL_REQUIRE(W == CONV_W, NATSL_ERR_UNSUPPORTED, "natsl_short_conv_fwd: kernel size %d is not built (4)", W);
-    const int groups = D / 8;
-    dim3 grid((groups + 127) / 128, (T + CONV_TT - 1) / CONV_TT, B);
-    short_conv_fwd_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(bfc(x), bfc(w), bfc(bias), bfm(y), T, D, silu);
+    dim3 grid((D + CF_L * CF_CH - 1) / (CF_L * CF_CH), (T + CF_TT - 1) / CF_TT, B);
+    short_conv_fwd_tile_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(bfc(x), bfc(w), bfc(bias), bfm(y), T, D, silu);
     return check_launch("natsl_short_conv_fwd");
 }
 
-// The same backward for span = 64 with the tiles staged in shared memory: one CTA = 256 channels x 64 tokens, all loads
+// The same backward for span = 64 with the tiles staged in shared memory: one CTA = 128 channels x 64 tokens, all loads
 // of the x tile (64 + 6 halo rows) and the dy tile (64 + 3) are issued at once with cp.async (the sliding-window form
 // above has two loads in flight per thread and is bound by their latency), warp s computes the tokens 8 s .. 8 s + 7 for
 // 32 groups of 8 channels, and the eight warps' weight-gradient partials are summed in shared memory in a fixed order:
@@ -588,6 +683,16 @@ extern "C" int natsl_rmsnorm_fwd(const void* x, const void* res, const void* w, 
     NATSL_REQUIRE(rows > 0, NATSL_ERR_BAD_SHAPE, "natsl_rmsnorm_fwd: empty input");
     NATSL_REQUIRE(w_dtype == NATSL_DT_BF16 || w_dtype == NATSL_DT_F32, NATSL_ERR_UNSUPPORTED, "natsl_rmsnorm_fwd: weight must be bf16 or f32");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (D == 64 || D == 128 || D == 256) {
+        const int rpc = 8 * (32 / (D / 8));                  // rows per CTA
+        const unsigned gridn = (unsigned)((rows + rpc - 1) / rpc);
+#define NATSL_NARROW(DD) rmsnorm_fwd_narrow_kernel<DD><<<gridn, 256, 0, st>>>(bfc(x), bfc(res), w, w_dtype == NATSL_DT_F32, bfm(y), bfm(sum_out), rows, eps)
+        if (D == 64) NATSL_NARROW(64);
+        else if (D == 128) NATSL_NARROW(128);
+        else NATSL_NARROW(256);
+#undef NATSL_NARROW
+        return check_launch("natsl_rmsnorm_fwd");
+    }
     const unsigned grid = (unsigned)((rows + 7) / 8);
 #define NATSL_CALL(DD) rmsnorm_fwd_kernel<DD><<<grid, 256, 0, st>>>(bfc(x), bfc(res), w, w_dtype == NATSL_DT_F32, bfm(y), bfm(sum_out), rows, eps)
     NATSL_ROW_DISPATCH(NATSL_CALL)

@@ -13,61 +13,52 @@ __device__ __forceinline__ float load_scalar(const void* p, int dtype, long i) {
                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
+// D / 8 lanes per row with 16 bytes each (32 / (D / 8) rows per warp): one pass, the three rows in registers.
 template <int D>
 __global__ void __launch_bounds__(256)
 norm_gate_mix_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __restrict__ x2,
                      const __nv_bfloat16* __restrict__ g, const void* __restrict__ xw, int xw_dtype,
                      const void* __restrict__ w1, const void* __restrict__ w2, int w_dtype,
                      __nv_bfloat16* __restrict__ y, long rows, float eps, int activation) {
-    constexpr int EPL = D / 32;                       // elements per lane (2, 4 or 8)
-    const int lane = threadIdx.x & 31;
-    const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const long base = row * D + lane * EPL;
-    float a[EPL], b[EPL], gg[EPL];
+    constexpr int LPR = D / 8, RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
+    const long row_raw = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + lane / LPR;
+    const bool ok = row_raw < rows;
+    const long row = ok ? row_raw : rows - 1;                 // keep every lane in the shuffles
+    const long base = row * D + sub * 8;
+    float a[8], b[8], gg[8];
     auto load = [&](const __nv_bfloat16* p, float* out) {
-        if (EPL == 8) {
-            uint4 v = *reinterpret_cast<const uint4*>(p + base);
-            const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
+        const uint4 v = *reinterpret_cast<const uint4*>(p + base);
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { float2 f = unpack_bf16(u[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
-        } else if (EPL == 4) {
-            uint2 v = *reinterpret_cast<const uint2*>(p + base);
-            float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y);
-            out[0] = f0.x; out[1] = f0.y; out[2] = f1.x; out[3] = f1.y;
-        } else {
-            float2 f = unpack_bf16(*reinterpret_cast<const uint32_t*>(p + base));
-            out[0] = f.x; out[1] = f.y;
-        }
+        for (int i = 0; i < 4; ++i) { float2 f = unpack_bf16(u[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
     };
     load(x1, a);
     load(x2, b);
     load(g, gg);
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) { s1 += a[i] * a[i]; s2 += b[i] * b[i]; }
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
+    for (int i = 0; i < 8; ++i) { s1 += a[i] * a[i]; s2 += b[i] * b[i]; }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
     const float r1 = rsqrtf(s1 / D + eps), r2 = rsqrtf(s2 / D + eps);
     float m1 = 1.f, m2 = 1.f;
     if (xw) { m1 = load_scalar(xw, xw_dtype, row * 2); m2 = load_scalar(xw, xw_dtype, row * 2 + 1); }
-    float out[EPL];
+    float out[8];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-        const int d = lane * EPL + i;
+    for (int i = 0; i < 8; ++i) {
+        const int d = sub * 8 + i;
         const float ww1 = w1 ? load_scalar(w1, w_dtype, d) : 1.f, ww2 = w2 ? load_scalar(w2, w_dtype, d) : 1.f;
         const float v = a[i] * r1 * ww1 * m1 + b[i] * r2 * ww2 * m2;
         const float sg = 1.f / (1.f + __expf(-gg[i]));
         out[i] = activation == 1 ? v * sg : v * gg[i] * sg;
     }
-    if (EPL == 8) {
+    if (ok)
         *reinterpret_cast<uint4*>(y + base) = make_uint4(pack_bf16(out[0], out[1]), pack_bf16(out[2], out[3]),
-                                                         pack_bf16(out[4 % EPL], out[5 % EPL]), pack_bf16(out[6 % EPL], out[7 % EPL]));
-    } else if (EPL == 4) {
-        *reinterpret_cast<uint2*>(y + base) = make_uint2(pack_bf16(out[0], out[1]), pack_bf16(out[2 % EPL], out[3 % EPL]));
-    } else {
-        *reinterpret_cast<uint32_t*>(y + base) = pack_bf16(out[0], out[1]);
-    }
+                                                         pack_bf16(out[4], out[5]), pack_bf16(out[6], out[7]));
 }
 
 
@@ -183,7 +174,8 @@ extern "C" int natsl_norm_gate_mix(const void* x1, const void* x2, const void* g
                   NATSL_ERR_UNSUPPORTED, "natsl_norm_gate_mix: weights must be bf16 or f32");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int wpb = 8;
-    const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+    const long rpc = (long)wpb * (32 / (D > 0 ? (D / 8 > 0 ? D / 8 : 1) : 1));      // rows per CTA
+    const unsigned grid = (unsigned)((rows + rpc - 1) / rpc);
 #define NATSL_NG(DD) norm_gate_mix_kernel<DD><<<grid, wpb * 32, 0, st>>>( \
         reinterpret_cast<const __nv_bfloat16*>(x1), reinterpret_cast<const __nv_bfloat16*>(x2), \
         reinterpret_cast<const __nv_bfloat16*>(g), xw, xw_dtype, w1, w2, w_dtype, reinterpret_cast<__nv_bfloat16*>(y), rows, eps, activation)
