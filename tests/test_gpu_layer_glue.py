@@ -19,7 +19,8 @@ def close(got, ref, what, tol=TOL):
 
 
 @pytest.mark.parametrize("B,T,D,bias,act", [(2, 100, 64, False, "silu"), (1, 1000, 1024, False, "silu"), (2, 77, 128, True, "silu"),
-                                            (1, 300, 256, False, None), (3, 3, 64, False, "silu")])
+                                            (1, 300, 256, False, None), (3, 3, 64, False, "silu"), (1, 130, 72, True, "silu"),
+                                            (2, 64, 136, False, "silu")])
 def test_short_conv(B, T, D, bias, act):
     from neuralattentionsearchlinear_b200.modules import ShortConvolution
     torch.manual_seed(T + D)
@@ -43,7 +44,8 @@ def test_short_conv(B, T, D, bias, act):
 
 
 @pytest.mark.parametrize("D,rows_shape,with_res", [(64, (2, 50, 4), False), (128, (3, 33, 2), False), (1024, (2, 70), True),
-                                                   (2048, (1, 40), True), (256, (5, 7), False), (512, (4, 9), True)])
+                                                   (2048, (1, 40), True), (256, (5, 7), False), (512, (4, 9), True), (128, (3, 5), True),
+                                                   (256, (1, 3), True), (64, (1, 1), False)])
 def test_rmsnorm(D, rows_shape, with_res):
     from neuralattentionsearchlinear_b200.modules import RMSNorm
     torch.manual_seed(D)
