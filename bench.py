@@ -251,7 +251,33 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize(dev)
     if rank == 0:
         clocks.rows.clear()          # keep only samples taken under load
-    # ---- device-resident throughput
+    # ---- device-resident throughput.  The step (tables, both branches on their two streams) is captured once into a
+    # CUDA graph and replayed: the timed region then holds device work only, whatever the host does meanwhile (issuing
+    # the step eagerly takes about as long on the host as it runs on the device, so a busy host shows up in the number).
+    # The eager figure is reported beside it.
+    graph, launches_per_step = None, None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                g_ = torch.cuda.CUDAGraph()
+                n0 = _lib.kernel_launches()
+                with torch.cuda.graph(g_, stream=side):
+                    g_out = step(d)
+                launches_per_step = _lib.kernel_launches() - n0
+            stream.wait_stream(side)
+            torch.cuda.synchronize(dev)
+            g_.replay()
+            torch.cuda.synchronize(dev)
+            ref_out = step(d)
+            torch.cuda.synchronize(dev)
+            if all(torch.equal(a, b) for a, b in zip(g_out, ref_out)):
+                graph = g_
+        except Exception as exc:                            # capture is an optimisation of the measurement, not a need
+            print(f"[bench] CUDA graph capture of the step failed ({type(exc).__name__}: {exc}); timing eagerly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize(dev)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = _lib.kernel_launches()
@@ -261,7 +287,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e1.record(stream)
     gpu_launches = _lib.kernel_launches() - launches_before      # kernels of this library launched in the timed region
     barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_eager = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    ms_total = ms_eager * args.steps
+    if graph is not None:
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        gpu_launches = launches_per_step * args.steps
+        out = g_out
     if rank == 0 and len(clocks.rows) < 3 and args.min_warm_seconds > 0:
         # the timed region was shorter than the sampling period: keep the same load up until a few samples exist
         t_w = time.perf_counter()
@@ -473,6 +512,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "pipelining": "uploads, compute and downloads of neighbouring steps overlap (three streams, two buffer sets)"},
+        "launch": "one CUDA graph per step, replayed" if graph is not None else "eager", "ms_per_step_eager": ms_eager,
         "kernel_ms": kernel_ms, "roofline": roofline, "roofline_all": roofs,
         "cpu_baseline": {"value": cpu_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": cpu_sample},
@@ -964,6 +1004,8 @@ def main():
                     help="gdn_layer: the headline single-GPU layer configuration (default); mamba_long: the long-context "
                          "Mamba2 layer, sequence-parallel over the ranks; model_prefill / model_fwdbwd: the 24-layer "
                          "decoder models (prefill of 16 x 4096 tokens; forward + backward of 8 x 4096 tokens per GPU)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="default workload: time the eagerly issued step instead of its CUDA-graph replay")
     ap.add_argument("--no-sp", action="store_true",
                     help="gdn_layer with N > 1: leave out the sequence-parallel long-context measurement (sp_long_context)")
     ap.add_argument("--layers", type=int, default=0, help="model workloads: number of layers (default 24)")
