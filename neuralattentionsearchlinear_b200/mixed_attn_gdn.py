@@ -34,10 +34,11 @@ def _get_attn_stream(device: torch.device) -> torch.cuda.Stream:
 
 
 _lin_streams: dict = {}
-# Optional: the linear branch (chunk preparation -> walk) on a high-priority stream, so that its CTAs are placed ahead
-# of the softmax branch's remaining ones whenever an SM frees up.  Off by default: measured, it changes the step time by
-# less than the run-to-run noise (0.74 - 0.80 ms in every combination with the split walk).
-LINEAR_BRANCH_PRIORITY = os.environ.get("NATSL_LINEAR_PRIORITY", "0") == "1"
+# The linear branch (chunk preparation -> walk) runs on a high-priority stream, so that its CTAs are placed ahead of the
+# softmax branch's remaining ones whenever an SM frees up: the serial walk then starts earlier and the attention CTAs
+# fill in around it.  Measured with the step replayed from a CUDA graph: 0.621 - 0.633 ms against 0.640 - 0.644 ms
+# (three runs each); NATSL_LINEAR_PRIORITY=0 puts the branch back on the caller's stream.
+LINEAR_BRANCH_PRIORITY = os.environ.get("NATSL_LINEAR_PRIORITY", "1") != "0"
 
 
 def _get_linear_stream(device: torch.device) -> torch.cuda.Stream:
