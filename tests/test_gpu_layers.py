@@ -102,3 +102,55 @@ def test_layers_refuse_unbuilt_paths():
         mamba(torch.randn(1, 128, 128, device="cuda", dtype=torch.bfloat16), cache_params=nat.NAtSCache())
     with pytest.raises(NotImplementedError):             # fewer than 64 tokens without a cache
         mamba(x)
+
+
+@pytest.mark.parametrize("rule", ["gdn", "mamba"])
+def test_ops_replay_from_a_cuda_graph(rule):
+    """Both ops can be captured into a CUDA graph after one eager call (they fork and join their side streams with
+    events, allocate through torch and never synchronise the host); a replay on new input contents equals the eager op."""
+    import neuralattentionsearchlinear_b200 as nat
+    from oracle import tables as otab
+    from tests.helpers import synth_gdn_inputs, synth_mamba_inputs
+    B, T, H, K, V, nbs = 2, 512, 4, 128, 128, 64
+    dev = torch.device("cuda")
+
+    def inputs(seed):
+        if rule == "gdn":
+            q, k, v, g, beta, _ = synth_gdn_inputs(B, T, H, K, V, seed=seed)
+        else:
+            q, k, v, g, _ = synth_mamba_inputs(B, T, H, K, V, seed=seed)
+            beta = torch.zeros(B, T, H).bfloat16()
+        types = otab.synth_types(B, T // nbs, H, 0.3, seed=seed + 1)
+        return [x.to(dev) for x in (q, k, v, g, beta, types)]
+
+    def op(q, k, v, g, beta, types):
+        if rule == "gdn":
+            return nat.nats_mixed_attn_gdn(q, k, v, q, k, v, None, g, beta, types, None, nats_block_size=nbs,
+                                           ops_for_incomplete_chunks="all", output_final_state_gated_delta=True,
+                                           decay_for_non_gdn_blocks=True)
+        return nat.nats_mixed_attn_mamba(q, k, v, q, k, v, None, g, types, None, scale_attn=K ** -0.5, nats_block_size=nbs,
+                                         ops_for_incomplete_chunks="all", output_final_state_mamba=True,
+                                         decay_for_non_mamba_blocks=True)
+
+    static = inputs(1)
+    with torch.no_grad():
+        op(*static)                                        # eager warm-up (per-device look-ups happen here)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                outs = op(*static)
+        torch.cuda.current_stream().wait_stream(side)
+        fresh = inputs(7)
+        for dst, src in zip(static, fresh):
+            dst.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = op(*fresh)
+        torch.cuda.synchronize()
+    for a, b in zip(outs, ref):
+        assert torch.equal(a, b)
+    from neuralattentionsearchlinear_b200 import _lib
+    assert _lib.load().natsl_device_status() == 0
