@@ -127,11 +127,13 @@ def test_sub_segment_split_matches_plain_op(B, T, nbs, splits, decay):
     assert _lib.load().natsl_device_status() == 0
 
 
+@pytest.mark.parametrize("persistent", [False, True])
 @pytest.mark.parametrize("DK,DV,nbs", [(128, 64, 256), (64, 128, 64), (128, 128, 128)])
-def test_attn_split_equals_concatenated_keys(DK, DV, nbs):
+def test_attn_split_equals_concatenated_keys(DK, DV, nbs, persistent, monkeypatch):
     """Keys held in two tensors (gathered part shared by two local segments + own part) against one call per
-    segment on the concatenated keys: bit-identical."""
+    segment on the concatenated keys: bit-identical (both forms of the kernel)."""
     from neuralattentionsearchlinear_b200 import _lib, _ops
+    monkeypatch.setattr(_ops, "ATTN_PERSISTENT", persistent)
     from neuralattentionsearchlinear_b200.nats_util import build_selection_tables
     dev = torch.device("cuda", 0)
     B_rem, n_loc, S, L, HQ, HKV = 2, 2, 1024, 768, 4, 2
@@ -151,10 +153,12 @@ def test_attn_split_equals_concatenated_keys(DK, DV, nbs):
     assert _lib.load().natsl_device_status() == 0
 
 
+@pytest.mark.parametrize("persistent", [False, True])
 @pytest.mark.parametrize("DK,DV,nbs,HKV,HN", [(128, 64, 128, 4, 2), (64, 64, 256, 2, 2)])
-def test_attn_split_packed_pairs_equals_head_major(DK, DV, nbs, HKV, HN):
+def test_attn_split_packed_pairs_equals_head_major(DK, DV, nbs, HKV, HN, persistent, monkeypatch):
     """The gathered keys as packed (block, head) pairs against the padded head-major layout: bit-identical."""
-    from neuralattentionsearchlinear_b200 import _lib
+    from neuralattentionsearchlinear_b200 import _lib, _ops
+    monkeypatch.setattr(_ops, "ATTN_PERSISTENT", persistent)
     from neuralattentionsearchlinear_b200.sequence_parallel import CudaSegmentOps, virtual_attn_types
     dev = torch.device("cuda", 0)
     be = CudaSegmentOps()
