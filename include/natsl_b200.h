@@ -338,6 +338,14 @@ int natsl_swiglu_bwd(const void* a, const void* b, const void* dy, void* da, voi
  * Replaces: fla mean_pooling, src/nats/layers/natsl_attn_gdn.py:412-416 (src/nats/ops/utils/pooling.py:26-57). */
 int natsl_block_mean(const void* x, void* y, int B, int T, int D, int nbs, void* stream);
 
+/* Cross entropy of bf16 logits [rows, vocab] (vocab a multiple of 8), row by row: loss_rows[r] = logsumexp(l) - l[y_r]
+ * (0 where y_r == ignore_index), and the logits are overwritten with (softmax(l) - onehot(y_r)) * inv_denom (0 for
+ * ignored rows) in bf16 -- the slice-wise loss + gradient of the language-model head.  labels: int64.
+ * Replaces: the loss part of FusedLinearCrossEntropyLoss as called at
+ * src/nats/models/natsl_attn_gdn/modeling_natsl_attn_gdn.py:474-491. */
+int natsl_xent_rows(void* logits, const void* labels, float* loss_rows, long rows, int vocab, long ignore_index,
+                    float inv_denom, void* stream);
+
 /* Gated-delta-rule branch forward (prep -> recurrence -> output) that allocates nothing and asks
  * the caller for no intermediate buffers: they live in a fixed NATSL_NOALLOC_SCRATCH_BYTES array
  * inside the library, one per GPU, shared by all calls (overlapping calls on one GPU race; the

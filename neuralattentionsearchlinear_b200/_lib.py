@@ -64,6 +64,7 @@ PROTOTYPES = {
     "natsl_swiglu_fwd": [_p, _p, _p, C.c_long, _p],
     "natsl_swiglu_bwd": [_p, _p, _p, _p, _p, C.c_long, _p],
     "natsl_block_mean": [_p, _p, _i, _i, _i, _i, _p],
+    "natsl_xent_rows": [_p, _p, _p, C.c_long, _i, C.c_long, _f, _p],
     "natsl_gdn_fwd_noalloc": [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p],
 }
 NOALLOC_SCRATCH_BYTES = 32 << 20

@@ -740,3 +740,87 @@ extern "C" int natsl_block_mean(const void* x, void* y, int B, int T, int D, int
     block_mean_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(bfc(x), bfm(y), T, D, nbs, NB);
     return check_launch("natsl_block_mean");
 }
+
+// ------------------------------------------------------------------------------------------------ cross entropy rows
+// One CTA per row of bf16 logits [rows, vocab]: loss_rows[r] = (logsumexp(l) - l[y]) if y != ignore else 0, and the
+// logits are overwritten with their gradient (softmax(l) - onehot(y)) * inv_denom (zero for ignored rows), bf16.
+// Two passes over the row: maximum and sum of exponentials (online, fp32), then the gradient.
+__global__ void __launch_bounds__(256)
+xent_rows_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ loss_rows,
+                 int vocab, long long ignore_index, float inv_denom) {
+    __shared__ float s_m[8], s_s[8];
+    const long row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __nv_bfloat16* lr = logits + row * (long)vocab;
+    const long long y = labels[row];
+    const bool ok = y != ignore_index;
+    const int n8 = vocab / 8;
+    float m = -INFINITY, s = 0.f;
+    for (int i = tid; i < n8; i += 256) {
+        float f[8];
+        natsl::ld8(lr + i * 8, f);
+        float mx = f[0];
+#pragma unroll
+        for (int e = 1; e < 8; ++e) mx = fmaxf(mx, f[e]);
+        const float mn = fmaxf(m, mx);
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += __expf(f[e] - mn);
+        s = s * __expf(m - mn) + acc;
+        m = mn;
+    }
+    for (int i = n8 * 8 + tid; i < vocab; i += 256) {          // tail (vocab not a multiple of 8)
+        const float f = __bfloat162float(lr[i]);
+        const float mn = fmaxf(m, f);
+        s = s * __expf(m - mn) + __expf(f - mn);
+        m = mn;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        const float mn = fmaxf(m, m2);
+        s = (mn == -INFINITY) ? 0.f : s * __expf(m - mn) + s2 * __expf(m2 - mn);
+        m = mn;
+    }
+    if (lane == 0) {
+        s_m[warp] = m;
+        s_s[warp] = s;
+    }
+    __syncthreads();
+    float M = s_m[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) M = fmaxf(M, s_m[w]);
+    float S = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) S += (s_m[w] == -INFINITY) ? 0.f : s_s[w] * __expf(s_m[w] - M);
+    const float lse = M + __logf(S);
+    if (tid == 0) loss_rows[row] = ok ? lse - __bfloat162float(lr[ok ? y : 0]) : 0.f;
+    __syncthreads();                                           // the target logit is read before the row is overwritten
+    const float sc = ok ? inv_denom : 0.f;
+    for (int i = tid; i < n8; i += 256) {
+        float f[8];
+        natsl::ld8(lr + i * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float p = __expf(f[e] - lse) - ((long long)(i * 8 + e) == y ? 1.f : 0.f);
+            f[e] = p * sc;
+        }
+        natsl::st8(lr + i * 8, f);
+    }
+    for (int i = n8 * 8 + tid; i < vocab; i += 256) {
+        const float p = __expf(__bfloat162float(lr[i]) - lse) - ((long long)i == y ? 1.f : 0.f);
+        lr[i] = __float2bfloat16(p * sc);
+    }
+}
+
+extern "C" int natsl_xent_rows(void* logits, const void* labels, float* loss_rows, long rows, int vocab, long ignore_index,
+                               float inv_denom, void* stream) {
+    NATSL_REQUIRE(logits && labels && loss_rows, NATSL_ERR_NULL, "natsl_xent_rows: null pointer");
+    NATSL_REQUIRE(rows > 0 && rows <= 0x7fffffffL && vocab > 0, NATSL_ERR_BAD_SHAPE, "natsl_xent_rows: bad shape");
+    NATSL_REQUIRE((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && vocab % 8 == 0, NATSL_ERR_UNSUPPORTED,
+                  "natsl_xent_rows: rows must be 16-byte aligned (vocab a multiple of 8)");
+    xent_rows_kernel<<<(unsigned)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<__nv_bfloat16*>(logits), reinterpret_cast<const long long*>(labels), loss_rows, vocab,
+        (long long)ignore_index, inv_denom);
+    return check_launch("natsl_xent_rows");
+}

@@ -17,7 +17,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import _lib
 from .modules import RMSNorm, swiglu
+from .nats_util import current_stream_ptr
 from .natsl_attn_gdn import NeuralAttentionSearchLinearAttnGDN
 
 
@@ -190,8 +192,21 @@ class _ChunkedLinearCrossEntropy(torch.autograd.Function):
         d_hidden = torch.empty_like(hidden)
         d_weight = torch.zeros_like(weight, dtype=torch.float32)
         loss = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        use_kernel = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                      and weight.shape[0] % 8 == 0)
         for s in range(0, n, slice_tokens):
             h, y = hidden[s:s + slice_tokens], labels[s:s + slice_tokens]
+            if use_kernel:
+                # one kernel turns the slice's logits into their gradient in place (unscaled: 1/denom is applied to the
+                # two products below, on the device) and returns the rows' losses
+                p = h @ weight.t()
+                rows_loss = torch.empty(p.shape[0], dtype=torch.float32, device=p.device)
+                _lib.call("natsl_xent_rows", p.data_ptr(), y.long().contiguous().data_ptr(), rows_loss.data_ptr(), p.shape[0],
+                          p.shape[1], int(ignore_index), 1.0, current_stream_ptr(p.device))
+                loss += rows_loss.sum()
+                d_hidden[s:s + slice_tokens] = ((p @ weight).float() / denom).to(hidden.dtype)
+                d_weight += (p.t() @ h).float()
+                continue
             logits = (h @ weight.t()).float()
             lse = torch.logsumexp(logits, -1)
             ok = y != ignore_index
@@ -202,6 +217,8 @@ class _ChunkedLinearCrossEntropy(torch.autograd.Function):
             p = (p * (ok[:, None] / denom)).to(hidden.dtype)
             d_hidden[s:s + slice_tokens] = p @ weight
             d_weight += (p.t() @ h).float()
+        if use_kernel:
+            d_weight /= denom
         ctx.save_for_backward(d_hidden, d_weight.to(weight.dtype))
         return loss / denom
 

@@ -117,3 +117,27 @@ def test_two_layer_gradients_against_oracle():
         # bf16 activations through two blocks and the LM head: a few per cent of noise per parameter tensor
         assert cos > 0.99 and rel < 0.15, f"{name}: relative L2 error {rel:.3f}, cosine {cos:.4f}"
     print("largest relative errors:", sorted(worst, reverse=True)[:5])
+
+
+def test_fused_cross_entropy_rows_match_torch():
+    """The loss head (slice-wise logits -> loss and gradients, one kernel per slice for the softmax part) against
+    torch's cross entropy with autograd in fp32 on the same bf16 operands; ignored labels, a ragged last slice."""
+    from neuralattentionsearchlinear_b200.models import _ChunkedLinearCrossEntropy
+    torch.manual_seed(3)
+    n, hdim, vocab = 1000, 256, 4096
+    hidden = (torch.randn(n, hdim) * 0.5).bfloat16().cuda().requires_grad_(True)
+    weight = (torch.randn(vocab, hdim) * 0.05).bfloat16().cuda().requires_grad_(True)
+    labels = torch.randint(0, vocab, (n,)).cuda()
+    labels[::7] = -100
+    loss = _ChunkedLinearCrossEntropy.apply(hidden, weight, labels, -100, 384)
+    loss.backward()
+    h32 = hidden.detach().float().requires_grad_(True)
+    w32 = weight.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy((h32 @ w32.t()).bfloat16().float(), labels, ignore_index=-100)
+    # the straight-through of the bf16 rounding of the logits: differentiate the unrounded expression
+    ref_g = torch.nn.functional.cross_entropy(h32 @ w32.t(), labels, ignore_index=-100)
+    ref_g.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref)))
+    for got, want, what in ((hidden.grad, h32.grad, "d hidden"), (weight.grad, w32.grad, "d weight")):
+        err = (got.float() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-6, (what, err, want.abs().max().item())
