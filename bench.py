@@ -263,7 +263,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             with torch.cuda.stream(side):
                 g_ = torch.cuda.CUDAGraph()
                 n0 = _lib.kernel_launches()
-                with torch.cuda.graph(g_, stream=side):
+                # thread-local error mode: calls made by other threads (NCCL's watchdog) do not break the capture
+                with torch.cuda.graph(g_, stream=side, capture_error_mode="thread_local"):
                     g_out = step(d)
                 launches_per_step = _lib.kernel_launches() - n0
             stream.wait_stream(side)
