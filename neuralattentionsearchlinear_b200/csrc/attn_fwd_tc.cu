@@ -14,7 +14,8 @@
 //             with tcgen05.st over the score buffer it came from; at the end O / l -> bf16 -> shared
 //             memory -> coalesced global stores.
 // While the softmax warps work on tile j the tensor core runs Q K_{j+1}^T and P_{j-1} V_{j-1}.
-// The key-tile list (start key, masked, selected) is computed once per CTA into shared memory.
+// The key-tile list (load coordinate, gathered bit) is computed by the producer warp, its only reader; the other
+// roles need just the tile count, and the softmax warps the selection bits of the blocks under the own span.
 // Same key-tile walk, mask and output conventions as the mma.sync kernel (attn_walk.cuh):
 // src/nats/ops/attns/attns.py:62-353 is the reference kernel this replaces.
 // Every mbarrier wait has an iteration limit; on expiry the CTA records a status, stops issuing
@@ -77,6 +78,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     constexpr int NSB = TcTmem<DV>::NSB, TC_KST = TcTmem<DV>::KST;
     constexpr uint32_t TC_O_COL = TcTmem<DV>::o_col;
 
+    // requested before anything else; first used after the barrier below
+    const int n_past_blocks = __ldg(attn_n_iters + ((long)b * NTq + it) * HN + hn);
     if (tid == 0) {
         mbar_init(bar_q, 1);
         for (int i = 0; i < 4; ++i) {
@@ -115,23 +118,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
-    const TileWalk walk = make_walk(q0, T, nbs, attn_n_iters[((long)b * NTq + it) * HN + hn]);
-    const int n_tiles = walk.n_tiles;
-    const int b_rem = b % B_rem;
-    RemoteKeys rk;
-    rk.k_split = k_split;
-    rk.slots = rem_slots;
-    rk.stride = HKV;
-    rk.base = rem_base ? rem_base + ((long)b_rem * (k_split / (rem_slots * nbs))) * HKV + hkv : nullptr;
-    for (int j = tid; j < min(n_tiles, TC_LIST_CAP); j += TC_THREADS)
-        tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs, rk);
+    // Nothing above waits for global memory: the barrier that publishes the mbarriers and the TMEM address comes
+    // before any table is read.  Each role then fetches what it needs by itself: every warp the tile count; the
+    // producer the tile list (it is the only reader of the index table); the softmax warps the selection bits of the
+    // one or two blocks that the own span touches.
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    auto tile_desc = [&](int j) -> int {
-        return j < TC_LIST_CAP ? tile_list[j] : pack_tile(walk, j, idx, selp, tstride, nbs, rk);
-    };
+    const TileWalk walk = make_walk(q0, T, nbs, n_past_blocks);
+    const int n_tiles = walk.n_tiles;
+    const int b_rem = b % B_rem;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -143,6 +140,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 prefetch_tensormap(&map_vr);
             }
         }
+        RemoteKeys rk;
+        rk.k_split = k_split;
+        rk.slots = rem_slots;
+        rk.stride = HKV;
+        rk.base = rem_base ? rem_base + ((long)b_rem * (k_split / (rem_slots * nbs))) * HKV + hkv : nullptr;
+        for (int j = lane; j < min(n_tiles, TC_LIST_CAP); j += 32)
+            tile_list[j] = pack_tile(walk, j, idx, selp, tstride, nbs, rk);
+        __syncwarp();
+        auto tile_desc = [&](int j) -> int {
+            return j < TC_LIST_CAP ? tile_list[j] : pack_tile(walk, j, idx, selp, tstride, nbs, rk);
+        };
         const int rem_head = rem_base ? 0 : hkv;     // packed pairs have no head axis
         auto load_k = [&](int j) {                    // lane 0 only
             const int td = tile_desc(j), stg = j % TC_KST;
@@ -263,6 +271,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t t_rows = tmem + ((uint32_t)(quad * 32 + half * 16) << 16);
         const uint32_t t_o = t_rows + TC_O_COL;
         float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+        // the own span lies in at most two selection blocks (nbs >= 64 and 64 | q0 - span_start)
+        const int blk0 = walk.span_start / nbs;
+        const bool sel0 = selp[(long)blk0 * tstride] != 0;
+        const bool sel1 = blk0 + 1 < TN && selp[(long)(blk0 + 1) * tstride] != 0;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int sb = j % NSB;
@@ -273,11 +285,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             uint32_t sr[32];
             tmem_ld_16x256b_x8(t_s, sr);
             tmem_ld_wait();
-            const int td = tile_desc(j);
-            if ((td >> 30) & 1) {
+            if (j < walk.n_span) {
                 // own-span tile: per row the visible keys are columns [0, limit] (attn_walk.cuh: visible())
-                const int s0 = (td & TILE_COORD_MASK) + k_split;     // masked tiles lie in the own keys
-                const bool selb = (td >> 31) & 1;
+                const int s0 = walk.span_start + j * ATT_BN;
+                const bool selb = (s0 / nbs == blk0) ? sel0 : sel1;
                 const int blk_end = (s0 / nbs + 1) * nbs;
                 int lim_a = T - 1 - s0, lim_b = lim_a;
                 if (own_chunk) {
