@@ -182,6 +182,19 @@ int natsl_gdn_walk_fused_vsplit(const void* q, const void* k, const void* w, con
                                 const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht,
                                 int B, int T, int H, int HN, int K, int V, int nbs, float scale, int flags, void* stream);
 
+/* Mamba2 / SSD state recurrence and chunk output in one walk on tcgen05 (state kept in TMEM, never written to memory;
+ * q k^T, the decay mask, the scaled v tile, all four products inside the walk): q, k [B,T,H,K] bf16, v [B,T,H,V] bf16,
+ * gcs = chunk-local cumsum of the log decay (natsl_chunk_local_cumsum), outputs o [B,T,H,V] bf16 and ht [B,H,K,V]
+ * fp32.  o == NULL (q may then be NULL): only the recurrence runs and ht is required.  Built for K = 128, V = 64
+ * and any nats_block_size that is a multiple of 64 (an unselected block's chunks update a temporary state which is
+ * rolled back at the end of the block); T <= 65536.
+ * Replaces: chunk_mamba_fwd_h + chunk_fwd_o of the Mamba2 branch (src/nats/ops/mamba/chunk_h.py:139-218,
+ * src/nats/ops/mamba/chunk_o.py:137-198) and chunk_cumsum_non_gated_chunks (src/nats/ops/utils/cumsum.py:136-180);
+ * same results as natsl_linear_fwd_h + natsl_linear_fwd_o with rule NATSL_RULE_MAMBA. */
+int natsl_mamba_walk_fused(const void* q, const void* k, const void* v, const float* gcs, const int32_t* types_i,
+                           const int32_t* indices, const int32_t* n_blocks, const float* h0, void* o, float* ht, int B,
+                           int T, int H, int HN, int K, int V, int nbs, float scale, int flags, void* stream);
+
 /* Reference-precision (fp32 math, CUDA cores) path for fp32 or bf16 tensors (dtype = NATSL_DT_F32 / _BF16 for
  * q, k, v, beta, o): token-by-token linear recurrence with re-roll to the block-start state, and plain masked
  * softmax attention.  ht = state after the last selected block, hstart = block-start state at the end (both

@@ -9,6 +9,7 @@ from . import _lib
 from .nats_util import SelectionTables, cdiv, current_stream_ptr
 
 BF16 = torch.bfloat16
+USE_MAMBA_WALK = os.environ.get("NATSL_MAMBA_WALK", "1") != "0"    # natsl_mamba_walk_fused (K = 128, V = 64)
 USE_FUSED_WALK = True        # K = V = 128, block 64: recurrence + output fused on tcgen05 (natsl_gdn_walk_fused)
 # value dimension of the fused walk split over two CTAs (natsl_gdn_walk_fused_vsplit, T <= 8192): half an SM per CTA.
 # Off by default: measured alone it is no faster than the one-CTA walk (0.204 vs 0.189 ms at B=8, T=4096, H=16), and
@@ -155,6 +156,9 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
     gcs = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     fused = (rule == _lib.RULE_GDN and K == 128 and V == 128 and nbs == 64 and NT <= 1024 and not return_intermediates
              and not skip_out and own_chunk and USE_FUSED_WALK)
+    # Mamba2 with state dim 128 and head dim 64: recurrence + output (or the recurrence alone) in one tcgen05 walk
+    mamba_fused = (rule == _lib.RULE_MAMBA and K == 128 and V == 64 and NT <= 1024 and not return_intermediates
+                   and own_chunk and USE_MAMBA_WALK and (not skip_out or output_final_state))
     if rule == _lib.RULE_GDN:
         beta = beta.contiguous()
         _need(beta.dtype in (BF16, torch.float32), "beta must be bf16 or fp32", TypeError)
@@ -185,6 +189,12 @@ def linear_fwd(rule: int, q, k, v, g, beta, tables: SelectionTables, scale: floa
                   tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0), o.data_ptr(), _lib.ptr(ht),
                   B, T, H, HN, K, V, nbs, float(scale), flags, st)
         return o, ht, None
+    if mamba_fused:
+        o = None if skip_out else torch.empty(B, T, H, V, dtype=BF16, device=dev)
+        _lib.call("natsl_mamba_walk_fused", None if skip_out else q.data_ptr(), k.data_ptr(), v.data_ptr(), gcs.data_ptr(),
+                  tables.types_i.data_ptr(), tables.indices.data_ptr(), tables.n_blocks.data_ptr(), _lib.ptr(h0),
+                  _lib.ptr(o), _lib.ptr(ht), B, T, H, HN, K, V, nbs, float(scale), flags, st)
+        return o, ht, (dict(gcs=gcs) if skip_out else None)
     state_only = skip_out and ht is not None and not return_intermediates
     h = None if state_only else torch.empty(B, NT, H, K, V, dtype=BF16, device=dev)
     carry = None if state_only else torch.empty(B, NT, H, dtype=torch.float32, device=dev)
